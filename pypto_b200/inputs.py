@@ -1,0 +1,210 @@
+"""Seeded synthetic inputs for the quantized DeepSeek-V3.2 sparse-attention decode path.
+
+The tensors follow the layouts the reference's example drivers hand to the operators
+(examples/models/deepseek_v32_exp/deepseekv32_lightning_indexer_quant.py:358-388 for the
+indexer, deepseekv32_sparse_flash_attention_quant.py:417-441 for the attention): a paged
+cache with 128-token blocks, one block table shared by the indexer cache and the latent cache,
+per-sequence lengths, and one query token (or s1 tokens) per sequence.
+
+Value distributions are the benchmark's (uniform int8 in [-127,127], scales uniform in
+[1e-3,1e-2], bf16 N(0,1) for q and rope, weights N(0,1)/8); the reference's goldens are
+distribution-agnostic.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+BLOCK_SIZE = 128
+IDX_HEADS = 64
+IDX_DIM = 128
+ATT_HEADS = 128
+KV_LORA = 512
+ROPE_DIM = 64
+TOPK = 2048
+PACKED_ROW_BYTES = KV_LORA + 2 * ROPE_DIM + 16  # 656
+
+
+@dataclass
+class DecodeInputs:
+    """All tensors of one decode step. Attribute names are the reference's argument names."""
+
+    b: int
+    s1: int
+    act_seq: List[int]
+    block_num: int
+    max_blocks: int
+    # shared paging state
+    act_seq_key: torch.Tensor = None  # int32 [b]
+    block_table: torch.Tensor = None  # int32 [b, max_blocks], -1 in unused slots
+    # lightning indexer
+    idx_query: Optional[torch.Tensor] = None  # int8 [t, 64, 128]
+    idx_query_scale: Optional[torch.Tensor] = None  # f16|f32 [t, 64]
+    idx_key_cache: Optional[torch.Tensor] = None  # int8 [block_num, 128, 1, 128]
+    idx_key_scale: Optional[torch.Tensor] = None  # f16|f32 [block_num, 128, 1]
+    idx_weight: Optional[torch.Tensor] = None  # f16|f32 [t, 64]
+    # sparse attention
+    query_nope: Optional[torch.Tensor] = None  # bf16 [t*128, 512]
+    query_rope: Optional[torch.Tensor] = None  # bf16 [t*128, 64]
+    key_nope_2d: Optional[torch.Tensor] = None  # int8 [block_num*128, 512]
+    key_rope_2d: Optional[torch.Tensor] = None  # bf16 [block_num*128, 64]
+    k_nope_scales: Optional[torch.Tensor] = None  # f32 [block_num*128, 4]
+    topk_indices: Optional[torch.Tensor] = None  # int32 [t, 2048] (attention-only cases)
+    extras: dict = field(default_factory=dict)
+
+    @property
+    def t(self) -> int:
+        return self.b * self.s1
+
+    def to(self, device) -> "DecodeInputs":
+        out = DecodeInputs(self.b, self.s1, list(self.act_seq), self.block_num, self.max_blocks)
+        for k, v in self.__dict__.items():
+            if isinstance(v, torch.Tensor):
+                setattr(out, k, v.to(device))
+        out.extras = dict(self.extras)
+        return out
+
+    def tensors(self):
+        return {k: v for k, v in self.__dict__.items() if isinstance(v, torch.Tensor)}
+
+
+def make_block_table(act_seq: Sequence[int], gen: torch.Generator, device="cpu", max_blocks: Optional[int] = None):
+    """Random permutation of the physical blocks, handed out to the sequences in order; unused
+    slots hold -1 (same convention as gen_block_table,
+    deepseekv32_sparse_flash_attention_quant.py:257-279)."""
+    per = [math.ceil(s / BLOCK_SIZE) for s in act_seq]
+    block_num = max(sum(per), 1)
+    if max_blocks is None:
+        max_blocks = max(max(per), 1)
+    perm = torch.randperm(block_num, generator=gen, device=device).to(torch.int32)
+    table = torch.full((len(act_seq), max_blocks), -1, dtype=torch.int32, device=device)
+    off = 0
+    for i, n in enumerate(per):
+        table[i, :n] = perm[off:off + n]
+        off += n
+    return block_num, max_blocks, table
+
+
+def _uniform(shape, lo, hi, gen, device, dtype=torch.float32):
+    return (torch.rand(shape, generator=gen, device=device, dtype=torch.float32) * (hi - lo) + lo).to(dtype)
+
+
+def _int8(shape, gen, device):
+    return torch.randint(-127, 128, shape, generator=gen, device=device, dtype=torch.int8)
+
+
+def random_topk_indices(act_seq, s1, gen, device="cpu", topk=TOPK):
+    """Distinct positions per query token, uniform over the causal range; rows shorter than
+    topk list every position and are padded with -1 (the indexer's own padding value)."""
+    b = len(act_seq)
+    out = torch.full((b * s1, topk), -1, dtype=torch.int32, device=device)
+    for bi, s in enumerate(act_seq):
+        for i in range(s1):
+            eff = s - (s1 - 1 - i)
+            if eff <= 0:
+                continue
+            perm = torch.randperm(eff, generator=gen, device=device)[:topk].to(torch.int32)
+            out[bi * s1 + i, : perm.numel()] = perm
+    return out
+
+
+def make_inputs(
+    act_seq: Sequence[int],
+    s1: int = 1,
+    seed: int = 1234,
+    device="cpu",
+    scale_dtype: torch.dtype = torch.float32,
+    with_indexer: bool = True,
+    with_attention: bool = True,
+    with_topk: bool = False,
+    max_blocks: Optional[int] = None,
+    attn_heads: int = ATT_HEADS,
+) -> DecodeInputs:
+    device = torch.device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    act_seq = [int(s) for s in act_seq]
+    b = len(act_seq)
+    t = b * s1
+    block_num, max_blocks, table = make_block_table(act_seq, gen, device, max_blocks)
+    d = DecodeInputs(b, s1, act_seq, block_num, max_blocks)
+    d.block_table = table
+    d.act_seq_key = torch.tensor(act_seq, dtype=torch.int32, device=device)
+    n_rows = block_num * BLOCK_SIZE
+    if with_indexer:
+        d.idx_query = _int8((t, IDX_HEADS, IDX_DIM), gen, device)
+        d.idx_query_scale = _uniform((t, IDX_HEADS), 1e-3, 1e-2, gen, device, scale_dtype)
+        d.idx_key_cache = _int8((block_num, BLOCK_SIZE, 1, IDX_DIM), gen, device)
+        d.idx_key_scale = _uniform((block_num, BLOCK_SIZE, 1), 1e-3, 1e-2, gen, device, scale_dtype)
+        d.idx_weight = (torch.randn((t, IDX_HEADS), generator=gen, device=device) / 8).to(scale_dtype)
+    if with_attention:
+        d.query_nope = torch.randn((t * attn_heads, KV_LORA), generator=gen, device=device).to(torch.bfloat16)
+        d.query_rope = torch.randn((t * attn_heads, ROPE_DIM), generator=gen, device=device).to(torch.bfloat16)
+        d.key_nope_2d = _int8((n_rows, KV_LORA), gen, device)
+        d.key_rope_2d = torch.randn((n_rows, ROPE_DIM), generator=gen, device=device).to(torch.bfloat16)
+        d.k_nope_scales = _uniform((n_rows, 4), 1e-3, 1e-2, gen, device)
+    if with_topk:
+        d.topk_indices = random_topk_indices(act_seq, s1, gen, device)
+    return d
+
+
+def pack_kv_rows(key_nope_2d, key_rope_2d, k_nope_scales):
+    """One 656-byte int8 row per token: 512 int8 latent | 64 bf16 rope | 4 fp32 scales
+    (deepseekv32_sparse_attention_antiquant.py:258-268)."""
+    n = key_nope_2d.shape[0]
+    out = torch.empty((n, PACKED_ROW_BYTES), dtype=torch.int8, device=key_nope_2d.device)
+    out[:, :KV_LORA] = key_nope_2d
+    out[:, KV_LORA:KV_LORA + 2 * ROPE_DIM] = key_rope_2d.contiguous().view(torch.int8)
+    out[:, KV_LORA + 2 * ROPE_DIM:] = k_nope_scales.contiguous().view(torch.int8)
+    return out
+
+
+# --- the five benchmark configurations ------------------------------------------------------
+
+def config_act_seq(config_id: int, seed: Optional[int] = None) -> dict:
+    """Sequence lengths and shapes of benchmark configuration `config_id` (0..4)."""
+    seed = 1234 + config_id if seed is None else seed
+    if config_id == 0:
+        return dict(act_seq=[8192] * 2, s1=1, indexer=False, attention=True, topk=True, seed=seed)
+    if config_id == 1:
+        return dict(act_seq=[32768] * 8, s1=1, indexer=True, attention=False, topk=False, seed=seed)
+    if config_id == 2:
+        g = torch.Generator().manual_seed(seed)
+        act = torch.randint(4096, 65536 + 1, (64,), generator=g).tolist()
+        return dict(act_seq=act, s1=1, indexer=True, attention=True, topk=False, seed=seed)
+    if config_id == 3:
+        return dict(act_seq=[131072] * 128, s1=2, indexer=True, attention=True, topk=False, seed=seed)
+    if config_id == 4:
+        return dict(act_seq=[131072], s1=4096, indexer=True, attention=True, topk=False, seed=seed)
+    raise ValueError(f"unknown config {config_id}")
+
+
+def shard_act_seq(act_seq: Sequence[int], rank: int, world: int) -> List[int]:
+    """Batch partition used for multi-GPU decode: sequences are dealt out longest-first to the
+    rank with the least keys so far (indexer cost is proportional to the keys scanned)."""
+    order = sorted(range(len(act_seq)), key=lambda i: -act_seq[i])
+    loads = [0] * world
+    owner = [0] * len(act_seq)
+    counts = [0] * world
+    cap = math.ceil(len(act_seq) / world)
+    for i in order:
+        cands = [r for r in range(world) if counts[r] < cap]
+        r = min(cands, key=lambda r_: loads[r_])
+        owner[i] = r
+        loads[r] += act_seq[i]
+        counts[r] += 1
+    return [i for i in range(len(act_seq)) if owner[i] == rank]
+
+
+def make_config(config_id: int, device="cpu", rank: int = 0, world: int = 1,
+                scale_dtype=torch.float32, seed: Optional[int] = None) -> DecodeInputs:
+    c = config_act_seq(config_id, seed)
+    act = c["act_seq"]
+    if world > 1:
+        mine = shard_act_seq(act, rank, world)
+        act = [act[i] for i in mine]
+    return make_inputs(act, s1=c["s1"], seed=c["seed"] + 1000 * rank, device=device, scale_dtype=scale_dtype,
+                       with_indexer=c["indexer"], with_attention=c["attention"], with_topk=c["topk"])

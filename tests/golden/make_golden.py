@@ -1,0 +1,179 @@
+#!/usr/bin/env python3
+"""Generate the committed golden vectors by running the REFERENCE's own torch goldens.
+
+Run once, in a container that has the reference checkout (default /root/reference, or
+$PYPTO_REFERENCE):
+
+    python tests/golden/make_golden.py
+
+The reference's example drivers import `torch_npu` and `pypto` at module level; neither exists
+off an Ascend host, so permissive stub modules are installed in `sys.modules` first. Only the
+drivers' pure-torch golden functions are called:
+
+  * lightning_indexer_compute  (examples/models/deepseek_v32_exp/deepseekv32_lightning_indexer_quant.py:184-269)
+  * its ST twin that also returns first_mm / mm_out
+    (framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_lightning_indexer.py:282-360)
+  * compute_attention_no_flash / compute_attention
+    (examples/models/deepseek_v32_exp/deepseekv32_sparse_flash_attention_quant.py:169-254, :49-166)
+  * compute_attention_aq       (examples/models/deepseek_v32_exp/deepseekv32_sparse_attention_antiquant.py:49-136)
+
+Inputs come from `pypto_b200.inputs.make_inputs` (seeded); each fixture stores the seed, a sha256
+of every input tensor and the reference's outputs, so the tests regenerate identical inputs
+without the reference being present.
+"""
+from __future__ import annotations
+
+import hashlib
+import importlib
+import os
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+
+from pypto_b200 import inputs as gen  # noqa: E402
+
+REF = Path(os.environ.get("PYPTO_REFERENCE", "/root/reference"))
+
+
+class _Anything(types.ModuleType):
+    """Module stub: any attribute is another stub; calling it works as a pass-through decorator."""
+
+    def __getattr__(self, name):
+        if name.startswith("__") and name.endswith("__"):
+            raise AttributeError(name)
+        child = _Anything(f"{self.__name__}.{name}")
+        setattr(self, name, child)
+        return child
+
+    def __call__(self, *args, **kwargs):
+        if len(args) == 1 and callable(args[0]) and not kwargs:
+            return args[0]
+        return self
+
+    def __mro_entries__(self, bases):
+        return (object,)
+
+
+def load_reference():
+    for name in ("torch_npu", "pypto", "pypto.experimental", "pypto.operation", "pypto.pypto_impl",
+                 "common_func", "golden_register", "ml_dtypes"):
+        if name == "ml_dtypes":
+            try:
+                importlib.import_module(name)
+                continue
+            except ImportError:
+                pass
+        sys.modules[name] = _Anything(name)
+    sys.path.insert(0, str(REF / "examples/models/deepseek_v32_exp"))
+    sys.path.insert(0, str(REF / "framework/tests/st/operator/src/test_deepseek_v3.2_exp"))
+    li = importlib.import_module("deepseekv32_lightning_indexer_quant")
+    sfa = importlib.import_module("deepseekv32_sparse_flash_attention_quant")
+    aq = importlib.import_module("deepseekv32_sparse_attention_antiquant")
+    st_li = importlib.import_module("gen_lightning_indexer")
+    return li, sfa, aq, st_li
+
+
+def sha(t: torch.Tensor) -> str:
+    raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+    return hashlib.sha256(raw).hexdigest()
+
+
+def input_hashes(d: gen.DecodeInputs):
+    return {k: sha(v) for k, v in sorted(d.tensors().items())}
+
+
+def as_np(t: torch.Tensor):
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.int16).numpy()
+    return t.numpy()
+
+
+LI_CASES = {
+    # name: (act_seq, s1, scale dtype)
+    "li_ragged_f32": ([15, 666, 2049, 4100], 1, "float32"),
+    "li_mtp_f16": ([129, 2500, 3000], 2, "float16"),
+    "li_short_f16": ([1, 2048, 2047], 2, "float16"),
+}
+SFA_CASES = {
+    "sfa_ragged_mtp": ([2500, 700, 1], 2),
+    "sfa_single": ([2300], 1),
+}
+
+
+def make_li(li_mod, st_mod, name, act_seq, s1, dt):
+    dtype = getattr(torch, dt)
+    seed = 7000 + sum(act_seq) + s1
+    d = gen.make_inputs(act_seq, s1=s1, seed=seed, scale_dtype=dtype, with_attention=False)
+    params = dict(block_size=128, selected_count=2048, b=d.b, s1=s1, n1=64, d=128, block_num=d.block_num,
+                  max_block_num=d.max_blocks)
+    data = dict(query=d.idx_query.reshape(d.b, s1, 64, 128), key=d.idx_key_cache, q_scale=d.idx_query_scale,
+                k_scale=d.idx_key_scale, weights=d.idx_weight, act_seq=d.act_seq_key, block_table=d.block_table)
+    topk = li_mod.lightning_indexer_compute(dict(data), params).reshape(d.t, 1, 2048)
+    first_mm, mm_out, topk_value, topk2 = st_mod.lightning_indexer_compute(dict(data), params)
+    assert torch.equal(topk.reshape(-1), topk2.reshape(-1).to(torch.int32)), "example and ST goldens disagree"
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed), scale_dtype=dt,
+        hashes=np.array([f"{k}={v}" for k, v in input_hashes(d).items()]),
+        topk_res=topk.numpy().astype(np.int32),
+        mm_out=mm_out.numpy().astype(np.float32),
+        first_mm_sha=sha(first_mm),
+        first_mm_head0=first_mm.reshape(d.t, 64, -1)[:, 0, :].numpy(),
+    )
+    print(name, "t", d.t, "blocks", d.block_num)
+
+
+def make_sfa(sfa_mod, aq_mod, name, act_seq, s1):
+    seed = 9000 + sum(act_seq) + s1
+    d = gen.make_inputs(act_seq, s1=s1, seed=seed, with_indexer=False, with_topk=True)
+    q = torch.cat([d.query_nope.reshape(d.b, s1, 128, 512), d.query_rope.reshape(d.b, s1, 128, 64)], dim=-1)
+    scale = 576 ** -0.5
+    data = [q, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales, d.topk_indices, d.block_table, list(act_seq)]
+    params = [128, scale, 2048, 512, 1]
+    out_nf, _ = sfa_mod.compute_attention_no_flash(data, params, 2048)
+    out_fl, _ = sfa_mod.compute_attention(data, params, 2048)
+    packed = gen.pack_kv_rows(d.key_nope_2d, d.key_rope_2d, d.k_nope_scales)
+    out_aq, _ = aq_mod.compute_attention_aq(
+        [d.query_nope, d.query_rope, packed, d.topk_indices, d.block_table, list(act_seq)],
+        [128, 128, scale, 2048, 512, 64], 2048)
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed),
+        hashes=np.array([f"{k}={v}" for k, v in input_hashes(d).items()]),
+        out_no_flash=as_np(out_nf),
+        # the packed-row golden and the single-tile online golden are stored as digests plus one head
+        out_packed_sha=sha(out_aq), out_packed_equals_no_flash=bool(torch.equal(out_aq, out_nf)),
+        out_flash_sha=sha(out_fl), out_flash_head0=as_np(out_fl[:, :, 0, :]),
+    )
+    print(name, "t", d.t, "rows", d.block_num * 128)
+
+
+def make_gather_kat():
+    """The paged-gather known answer printed in the reference docstring
+    (python/pypto/experimental.py:62-87) and the `10*token + h` buffer pattern of
+    python/tests/st/test_gatherinub.py:83-94, written down as data."""
+    param = np.array([[10 * r + c for c in range(4)] for r in range(6)], dtype=np.float32)
+    np.savez_compressed(HERE / "gather_kat.npz", param=param, indices=np.array([0, 4, 3], dtype=np.int32),
+                        block_table=np.array([0, 2, 1], dtype=np.int32), block_size=np.int32(2),
+                        out=np.array([[0, 1, 2, 3], [20, 21, 22, 23], [50, 51, 52, 53]], dtype=np.float32))
+
+
+def main():
+    torch.set_num_threads(os.cpu_count() or 1)
+    li_mod, sfa_mod, aq_mod, st_mod = load_reference()
+    for name, (act, s1, dt) in LI_CASES.items():
+        make_li(li_mod, st_mod, name, act, s1, dt)
+    for name, (act, s1) in SFA_CASES.items():
+        make_sfa(sfa_mod, aq_mod, name, act, s1)
+    make_gather_kat()
+
+
+if __name__ == "__main__":
+    main()

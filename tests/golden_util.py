@@ -1,0 +1,49 @@
+"""Helpers shared by the tests that use the committed golden fixtures."""
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from pypto_b200 import inputs as gen
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def from_np_bf16(a) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16)
+
+
+def load_case(name: str, **kw):
+    """Regenerate the fixture's inputs from its seed and check them against the stored digests."""
+    z = np.load(GOLDEN / f"{name}.npz")
+    act_seq = [int(x) for x in z["act_seq"]]
+    s1 = int(z["s1"])
+    if name.startswith("li_"):
+        d = gen.make_inputs(act_seq, s1=s1, seed=int(z["seed"]), scale_dtype=getattr(torch, str(z["scale_dtype"])),
+                            with_attention=False)
+    else:
+        d = gen.make_inputs(act_seq, s1=s1, seed=int(z["seed"]), with_indexer=False, with_topk=True)
+    want = dict(h.split("=") for h in z["hashes"])
+    got = {k: sha(v) for k, v in d.tensors().items()}
+    assert got == want, f"regenerated inputs of {name} differ from the ones the fixture was made with"
+    return d, z
+
+
+LI_CASES = ["li_ragged_f32", "li_mtp_f16", "li_short_f16"]
+SFA_CASES = ["sfa_ragged_mtp", "sfa_single"]
+
+
+def mask_empty_rows(want: torch.Tensor, d) -> torch.Tensor:
+    """Zero the rows of a reference attention output whose query token sees no key: the
+    reference golden stores a stale value there (see test_degenerate_rows)."""
+    want = want.clone().reshape(d.b, d.s1, *want.shape[-2:])
+    for bi, s in enumerate(d.act_seq):
+        for i in range(d.s1):
+            if s - d.s1 + 1 + i <= 0:
+                want[bi, i] = 0
+    return want
