@@ -1,0 +1,163 @@
+/*
+ * pypto_b200 — C ABI of the B200 (sm_100a) implementation of the quantized DeepSeek-V3.2
+ * sparse-attention decode path: lightning-indexer score -> exact top-k -> sparse MLA attention.
+ *
+ * Every entry point replaces one operator of the reference's
+ * examples/models/deepseek_v32_exp package (the reference binds its operators through
+ * `pypto.jit`, python/pypto/runtime.py:218-253, which launches on the current stream with device
+ * pointers taken from `pypto.from_torch`, python/pypto/converter.py:36-112). The contract is the
+ * same here: all pointers are DEVICE pointers owned by the caller, outputs are written in place,
+ * the call is asynchronous on `stream`, nothing is retained after the call returns.
+ *
+ * Conventions
+ *   - return value: 0 on success, a negative PTO_ERR_* code otherwise; no exception crosses the
+ *     ABI. `pto_last_error()` gives a thread-local detail string for the last failing call.
+ *   - `workspace` is caller-allocated device scratch of at least `*_workspace_bytes(...)` bytes,
+ *     256-byte aligned. Its first PTO_STATUS_WORDS int32 words are a device status area that the
+ *     kernels set on a rejected page-table entry or an expired bounded wait; read it with
+ *     `pto_workspace_status` (which synchronises the stream).
+ *   - the library allocates no device memory and is re-entrant; calls on different streams need
+ *     different workspaces.
+ *   - t = b * s1 query tokens; the tokens of sequence `bi` are rows bi*s1 .. bi*s1+s1-1.
+ */
+#ifndef PYPTO_B200_H_
+#define PYPTO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* pto_stream_t; /* cudaStream_t */
+
+#define PTO_ABI_VERSION 1
+
+#define PTO_OK 0
+#define PTO_ERR_INVALID (-1)     /* bad argument (null pointer, unsupported shape, misalignment) */
+#define PTO_ERR_WORKSPACE (-2)   /* workspace null or too small */
+#define PTO_ERR_CUDA (-3)        /* a CUDA runtime call or launch failed */
+#define PTO_ERR_UNSUPPORTED (-4) /* device is not sm_100 / feature not built */
+#define PTO_ERR_DRIVER (-5)      /* tensor-map encoding through the driver failed */
+
+/* dtype of idx_query_scale / idx_key_scale / idx_weight */
+#define PTO_DT_F16 0
+#define PTO_DT_F32 1
+
+/* flags of the indexer entry points */
+#define PTO_LI_SCORE_SIMT 0x1 /* score stage on CUDA cores (dp4a) instead of tcgen05; validation aid */
+#define PTO_LI_UNSORTED 0x2   /* leave the selected indices unordered (default: value-descending) */
+
+/* device status area at the start of every workspace */
+#define PTO_STATUS_WORDS 8
+#define PTO_ST_BAD_PAGE 0x1    /* a block-table entry or top-k index outside its range was skipped */
+#define PTO_ST_WAIT_EXPIRED 0x2 /* a bounded mbarrier wait gave up; results are incomplete */
+
+int pto_abi_version(void);
+const char* pto_strerror(int code);
+const char* pto_last_error(void);
+
+/* Copies the status words of `workspace` to `host_out[PTO_STATUS_WORDS]` and synchronises `stream`. */
+int pto_workspace_status(const void* workspace, int32_t* host_out, pto_stream_t stream);
+/* Clears the status area (asynchronous on `stream`). */
+int pto_workspace_reset(void* workspace, pto_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Lightning indexer. Replaces `lightning_indexer_decode`
+ * (examples/models/deepseek_v32_exp/lightning_indexer_quant_impl.py:315-346; score stage :138-194,
+ * top-k stage :196-312; golden deepseekv32_lightning_indexer_quant.py:184-269).
+ *
+ *   idx_query        int8  [t, n_heads=64, head_dim=128]
+ *   idx_query_scale  f16|f32 [t, 64]
+ *   idx_key_cache    int8  [block_num, block_size=128, 1, 128]
+ *   idx_key_scale    f16|f32 [block_num, 128, 1]
+ *   idx_weight       f16|f32 [t, 64]
+ *   act_seq_key      int32 [b]
+ *   block_table      int32 [b, max_blocks]   (-1 in unused slots)
+ *   topk_res         int32 [t, 1, selected_count]   out; value-descending, -1 padded
+ *
+ * score[pos] = k_scale[pos] * sum_h fp32(q_scale_h*weight_h) * fp32(fp16(relu(q_h.k[pos]) / 2048)),
+ * top-k over pos < S_b - (s1 - 1 - i).
+ * ------------------------------------------------------------------------------------------ */
+size_t pto_li_workspace_bytes(int t, int max_blocks, int block_size);
+
+int pto_li_decode(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
+                  const void* idx_key_scale, const void* idx_weight, int scale_dtype,
+                  const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res,
+                  int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
+                  int max_blocks, int selected_count, int flags,
+                  void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* Score stage alone (the reference ST's `mm_out` hook,
+ * framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_lightning_indexer.py:282-360).
+ * scores: f32 [t, max_blocks*block_size]; positions >= S_b are left untouched.
+ * first_mm (optional, may be NULL; SIMT path only): f16 [t*64, max_blocks*block_size]. */
+int pto_li_scores(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
+                  const void* idx_key_scale, const void* idx_weight, int scale_dtype,
+                  const int32_t* act_seq_key, const int32_t* block_table, float* scores, void* first_mm,
+                  int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
+                  int max_blocks, int flags, void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* Top-k stage alone over f32 score rows with row stride `row_stride` elements
+ * (TopKSort/Merge/Extract semantics, lightning_indexer_quant_impl.py:196-312: exact, -1 padded). */
+int pto_li_topk(const float* scores, int64_t row_stride, const int32_t* act_seq_key, int32_t* topk_res,
+                int b, int s1, int selected_count, int flags, void* workspace, size_t workspace_bytes,
+                pto_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Sparse MLA attention over the selected rows. Replaces `sparse_flash_attention_quant_d/_p`
+ * (examples/models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:420-476, :479-538; body
+ * :45-207; golden deepseekv32_sparse_flash_attention_quant.py:169-254).
+ *
+ *   query_nope     bf16 [t*nq, 512]       query_rope   bf16 [t*nq, 64]
+ *   key_nope_2d    int8 [n_rows, 512]     key_rope_2d  bf16 [n_rows, 64]
+ *   k_nope_scales  f32  [n_rows, 4]       topk_indices int32 [t, topk]
+ *   block_table    int32 [b, max_blocks]  kv_act_seqs  int32 [b]
+ *   attention_out  bf16 [b, s1, nq, 512]  out (rows of tokens that see no key are zeroed)
+ *
+ * `q_row_stride_tokens` heads per token in the query/out arrays (= nq unless a head slice
+ * [head_begin, head_begin+nq) of a wider tensor is processed; pass nq_total there).
+ * ------------------------------------------------------------------------------------------ */
+size_t pto_sfa_workspace_bytes(int t, int nq);
+
+int pto_sfa_quant(const void* query_nope, const void* query_rope, const int8_t* key_nope_2d,
+                  const void* key_rope_2d, const float* k_nope_scales, const int32_t* topk_indices,
+                  const int32_t* block_table, const int32_t* kv_act_seqs, void* attention_out,
+                  int b, int s1, int nq, int n_kv, float softmax_scale, int topk, int block_size,
+                  int64_t n_rows, int max_blocks, int nq_total, int head_begin,
+                  void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* Packed-row variant. Replaces `sparse_attention_antiquant_d/_p`
+ * (examples/models/deepseek_v32_exp/sparse_attention_antiquant_impl.py:246-358; golden
+ * deepseekv32_sparse_attention_antiquant.py:49-136). nope_cache: int8 [n_rows, 656] =
+ * 512 int8 latent | 64 bf16 rope | 4 f32 scales. */
+int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t* nope_cache,
+                   const int32_t* topk_indices, const int32_t* block_table, const int32_t* kv_act_seqs,
+                   void* attention_out, int b, int s1, int nq, int n_kv, float softmax_scale, int topk,
+                   int block_size, int64_t n_rows, int max_blocks, int nq_total, int head_begin,
+                   void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused decode chain: indexer -> top-k -> sparse attention on one stream, the order of
+ * `DeepSeekIndexerAttentionQuant`
+ * (framework/src/operator/models/deepseek_v3.2_exp/deepseek_indexer_attention_quant.cpp:170-250).
+ * Both caches share `block_table` / `act_seq`. topk_res (int32 [t,1,selected_count]) is written
+ * too (unordered unless PTO_LI_UNSORTED is cleared in `flags`).
+ * ------------------------------------------------------------------------------------------ */
+size_t pto_decode_workspace_bytes(int t, int max_blocks, int block_size, int nq);
+
+int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
+                     const void* idx_key_scale, const void* idx_weight, int scale_dtype,
+                     const void* query_nope, const void* query_rope, const int8_t* key_nope_2d,
+                     const void* key_rope_2d, const float* k_nope_scales,
+                     const int32_t* act_seq, const int32_t* block_table,
+                     int32_t* topk_res, void* attention_out,
+                     int b, int s1, int block_num, int max_blocks, int selected_count, int nq,
+                     float softmax_scale, int flags,
+                     void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PYPTO_B200_H_ */

@@ -1,0 +1,19 @@
+"""B200-native (sm_100a) implementation of the quantized DeepSeek-V3.2 sparse-attention decode
+path, behind the operator names of the reference's examples/models/deepseek_v32_exp package."""
+import importlib
+
+from .compat import LightningIndexerConfigs, SaTileShapeConfig, Tensor, from_torch  # noqa: F401
+
+_OPS = (
+    "lightning_indexer_decode", "lightning_indexer_scores", "lightning_indexer_topk",
+    "sparse_flash_attention_quant_d", "sparse_flash_attention_quant_p",
+    "sparse_attention_antiquant_d", "sparse_attention_antiquant_p",
+    "decode_indexer_attention_quant", "workspace_status", "reset_workspace_status",
+)
+
+
+def __getattr__(name):
+    # operators resolve lazily so that `pypto_b200.inputs` / `pypto_b200.build` import before the library is built
+    if name in _OPS:
+        return getattr(importlib.import_module(".ops", __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -1,0 +1,246 @@
+// Shared device helpers: PTX wrappers for mbarrier, TMA (no multicast), tcgen05/TMEM, plus the
+// parameter blocks passed from the C ABI to the kernels. sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pypto_b200.h"
+
+namespace pto {
+
+// ---------------------------------------------------------------------------------------------
+// status area (first PTO_STATUS_WORDS int32 of every workspace)
+// word 0: OR of PTO_ST_* flags; word 1: first offending value; word 2: site id of an expired wait
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void set_status(int32_t* status, int flag, int detail, int site = 0) {
+  if (status == nullptr) return;
+  int old = atomicOr(status, flag);
+  if ((old & flag) == 0) {
+    status[1] = detail;
+    status[2] = site;
+  }
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---------------------------------------------------------------------------------------------
+// mbarrier
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: gives up after ~`kWaitBudgetCycles` SM clocks and returns false. Every spin in the
+// library goes through this, so a protocol error turns into a status word, not a hang.
+constexpr long long kWaitBudgetCycles = 2000000000LL;  // about one second at 2 GHz
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMA: tiled 2-D load global -> shared, completion on an mbarrier. No multicast anywhere.
+// x is the innermost (contiguous) coordinate and must make x * elem_size a multiple of 16 bytes.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / TMEM
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// arrives (count 1) on the mbarrier once all previously issued tcgen05.mma of this thread completed
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, int8 x int8 -> int32
+__device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// bf16/f16 x bf16/f16 -> f32
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart (tile base 1024-byte aligned). Advance along K inside the 128-byte row by
+// adding (bytes >> 4) to the low word.
+__device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset: 8 rows * 128 B
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor fields (dense, no negate, no saturate)
+constexpr uint32_t kCFmtF32 = 1, kCFmtS32 = 2;
+constexpr uint32_t kABFmtBF16 = 1, kABFmtS8 = 1;
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major,
+                                                  uint32_t b_mn_major, uint32_t m, uint32_t n) {
+  return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+         ((m >> 4) << 24);
+}
+
+// TMEM -> registers: this warp's 32 lanes, 32 consecutive 32-bit columns each
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// misc
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred)
+      :
+      : "memory");
+  return pred != 0;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// kernel launchers (defined in the .cu files, called from capi.cu)
+// ---------------------------------------------------------------------------------------------
+struct LiParams {
+  const int8_t* q;          // [t*64, 128]
+  const void* q_scale;      // [t, 64]
+  const int8_t* k_cache;    // [block_num*128, 128]
+  const void* k_scale;      // [block_num*128]
+  const void* weight;       // [t, 64]
+  int scale_dtype;          // PTO_DT_*
+  const int32_t* act_seq;   // [b]
+  const int32_t* block_table;  // [b, max_blocks]
+  float* scores;            // [t, row_stride]
+  void* first_mm;           // optional f16 [t*64, row_stride] (SIMT path)
+  int64_t row_stride;
+  int b, s1, block_num, max_blocks;
+  int s1_total;    // query tokens per sequence in memory (>= s1)
+  int tok_offset;  // first token of each sequence handled by this launch
+  int32_t* status;
+};
+
+struct TopkParams {
+  const float* scores;
+  int64_t row_stride;
+  const int32_t* act_seq;
+  int32_t* out;  // [t, k]
+  int b, s1, k, flags;
+  int32_t* status;
+};
+
+struct SfaParams {
+  const __nv_bfloat16* q_nope;  // [t*nq_total, 512]
+  const __nv_bfloat16* q_rope;  // [t*nq_total, 64]
+  const int8_t* kn;             // [n_rows, 512]   (or packed rows when packed != 0)
+  const __nv_bfloat16* kr;      // [n_rows, 64]
+  const float* kn_scales;       // [n_rows, 4]
+  const int32_t* topk;          // [t, topk]
+  const int32_t* block_table;   // [b, max_blocks]
+  const int32_t* act_seq;       // [b]
+  __nv_bfloat16* out;           // [t, nq_total, 512]
+  float* part_o;                // [t, n_split, nq, 512]
+  float* part_ml;               // [t, n_split, nq, 2]
+  int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed;
+  int64_t n_rows;
+  float scale_log2;  // softmax_scale * log2(e)
+  int32_t* status;
+};
+
+cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void* tmap_q, int num_sms,
+                               cudaStream_t stream);
+cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
+cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream);
+cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
+
+}  // namespace pto

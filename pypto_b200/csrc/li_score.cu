@@ -1,0 +1,406 @@
+// Lightning-indexer score stage.
+//
+//   d[h, pos]  = int32( q[h, :] . k[pos, :] )                    64 heads x 128 dims, int8
+//   h16        = fp16( relu(d) * 2^-11 )
+//   score[pos] = k_scale[pos] * sum_h fp32(ws_h) * fp32(h16),    ws_h = q_scale_h * weight_h
+//
+// (reference: examples/models/deepseek_v32_exp/lightning_indexer_quant_impl.py:138-194; golden
+// deepseekv32_lightning_indexer_quant.py:205-241).
+//
+// Tensor-core kernel: persistent CTAs, each owning a contiguous range of the flattened
+// (sequence, page) list. Per page: one TMA load of the 16 KB key page (128 keys x 128 B,
+// 128-byte swizzle) -> four tcgen05.mma kind::i8 (M = 128 keys, N = 64*s1 heads, K = 32) into a
+// TMEM accumulator -> epilogue warps read their key's row (one TMEM lane = one key), apply
+// ReLU/2^-11/fp16 rounding and the weighted head sum, and write the fp32 score.
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2..9 epilogue (two groups
+// of four warps that take alternate pages). All waits are bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pto {
+
+namespace {
+
+constexpr int kLiStages = 6;
+constexpr int kPageKeys = 128;
+constexpr int kPageBytes = kPageKeys * 128;
+constexpr int kHeads = 64;
+constexpr int kQBytesPerToken = kHeads * 128;
+constexpr int kLiThreads = 320;
+constexpr int kMaxS1 = 4;
+constexpr int kMaxSeqPerLaunch = 2048;
+constexpr int kTmemCols = 512;
+
+struct LiCtl {
+  uint64_t full[kLiStages];
+  uint64_t empty[kLiStages];
+  uint64_t accfull[8];
+  uint64_t accempty[8];
+  uint64_t qfull;
+  uint32_t tmem_base;
+  int abort;
+  int prefix[kMaxSeqPerLaunch + 1];
+  __align__(16) float ws[kMaxS1 * kHeads];
+};
+
+constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiStages * kPageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
+
+__device__ __forceinline__ float load_scale(const void* base, int dtype, int64_t i) {
+  if (dtype == PTO_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
+  return reinterpret_cast<const float*>(base)[i];
+}
+
+// ws = q_scale * weight, the product taken in the tensors' own dtype (fp16 product is rounded to
+// fp16 before widening, as the golden does).
+__device__ __forceinline__ float load_ws(const void* qs, const void* w, int dtype, int64_t i) {
+  if (dtype == PTO_DT_F16) {
+    return __half2float(__hmul(reinterpret_cast<const __half*>(qs)[i], reinterpret_cast<const __half*>(w)[i]));
+  }
+  return __fmul_rn(reinterpret_cast<const float*>(qs)[i], reinterpret_cast<const float*>(w)[i]);
+}
+
+// relu(d) * 2^-11 rounded to fp16, for two dots at once; exact for |d| < 2^21:
+// adding d to the bit pattern of 6144.0f (ulp 2^-11) and subtracting 6144 gives d * 2^-11.
+__device__ __forceinline__ float2 relu_scale_round(int d0, int d1) {
+  const float f0 = __int_as_float(0x45C00000 + d0) - 6144.0f;
+  const float f1 = __int_as_float(0x45C00000 + d1) - 6144.0f;
+  __half2 h = __floats2half2_rn(f0, f1);
+  h = __hmax2(h, __float2half2_rn(0.0f));
+  return __half22float2(h);
+}
+
+__device__ __forceinline__ float weighted_sum_32(const uint32_t (&v)[32], const float* ws) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const float4 w = *reinterpret_cast<const float4*>(ws + c);
+    const float2 x = relu_scale_round(static_cast<int>(v[c]), static_cast<int>(v[c + 1]));
+    const float2 y = relu_scale_round(static_cast<int>(v[c + 2]), static_cast<int>(v[c + 3]));
+    a0 = fmaf(w.x, x.x, a0);
+    a1 = fmaf(w.y, x.y, a1);
+    a2 = fmaf(w.z, y.x, a2);
+    a3 = fmaf(w.w, y.y, a3);
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
+__global__ void __launch_bounds__(kLiThreads, 1)
+li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q, LiParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t stage_base = base;
+  const uint32_t q_base = base + kLiStages * kPageBytes;
+  LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiStages * kPageBytes + kMaxS1 * kQBytesPerToken);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int s1 = p.s1;
+  const int n_cols = kHeads * s1;                      // accumulator columns per page
+  const int n_acc = min(8, kTmemCols / n_cols);        // accumulator buffers
+
+  if (tid == 0) {
+    for (int i = 0; i < kLiStages; ++i) {
+      mbar_init(smem_u32(&ctl->full[i]), 1);
+      mbar_init(smem_u32(&ctl->empty[i]), 1);
+    }
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(smem_u32(&ctl->accfull[i]), 1);
+      mbar_init(smem_u32(&ctl->accempty[i]), 4);
+    }
+    mbar_init(smem_u32(&ctl->qfull), 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_q);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    // exclusive prefix of pages per sequence
+    int carry = 0;
+    for (int b0 = 0; b0 < p.b; b0 += 32) {
+      int v = 0;
+      if (b0 + lane < p.b) {
+        int s = p.act_seq[b0 + lane];
+        s = max(s, 0);
+        v = min((s + kPageKeys - 1) / kPageKeys, p.max_blocks);
+      }
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (b0 + lane < p.b) ctl->prefix[b0 + lane] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) ctl->prefix[p.b] = carry;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  const int total = ctl->prefix[p.b];
+  const int it0 = static_cast<int>(static_cast<long long>(total) * blockIdx.x / gridDim.x);
+  const int it1 = static_cast<int>(static_cast<long long>(total) * (blockIdx.x + 1) / gridDim.x);
+
+  const uint32_t idesc = umma_idesc(kCFmtS32, kABFmtS8, kABFmtS8, 0, 0, 128, n_cols);
+
+  int cur = it0;
+  int bi = 0;
+  if (cur < it1) {
+    int lo = 0, hi = p.b;  // largest bi with prefix[bi] <= cur
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (ctl->prefix[mid] <= cur) lo = mid; else hi = mid;
+    }
+    bi = lo;
+  }
+  uint32_t n_item = 0;
+  uint32_t seg = 0;
+
+  while (cur < it1) {
+    while (ctl->prefix[bi + 1] <= cur) ++bi;
+    const int seg_end = min(it1, ctl->prefix[bi + 1]);
+    const int page0 = cur - ctl->prefix[bi];
+    const int npages = seg_end - cur;
+    const int seq_len = p.act_seq[bi];
+
+    __syncthreads();  // previous segment fully drained: Q tile and ws may be overwritten
+    const bool aborted = ctl->abort != 0;
+    if (!aborted) {
+      if (warp == 0 && lane == 0) {
+        mbar_arrive_expect_tx(smem_u32(&ctl->qfull), s1 * kQBytesPerToken);
+        tma_load_2d(q_base, &tmap_q, 0, (bi * p.s1_total + p.tok_offset) * kHeads, smem_u32(&ctl->qfull));
+      }
+      if (tid >= 64 && tid - 64 < s1 * kHeads) {
+        const int e = tid - 64;
+        ctl->ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype,
+                             (static_cast<int64_t>(bi) * p.s1_total + p.tok_offset) * kHeads + e);
+      }
+    }
+    __syncthreads();
+
+    if (!aborted) {
+      if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        const int32_t* bt = p.block_table + static_cast<int64_t>(bi) * p.max_blocks + page0;
+        bool ok = true;
+        for (int j0 = 0; j0 < npages && ok; j0 += 32) {
+          const int mine = (j0 + lane < npages) ? bt[j0 + lane] : 0;
+          const int cnt = min(32, npages - j0);
+          for (int jj = 0; jj < cnt; ++jj) {
+            int phys = __shfl_sync(0xffffffffu, mine, jj);
+            if (lane == 0) {
+              const uint32_t n = n_item + j0 + jj;
+              const uint32_t stage = n % kLiStages;
+              const uint32_t ph = (n / kLiStages) & 1u;
+              if (!mbar_wait(smem_u32(&ctl->empty[stage]), ph ^ 1u)) {
+                ok = false;
+                ctl->abort = 1;
+                set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 1);
+              } else {
+                if (phys < 0 || phys >= p.block_num) {
+                  set_status(p.status, PTO_ST_BAD_PAGE, phys, 1);
+                  phys = p.block_num;  // out of range of the tensor map: the page reads as zeros
+                }
+                const uint32_t bar = smem_u32(&ctl->full[stage]);
+                mbar_arrive_expect_tx(bar, kPageBytes);
+                tma_load_2d(stage_base + stage * kPageBytes, &tmap_k, 0, phys * kPageKeys, bar);
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+          }
+        }
+      } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        bool ok = true;
+        if (lane == 0) {
+          if (!mbar_wait(smem_u32(&ctl->qfull), seg & 1u)) {
+            ok = false;
+            ctl->abort = 1;
+            set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(seg), 2);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        const uint64_t b_desc = umma_desc_kmajor_sw128(q_base);
+        for (int j = 0; j < npages && ok; ++j) {
+          if (lane == 0) {
+            const uint32_t n = n_item + j;
+            const uint32_t stage = n % kLiStages;
+            const uint32_t ph = (n / kLiStages) & 1u;
+            const uint32_t acc = n % n_acc;
+            const uint32_t aph = (n / n_acc) & 1u;
+            if (!mbar_wait(smem_u32(&ctl->full[stage]), ph) || !mbar_wait(smem_u32(&ctl->accempty[acc]), aph ^ 1u)) {
+              ok = false;
+              ctl->abort = 1;
+              set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 3);
+            } else {
+              tc_fence_after();
+              const uint64_t a_desc = umma_desc_kmajor_sw128(stage_base + stage * kPageBytes);
+              const uint32_t d = tmem_base + acc * n_cols;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                mma_i8_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+              }
+              tc_commit(smem_u32(&ctl->empty[stage]));
+              tc_commit(smem_u32(&ctl->accfull[acc]));
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+      } else {
+        // ---------------- epilogue ----------------
+        const int grp = (warp - 2) >> 2;
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        const int row = quarter * 32 + lane;
+        const int32_t* bt = p.block_table + static_cast<int64_t>(bi) * p.max_blocks + page0;
+        for (int j = 0; j < npages; ++j) {
+          const uint32_t n = n_item + j;
+          if (static_cast<int>(n & 1u) != grp) continue;
+          const uint32_t acc = n % n_acc;
+          const uint32_t aph = (n / n_acc) & 1u;
+          const int phys = bt[j];
+          const bool page_ok = phys >= 0 && phys < p.block_num;
+          const float ks = page_ok ? load_scale(p.k_scale, p.scale_dtype, static_cast<int64_t>(phys) * kPageKeys + row) : 0.f;
+          if (!mbar_wait(smem_u32(&ctl->accfull[acc]), aph)) {
+            ctl->abort = 1;
+            set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 4);
+            break;
+          }
+          tc_fence_after();
+          const int pos = (page0 + j) * kPageKeys + row;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * n_cols;
+          for (int i = 0; i < s1; ++i) {
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32b_x32(taddr + i * kHeads, v0);
+            tmem_ld_32x32b_x32(taddr + i * kHeads + 32, v1);
+            tc_wait_ld();
+            const float s = weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32);
+            if (pos < seq_len) {
+              p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = s * ks;
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->accempty[acc]));
+        }
+      }
+    }
+    n_item += npages;
+    cur = seg_end;
+    ++seg;
+  }
+
+  // teardown
+  tc_fence_before();
+  __syncthreads();
+  if (ctl->abort) {
+    // give copies still in flight time to land before the CTA's shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA-core variant (dp4a), one thread per key position. Used to cross-check the tensor-core
+// kernel bit for bit and to produce the `first_mm` debug tile.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+li_score_simt_kernel(LiParams p) {
+  __shared__ __align__(16) int8_t qs[kMaxS1 * kQBytesPerToken];
+  __shared__ float ws[kMaxS1 * kHeads];
+  const int bi = blockIdx.y;
+  const int page = blockIdx.x;
+  const int seq_len = p.act_seq[bi];
+  if (page * kPageKeys >= seq_len) return;
+  const int s1 = p.s1;
+  const int tid = threadIdx.x;
+  {
+    const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset;
+    const int4* src = reinterpret_cast<const int4*>(p.q + tok0 * kQBytesPerToken);
+    int4* dst = reinterpret_cast<int4*>(qs);
+    for (int i = tid; i < s1 * kQBytesPerToken / 16; i += blockDim.x) dst[i] = src[i];
+    for (int e = tid; e < s1 * kHeads; e += blockDim.x) {
+      ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
+    }
+  }
+  __syncthreads();
+  const int phys = p.block_table[static_cast<int64_t>(bi) * p.max_blocks + page];
+  if (phys < 0 || phys >= p.block_num) {
+    if (tid == 0) set_status(p.status, PTO_ST_BAD_PAGE, phys, 5);
+    return;
+  }
+  const int pos = page * kPageKeys + tid;
+  if (pos >= seq_len) return;
+  int4 kreg[8];
+  const int4* krow = reinterpret_cast<const int4*>(p.k_cache + (static_cast<int64_t>(phys) * kPageKeys + tid) * 128);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) kreg[c] = krow[c];
+  const float ks = load_scale(p.k_scale, p.scale_dtype, static_cast<int64_t>(phys) * kPageKeys + tid);
+  for (int i = 0; i < s1; ++i) {
+    float acc = 0.f;
+    for (int h = 0; h < kHeads; ++h) {
+      const int4* qrow = reinterpret_cast<const int4*>(qs + (i * kHeads + h) * 128);
+      int d = 0;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int4 qv = qrow[c];
+        d = __dp4a(kreg[c].x, qv.x, d);
+        d = __dp4a(kreg[c].y, qv.y, d);
+        d = __dp4a(kreg[c].z, qv.z, d);
+        d = __dp4a(kreg[c].w, qv.w, d);
+      }
+      const float f = fmaxf(static_cast<float>(d), 0.f) * (1.0f / 2048.0f);
+      const __half hh = __float2half_rn(f);
+      if (p.first_mm != nullptr) {
+        reinterpret_cast<__half*>(p.first_mm)[((static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * kHeads + h) * p.row_stride + pos] = hh;
+      }
+      acc = fmaf(ws[i * kHeads + h], __half2float(hh), acc);
+    }
+    p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = acc * ks;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void* tmap_q, int num_sms,
+                               cudaStream_t stream) {
+  static bool configured = false;  // attribute is per function, idempotent
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(li_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kLiSmemBytes));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  long long max_items = static_cast<long long>(p.b) * p.max_blocks;
+  int grid = static_cast<int>(max_items < num_sms ? max_items : num_sms);
+  if (grid < 1) grid = 1;
+  li_score_tc_kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
+                                                                 *reinterpret_cast<const CUtensorMap*>(tmap_q), p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream) {
+  dim3 grid(p.max_blocks, p.b);
+  li_score_simt_kernel<<<grid, 128, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+int li_max_s1() { return kMaxS1; }
+int li_max_sequences() { return kMaxSeqPerLaunch; }
+
+}  // namespace pto

@@ -208,3 +208,75 @@ def make_config(config_id: int, device="cpu", rank: int = 0, world: int = 1,
         act = [act[i] for i in mine]
     return make_inputs(act, s1=c["s1"], seed=c["seed"] + 1000 * rank, device=device, scale_dtype=scale_dtype,
                        with_indexer=c["indexer"], with_attention=c["attention"], with_topk=c["topk"])
+
+
+def take_sequences(d: DecodeInputs, seq_ids: Sequence[int], device=None) -> DecodeInputs:
+    """Compact copy holding only the listed sequences: their cache pages are renumbered
+    0..n-1 in block-table order, query rows are sliced. Used to cut a bounded CPU sample out of a
+    large configuration and to hand each rank its batch shard."""
+    device = torch.device(device) if device is not None else d.block_table.device
+    seq_ids = list(seq_ids)
+    act = [d.act_seq[i] for i in seq_ids]
+    per = [math.ceil(s / BLOCK_SIZE) for s in act]
+    max_blocks = max(max(per), 1)
+    block_num = max(sum(per), 1)
+    out = DecodeInputs(len(seq_ids), d.s1, act, block_num, max_blocks)
+    table = torch.full((len(seq_ids), max_blocks), -1, dtype=torch.int32)
+    old_pages = []
+    off = 0
+    for j, (i, n) in enumerate(zip(seq_ids, per)):
+        old_pages.append(d.block_table[i, :n].to("cpu", torch.long))
+        table[j, :n] = torch.arange(off, off + n, dtype=torch.int32)
+        off += n
+    pages = torch.cat(old_pages) if old_pages else torch.zeros(0, dtype=torch.long)
+    if pages.numel() == 0:
+        pages = torch.zeros(1, dtype=torch.long)
+    pages_dev = pages.to(d.block_table.device)
+    rows_dev = (pages_dev[:, None] * BLOCK_SIZE + torch.arange(BLOCK_SIZE, device=pages_dev.device)[None, :]).reshape(-1)
+    tok = torch.tensor([i * d.s1 + k for i in seq_ids for k in range(d.s1)], dtype=torch.long,
+                       device=d.block_table.device)
+    out.block_table = table.to(device)
+    out.act_seq_key = torch.tensor(act, dtype=torch.int32, device=device)
+    if d.idx_query is not None:
+        out.idx_query = d.idx_query[tok].to(device)
+        out.idx_query_scale = d.idx_query_scale[tok].to(device)
+        out.idx_weight = d.idx_weight[tok].to(device)
+        out.idx_key_cache = d.idx_key_cache[pages_dev].to(device)
+        out.idx_key_scale = d.idx_key_scale[pages_dev].to(device)
+    if d.query_nope is not None:
+        nq = d.query_nope.shape[0] // d.t
+        out.query_nope = d.query_nope.reshape(d.t, nq, -1)[tok].reshape(-1, KV_LORA).to(device)
+        out.query_rope = d.query_rope.reshape(d.t, nq, -1)[tok].reshape(-1, ROPE_DIM).to(device)
+        out.key_nope_2d = d.key_nope_2d[rows_dev].to(device)
+        out.key_rope_2d = d.key_rope_2d[rows_dev].to(device)
+        out.k_nope_scales = d.k_nope_scales[rows_dev].to(device)
+    if d.topk_indices is not None:
+        out.topk_indices = d.topk_indices[tok].to(device)
+    return out
+
+
+def algorithmic_bytes(d: DecodeInputs, indexer=True, attention=True, topk=TOPK) -> dict:
+    """Bytes one pass must move at minimum (no scratch): the indexer reads every key and scale of
+    each sequence once, its queries, scales and weights and the used block-table entries, and
+    writes the indices; the attention reads the selected rows (656 B each), q, the indices and
+    writes the output."""
+    s_el = d.idx_key_scale.element_size() if d.idx_key_scale is not None else 4
+    li = 0
+    sfa = 0
+    for s in d.act_seq:
+        if indexer:
+            li += s * (IDX_DIM + s_el) + d.s1 * (IDX_HEADS * IDX_DIM + IDX_HEADS * 2 * s_el) \
+                + 4 * math.ceil(s / BLOCK_SIZE) + d.s1 * topk * 4
+        if attention:
+            for i in range(d.s1):
+                n = min(max(s - d.s1 + 1 + i, 0), topk)
+                sfa += n * PACKED_ROW_BYTES + ATT_HEADS * (KV_LORA + ROPE_DIM) * 2 + 4 * n + ATT_HEADS * KV_LORA * 2
+    return dict(indexer=li, attention=sfa, total=li + sfa)
+
+
+def score_stage_bytes(d: DecodeInputs) -> int:
+    """Algorithmic bytes of the score kernel alone: keys + key scales + queries + q scales/weights
+    + block-table entries (the fp32 score scratch it writes is not algorithmic)."""
+    s_el = d.idx_key_scale.element_size()
+    return sum(s * (IDX_DIM + s_el) + d.s1 * (IDX_HEADS * IDX_DIM + IDX_HEADS * 2 * s_el) + 4 * math.ceil(s / BLOCK_SIZE)
+               for s in d.act_seq)

@@ -1,0 +1,322 @@
+"""Operators of the quantized DeepSeek-V3.2 sparse-attention decode path, with the reference's
+names and positional signatures (examples/models/deepseek_v32_exp):
+
+  lightning_indexer_decode          lightning_indexer_quant_impl.py:315-346
+  sparse_flash_attention_quant_d/_p sparse_flash_attention_quant_impl.py:420-476 / :479-538
+  sparse_attention_antiquant_d/_p   sparse_attention_antiquant_impl.py:246-358
+  decode_indexer_attention_quant    the fused order of
+                                    framework/src/operator/models/deepseek_v3.2_exp/deepseek_indexer_attention_quant.cpp:170-250
+
+Like the reference's `pypto.jit` callables (python/pypto/runtime.py:218-253) they take device
+tensors (raw torch CUDA tensors or `from_torch` handles), write the output tensor in place, return
+None and run asynchronously on the current stream; the caller synchronises. Host-side validation
+raises ValueError / RuntimeError / TypeError before anything is launched. The scratch workspace is
+a cached torch allocation per (device, stream), so a call inside CUDA-graph capture allocates
+nothing once warmed up.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Tuple
+
+import torch
+
+from . import _lib
+from .compat import unwrap
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    stream = torch.cuda.current_stream(device).cuda_stream
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(device=None):
+    """Status words of the current stream's workspace (synchronises the stream).
+    Word 0 is an OR of PTO_ST_BAD_PAGE / PTO_ST_WAIT_EXPIRED."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(device, 256)
+    out = (C.c_int32 * _lib.PTO_STATUS_WORDS)()
+    _lib.check(_lib.load().pto_workspace_status(ws.data_ptr(), out, torch.cuda.current_stream(device).cuda_stream))
+    return list(out)
+
+
+def reset_workspace_status(device=None):
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(device, 256)
+    _lib.check(_lib.load().pto_workspace_reset(ws.data_ptr(), torch.cuda.current_stream(device).cuda_stream))
+
+
+def _need(cond: bool, msg: str):
+    if not cond:
+        raise ValueError(msg)
+
+
+def _same_device(tensors):
+    if not tensors:
+        raise RuntimeError("at least one tensor is required")
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    if dev.type != "cuda":
+        raise RuntimeError(f"tensors are on {dev}; this operator runs on a CUDA device only (no CPU path)")
+    return dev
+
+
+def _scale_dtype(*ts):
+    dt = ts[0].dtype
+    _need(all(t.dtype == dt for t in ts), "idx_query_scale, idx_key_scale and idx_weight must share one dtype")
+    if dt == torch.float16:
+        return _lib.PTO_DT_F16
+    if dt == torch.float32:
+        return _lib.PTO_DT_F32
+    raise ValueError(f"scale dtype {dt}: float16 or float32 expected")
+
+
+def _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key, block_table):
+    q = unwrap(idx_query, "idx_query")
+    qs = unwrap(idx_query_scale, "idx_query_scale")
+    kc = unwrap(idx_key_cache, "idx_key_cache")
+    ks = unwrap(idx_key_scale, "idx_key_scale")
+    w = unwrap(idx_weight, "idx_weight")
+    act = unwrap(act_seq_key, "act_seq_key")
+    bt = unwrap(block_table, "block_table")
+    _need(q.dtype == torch.int8 and q.dim() == 3, "idx_query: int8 [t, n_heads, head_dim]")
+    t, n_heads, head_dim = q.shape
+    _need(kc.dtype == torch.int8 and kc.dim() == 4 and kc.shape[2] == 1 and kc.shape[3] == head_dim,
+          "idx_key_cache: int8 [block_num, block_size, 1, head_dim]")
+    block_num, block_size = kc.shape[0], kc.shape[1]
+    _need(tuple(qs.shape) == (t, n_heads), "idx_query_scale: [t, n_heads]")
+    _need(tuple(w.shape) == (t, n_heads), "idx_weight: [t, n_heads]")
+    _need(ks.numel() == block_num * block_size, "idx_key_scale: [block_num, block_size, 1]")
+    _need(act.dtype == torch.int32 and act.dim() == 1, "act_seq_key: int32 [b]")
+    b = act.shape[0]
+    _need(b >= 1 and t % b == 0, "t must be a multiple of the batch size")
+    _need(bt.dtype == torch.int32 and bt.dim() == 2 and bt.shape[0] == b, "block_table: int32 [b, max_blocks]")
+    sd = _scale_dtype(qs, ks, w)
+    _need(n_heads == 64 and head_dim == 128 and block_size == 128,
+          "indexer geometry: 64 heads x 128 dims, 128-token blocks")
+    dev = _same_device([q, qs, kc, ks, w, act, bt])
+    return dev, (q, qs, kc, ks, w, act, bt), dict(t=t, b=b, s1=t // b, n_heads=n_heads, head_dim=head_dim,
+                                                   block_size=block_size, block_num=block_num,
+                                                   max_blocks=bt.shape[1], scale_dtype=sd)
+
+
+def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                             block_table, topk_res, unroll_list=None, configs=None, selected_count=2048, *,
+                             sort=True, _simt_scores=False):
+    """Top-`selected_count` key positions per query token (value-descending, -1 padded)."""
+    dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
+                                                    idx_weight, act_seq_key, block_table)
+    out = unwrap(topk_res, "topk_res")
+    _need(out.dtype == torch.int32 and out.numel() == m["t"] * selected_count,
+          "topk_res: int32 [t, 1, selected_count]")
+    _need(1 <= selected_count <= 2048, "selected_count must be in [1, 2048]")
+    _need(out.device == dev, "topk_res must be on the same device")
+    lib = _lib.load()
+    nbytes = lib.pto_li_workspace_bytes(m["t"], m["max_blocks"], m["block_size"])
+    flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_SCORE_SIMT if _simt_scores else 0)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_li_decode(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
+                                     m["scale_dtype"], act.data_ptr(), bt.data_ptr(), out.data_ptr(), m["b"], m["s1"],
+                                     m["n_heads"], m["head_dim"], m["block_size"], m["block_num"], m["max_blocks"],
+                                     int(selected_count), flags, ws.data_ptr(), ws.numel(),
+                                     torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def lightning_indexer_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
+                             block_table, scores, first_mm=None, *, simt=False):
+    """Score stage alone: fp32 [t, max_blocks*block_size] (the reference ST's `mm_out` hook);
+    positions at or beyond a sequence's length are left untouched. `first_mm` (fp16
+    [t*64, max_blocks*block_size]) is available with simt=True only."""
+    dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
+                                                    idx_weight, act_seq_key, block_table)
+    sc = unwrap(scores, "scores")
+    stride = m["max_blocks"] * m["block_size"]
+    _need(sc.device == dev and sc.dtype == torch.float32 and tuple(sc.shape) == (m["t"], stride),
+          "scores: float32 [t, max_blocks*block_size]")
+    fm_ptr = None
+    if first_mm is not None:
+        fm = unwrap(first_mm, "first_mm")
+        _need(simt, "first_mm needs simt=True")
+        _need(fm.device == dev and fm.dtype == torch.float16 and tuple(fm.shape) == (m["t"] * m["n_heads"], stride),
+              "first_mm: float16 [t*n_heads, max_blocks*block_size]")
+        fm_ptr = fm.data_ptr()
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, 256)
+        _lib.check(lib.pto_li_scores(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
+                                     m["scale_dtype"], act.data_ptr(), bt.data_ptr(), sc.data_ptr(), fm_ptr, m["b"],
+                                     m["s1"], m["n_heads"], m["head_dim"], m["block_size"], m["block_num"],
+                                     m["max_blocks"], _lib.PTO_LI_SCORE_SIMT if simt else 0, ws.data_ptr(), ws.numel(),
+                                     torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def lightning_indexer_topk(scores, act_seq_key, topk_res, s1=1, selected_count=2048, *, sort=True):
+    """Top-k stage alone over fp32 score rows [t, row_stride]."""
+    sc = unwrap(scores, "scores")
+    act = unwrap(act_seq_key, "act_seq_key")
+    out = unwrap(topk_res, "topk_res")
+    _need(sc.dtype == torch.float32 and sc.dim() == 2, "scores: float32 [t, row_stride]")
+    _need(act.dtype == torch.int32 and act.dim() == 1 and act.shape[0] * s1 == sc.shape[0], "act_seq_key: int32 [t/s1]")
+    _need(out.dtype == torch.int32 and out.numel() == sc.shape[0] * selected_count, "topk_res: int32 [t, 1, k]")
+    _need(1 <= selected_count <= 2048, "selected_count must be in [1, 2048]")
+    dev = _same_device([sc, act, out])
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, 256)
+        _lib.check(lib.pto_li_topk(sc.data_ptr(), sc.shape[1], act.data_ptr(), out.data_ptr(), act.shape[0], int(s1),
+                                   int(selected_count), 0 if sort else _lib.PTO_LI_UNSORTED, ws.data_ptr(), ws.numel(),
+                                   torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv, topk):
+    qn = unwrap(query_nope, "query_nope")
+    qr = unwrap(query_rope, "query_rope")
+    ti = unwrap(topk_indices, "topk_indices")
+    bt = unwrap(block_table, "block_table")
+    act = unwrap(kv_act_seqs, "kv_act_seqs")
+    out = unwrap(attention_out, "attention_out")
+    _need(qn.dtype == torch.bfloat16 and qn.dim() == 2 and qn.shape[1] == 512, "query_nope: bfloat16 [t*nq, 512]")
+    _need(qr.dtype == torch.bfloat16 and tuple(qr.shape) == (qn.shape[0], 64), "query_rope: bfloat16 [t*nq, 64]")
+    _need(int(n_kv) == 1, "n_kv must be 1")
+    _need(qn.shape[0] % nq == 0, "query rows must be a multiple of nq")
+    t = qn.shape[0] // nq
+    _need(ti.dtype == torch.int32 and ti.numel() == t * topk, "topk_indices: int32 [t, n_kv*topk]")
+    _need(act.dtype == torch.int32 and act.dim() == 1 and t % act.shape[0] == 0, "kv_act_seqs: int32 [b]")
+    b = act.shape[0]
+    _need(bt.dtype == torch.int32 and bt.dim() == 2 and bt.shape[0] == b, "block_table: int32 [b, max_blocks]")
+    _need(out.dtype == torch.bfloat16 and out.numel() == t * nq * 512, "attention_out: bfloat16 [b, s1, nq, 512]")
+    return qn, qr, ti, bt, act, out, t, b
+
+
+def _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
+                                  block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
+                                  max_blocknum_perbatch, tile_config=None):
+    qn, qr, ti, bt, act, out, t, b = _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs,
+                                                 attention_out, nq, n_kv, topk)
+    kn = unwrap(key_nope_2d, "key_nope_2d")
+    kr = unwrap(key_rope_2d, "key_rope_2d")
+    sc = unwrap(k_nope_scales, "k_nope_scales")
+    _need(kn.dtype == torch.int8 and kn.dim() == 2 and kn.shape[1] == 512,
+          "key_nope_2d: int8 [block_num*block_size, 512] (the quantized cache)")
+    n_rows = kn.shape[0]
+    _need(kr.dtype == torch.bfloat16 and tuple(kr.shape) == (n_rows, 64), "key_rope_2d: bfloat16 [rows, 64]")
+    _need(sc.dtype == torch.float32 and tuple(sc.shape) == (n_rows, 4), "k_nope_scales: float32 [rows, 4]")
+    _need(bt.shape[1] >= int(max_blocknum_perbatch), "block_table narrower than max_blocknum_perbatch")
+    _need(int(nq) % 16 == 0, "nq must be a multiple of 16")
+    dev = _same_device([qn, qr, kn, kr, sc, ti, bt, act, out])
+    lib = _lib.load()
+    nbytes = lib.pto_sfa_workspace_bytes(t, int(nq))
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_sfa_quant(qn.data_ptr(), qr.data_ptr(), kn.data_ptr(), kr.data_ptr(), sc.data_ptr(),
+                                     ti.data_ptr(), bt.data_ptr(), act.data_ptr(), out.data_ptr(), b, t // b, int(nq),
+                                     int(n_kv), float(softmax_scale), int(topk), int(block_size), n_rows, bt.shape[1],
+                                     int(nq), 0, ws.data_ptr(), ws.numel(),
+                                     torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def sparse_flash_attention_quant_d(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
+                                   block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
+                                   max_blocknum_perbatch, tile_config=None):
+    """Decode entry: attention_out[b, s1, nq, 512] over the selected int8 latent + bf16 rope rows."""
+    return _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales,
+                                         topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv,
+                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config)
+
+
+def sparse_flash_attention_quant_p(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
+                                   block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
+                                   max_blocknum_perbatch, tile_config=None):
+    """Prefill entry: same arithmetic and kernel as the decode entry (the reference differs only
+    in compiler options between the two)."""
+    return _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales,
+                                         topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv,
+                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config)
+
+
+def _sparse_attention_antiquant(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,
+                                attention_out, nq, n_kv, softmax_scale, topk, block_size, max_blocknum_perbatch,
+                                tile_config=None):
+    qn, qr, ti, bt, act, out, t, b = _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs,
+                                                 attention_out, nq, n_kv, topk)
+    cache = unwrap(nope_cache, "nope_cache")
+    _need(cache.dtype == torch.int8 and cache.dim() == 2 and cache.shape[1] == 656,
+          "nope_cache: int8 [rows, 656] = 512 int8 | 64 bf16 | 4 fp32")
+    dev = _same_device([qn, qr, cache, ti, bt, act, out])
+    lib = _lib.load()
+    nbytes = lib.pto_sfa_workspace_bytes(t, int(nq))
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_sfa_packed(qn.data_ptr(), qr.data_ptr(), cache.data_ptr(), ti.data_ptr(), bt.data_ptr(),
+                                      act.data_ptr(), out.data_ptr(), b, t // b, int(nq), int(n_kv),
+                                      float(softmax_scale), int(topk), int(block_size), cache.shape[0], bt.shape[1],
+                                      int(nq), 0, ws.data_ptr(), ws.numel(),
+                                      torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def sparse_attention_antiquant_d(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,
+                                 attention_out, nq, n_kv, softmax_scale, topk, block_size, max_blocknum_perbatch,
+                                 tile_config=None):
+    """Decode entry over the packed 656-byte cache rows."""
+    return _sparse_attention_antiquant(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,
+                                       attention_out, nq, n_kv, softmax_scale, topk, block_size,
+                                       max_blocknum_perbatch, tile_config)
+
+
+def sparse_attention_antiquant_p(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,
+                                 attention_out, nq, n_kv, softmax_scale, topk, block_size, max_blocknum_perbatch,
+                                 tile_config=None):
+    """Prefill entry over the packed 656-byte cache rows."""
+    return _sparse_attention_antiquant(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,
+                                       attention_out, nq, n_kv, softmax_scale, topk, block_size,
+                                       max_blocknum_perbatch, tile_config)
+
+
+def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, query_nope,
+                                   query_rope, key_nope_2d, key_rope_2d, k_nope_scales, act_seq, block_table,
+                                   topk_res, attention_out, nq=128, softmax_scale=576 ** -0.5, selected_count=2048, *,
+                                   sort=False):
+    """Fused chain: indexer score -> top-k -> sparse attention with the kernel's own indices.
+    Both caches share `block_table` / `act_seq`. Writes `topk_res` and `attention_out`."""
+    dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
+                                                    idx_weight, act_seq, block_table)
+    out_idx = unwrap(topk_res, "topk_res")
+    qn, qr, ti, bt2, act2, out, t, b = _sfa_common(query_nope, query_rope, out_idx, bt, act, attention_out, nq, 1,
+                                                   selected_count)
+    kn = unwrap(key_nope_2d, "key_nope_2d")
+    kr = unwrap(key_rope_2d, "key_rope_2d")
+    sc = unwrap(k_nope_scales, "k_nope_scales")
+    _same_device([q, qn, qr, kn, kr, sc, out_idx, out])
+    _need(t == m["t"], "indexer and attention query token counts differ")
+    _need(m["block_size"] == 128, "block_size must be 128")
+    n_rows = m["block_num"] * 128
+    _need(kn.dtype == torch.int8 and tuple(kn.shape) == (n_rows, 512), "key_nope_2d: int8 [block_num*128, 512]")
+    _need(kr.dtype == torch.bfloat16 and tuple(kr.shape) == (n_rows, 64), "key_rope_2d: bfloat16 [block_num*128, 64]")
+    _need(sc.dtype == torch.float32 and tuple(sc.shape) == (n_rows, 4), "k_nope_scales: float32 [block_num*128, 4]")
+    lib = _lib.load()
+    nbytes = lib.pto_decode_workspace_bytes(t, m["max_blocks"], 128, int(nq))
+    flags = 0 if sort else _lib.PTO_LI_UNSORTED
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_decode_fused(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
+                                        m["scale_dtype"], qn.data_ptr(), qr.data_ptr(), kn.data_ptr(), kr.data_ptr(),
+                                        sc.data_ptr(), act.data_ptr(), bt.data_ptr(), out_idx.data_ptr(),
+                                        out.data_ptr(), b, m["s1"], m["block_num"], m["max_blocks"],
+                                        int(selected_count), int(nq), float(softmax_scale), flags, ws.data_ptr(),
+                                        ws.numel(), torch.cuda.current_stream(dev).cuda_stream))
+    return None
