@@ -160,6 +160,45 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_stage(args, dev):
+    """Profiling aid: one stage alone on a uniform synthetic case, timed with CUDA events."""
+    import pypto_b200 as pto
+
+    d = gen.make_inputs([args.ctx] * args.batch, s1=args.s1, seed=4321, device=dev,
+                        scale_dtype=getattr(torch, args.scale_dtype), with_topk=True)
+    t = d.t
+    idx = torch.zeros((t, 1, 2048), dtype=torch.int32, device=dev)
+    out = torch.zeros((d.b, d.s1, 128, 512), dtype=torch.bfloat16, device=dev)
+    sc = torch.randn((t, d.max_blocks * 128), dtype=torch.float32, device=dev)
+    li = (d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale, d.idx_weight, d.act_seq_key, d.block_table)
+    fns = {
+        "li_score": lambda: pto.lightning_indexer_scores(*li, sc),
+        "li_decode": lambda: pto.lightning_indexer_decode(*li, idx, None, None, 2048),
+        "topk": lambda: pto.lightning_indexer_topk(sc, d.act_seq_key, idx, s1=d.s1),
+        "sfa": lambda: pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d,
+                                                          d.k_nope_scales, d.topk_indices, d.block_table,
+                                                          d.act_seq_key, out, 128, 1, SCALE, 2048, 128, d.max_blocks),
+        "fused": lambda: pto.decode_indexer_attention_quant(*li[:5], d.query_nope, d.query_rope, d.key_nope_2d,
+                                                            d.key_rope_2d, d.k_nope_scales, d.act_seq_key,
+                                                            d.block_table, idx, out),
+    }
+    fn = fns[args.stage]
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / max(args.steps, 1)
+    by = gen.algorithmic_bytes(d)
+    print(json.dumps({"stage": args.stage, "batch": args.batch, "ctx": args.ctx, "s1": args.s1, "ms": ms,
+                      "score_stage_bytes": gen.score_stage_bytes(d), "algorithmic_bytes": by,
+                      "status": pto.workspace_status(dev)[0]}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,7 +206,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2)
-    ap.add_argument("--cpu-seqs", type=int, default=8, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "fused"],
+                    help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--ctx", type=int, default=65536)
+    ap.add_argument("--s1", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-dtype", default="float32", choices=["float32", "float16"])
     args = ap.parse_args()
@@ -191,6 +235,10 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.stage is not None:
+        run_stage(args, dev)
+        return
 
     # every rank owns a full batch of the configuration (weak scaling, batch-partitioned)
     c = gen.config_act_seq(args.config)
@@ -313,10 +361,14 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             n_seq = args.cpu_seqs
             dcpu = cpu_sample(n_seq)
-            dt = time_cpu(dcpu)
-            line["cpu_baseline"] = {"value": n_seq / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
-                                    "sample": f"oracle chain on the first {n_seq} sequences of config 2, one pass, "
-                                              f"{dt:.2f} s"}
+            passes, spent = 0, 0.0
+            while spent < 10.0 and passes < 50:
+                spent += time_cpu(dcpu)
+                passes += 1
+            line["cpu_baseline"] = {"value": n_seq * passes / spent, "unit": UNIT, "cores": os.cpu_count() or 1,
+                                    "kind": "port",
+                                    "sample": f"oracle chain (torch CPU) on the first {n_seq} sequences of config 2, "
+                                              f"{passes} passes, {spent:.1f} s"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
