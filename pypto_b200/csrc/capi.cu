@@ -140,7 +140,7 @@ int check_li_common(const void* q, const void* qs, const void* kc, const void* k
   PTO_REQUIRE(block_num >= 1 && max_blocks >= 1, "block_num %d / max_blocks %d", block_num, max_blocks);
   PTO_REQUIRE(static_cast<long long>(max_blocks) * block_size <= (1ll << 24), "context of %lld keys is too long",
               static_cast<long long>(max_blocks) * block_size);
-  PTO_REQUIRE(aligned16(q) && aligned16(kc), "idx_query / idx_key_cache must be 16-byte aligned");
+  PTO_REQUIRE(aligned16(q) && aligned16(kc) && aligned16(ks), "idx_query / idx_key_cache / idx_key_scale must be 16-byte aligned");
   return PTO_OK;
 }
 

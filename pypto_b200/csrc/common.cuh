@@ -86,6 +86,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
       ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -242,5 +248,6 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
 cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
+cudaError_t launch_sfa_tc(const SfaParams& p, cudaStream_t stream);  // nq == 128 only
 
 }  // namespace pto

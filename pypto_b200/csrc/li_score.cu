@@ -22,9 +22,10 @@ namespace pto {
 
 namespace {
 
-constexpr int kLiStages = 6;
+constexpr int kLiStages = 8;
 constexpr int kPageKeys = 128;
 constexpr int kPageBytes = kPageKeys * 128;
+constexpr int kStageBytes = kPageBytes + 1024;  // key page + the page's 128 key scales (<= 512 B), 1024-aligned
 constexpr int kHeads = 64;
 constexpr int kQBytesPerToken = kHeads * 128;
 constexpr int kLiThreads = 320;
@@ -44,7 +45,7 @@ struct LiCtl {
   __align__(16) float ws[kMaxS1 * kHeads];
 };
 
-constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiStages * kPageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
+constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiStages * kStageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
 
 __device__ __forceinline__ float load_scale(const void* base, int dtype, int64_t i) {
   if (dtype == PTO_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
@@ -92,8 +93,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t stage_base = base;
-  const uint32_t q_base = base + kLiStages * kPageBytes;
-  LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiStages * kPageBytes + kMaxS1 * kQBytesPerToken);
+  const uint32_t q_base = base + kLiStages * kStageBytes;
+  LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiStages * kStageBytes + kMaxS1 * kQBytesPerToken);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -105,7 +106,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   if (tid == 0) {
     for (int i = 0; i < kLiStages; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
-      mbar_init(smem_u32(&ctl->empty[i]), 1);
+      mbar_init(smem_u32(&ctl->empty[i]), 1 + 4);  // MMA commit + the four epilogue warps that read the scales
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(smem_u32(&ctl->accfull[i]), 1);
@@ -153,6 +154,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int it1 = static_cast<int>(static_cast<long long>(total) * (blockIdx.x + 1) / gridDim.x);
 
   const uint32_t idesc = umma_idesc(kCFmtS32, kABFmtS8, kABFmtS8, 0, 0, 128, n_cols);
+  const uint32_t scale_bytes = kPageKeys * (p.scale_dtype == PTO_DT_F16 ? 2u : 4u);
 
   int cur = it0;
   int bi = 0;
@@ -208,13 +210,19 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 ctl->abort = 1;
                 set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 1);
               } else {
+                int scale_page = phys;
                 if (phys < 0 || phys >= p.block_num) {
                   set_status(p.status, PTO_ST_BAD_PAGE, phys, 1);
                   phys = p.block_num;  // out of range of the tensor map: the page reads as zeros
+                  scale_page = 0;      // any valid scales: the dots are zero
                 }
                 const uint32_t bar = smem_u32(&ctl->full[stage]);
-                mbar_arrive_expect_tx(bar, kPageBytes);
-                tma_load_2d(stage_base + stage * kPageBytes, &tmap_k, 0, phys * kPageKeys, bar);
+                const uint32_t dst = stage_base + stage * kStageBytes;
+                mbar_arrive_expect_tx(bar, kPageBytes + scale_bytes);
+                tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
+                bulk_load_1d(dst + kPageBytes,
+                             reinterpret_cast<const uint8_t*>(p.k_scale) + static_cast<int64_t>(scale_page) * scale_bytes,
+                             scale_bytes, bar);
               }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -246,7 +254,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
               set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 3);
             } else {
               tc_fence_after();
-              const uint64_t a_desc = umma_desc_kmajor_sw128(stage_base + stage * kPageBytes);
+              const uint64_t a_desc = umma_desc_kmajor_sw128(stage_base + stage * kStageBytes);
               const uint32_t d = tmem_base + acc * n_cols;
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
@@ -263,21 +271,27 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         const int grp = (warp - 2) >> 2;
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         const int row = quarter * 32 + lane;
-        const int32_t* bt = p.block_table + static_cast<int64_t>(bi) * p.max_blocks + page0;
         for (int j = 0; j < npages; ++j) {
           const uint32_t n = n_item + j;
           if (static_cast<int>(n & 1u) != grp) continue;
           const uint32_t acc = n % n_acc;
           const uint32_t aph = (n / n_acc) & 1u;
-          const int phys = bt[j];
-          const bool page_ok = phys >= 0 && phys < p.block_num;
-          const float ks = page_ok ? load_scale(p.k_scale, p.scale_dtype, static_cast<int64_t>(phys) * kPageKeys + row) : 0.f;
+          const uint32_t stage = n % kLiStages;
+          const uint32_t ph = (n / kLiStages) & 1u;
           if (!mbar_wait(smem_u32(&ctl->accfull[acc]), aph)) {
             ctl->abort = 1;
             set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 4);
             break;
           }
           tc_fence_after();
+          // the page's scales came in with the page; its `full` phase has completed (the MMA waited
+          // on it), observing it here orders this thread after the bulk copy
+          mbar_wait(smem_u32(&ctl->full[stage]), ph);
+          const uint8_t* sc_smem = smem + stage * kStageBytes + kPageBytes;
+          const float ks = (p.scale_dtype == PTO_DT_F16) ? __half2float(reinterpret_cast<const __half*>(sc_smem)[row])
+                                                         : reinterpret_cast<const float*>(sc_smem)[row];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[stage]));
           const int pos = (page0 + j) * kPageKeys + row;
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * n_cols;
           for (int i = 0; i < s1; ++i) {

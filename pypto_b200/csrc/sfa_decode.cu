@@ -449,8 +449,13 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   const int t = p.b * p.s1;
   const int n_hb = (p.nq + kHB - 1) / kHB;
-  sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);
-  e = cudaGetLastError();
+  if (p.nq == 128) {
+    // all 128 heads of a token: tcgen05 kernel (M = 128); narrower head slices use mma.sync below
+    e = launch_sfa_tc(p, stream);
+  } else {
+    sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) return e;
   if (p.n_split > 1) {
     sfa_combine_kernel<<<t * p.nq, 128, 0, stream>>>(p);

@@ -1,0 +1,487 @@
+// Sparse MLA attention for 128 heads on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Same arithmetic as sfa_decode.cu (reference:
+// examples/models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:45-207; golden
+// deepseekv32_sparse_flash_attention_quant.py:169-254): per query token the first n selected rows
+// are gathered from the paged cache, kn = bf16(int8 * scale), s = q.[kn|rope]^T * scale,
+// online softmax with P rounded once to bf16, O = P.kn accumulated in fp32.
+//
+// One CTA per (token, half of the 512 value dims, split of the selected rows). TMEM cannot hold a
+// 128 x 512 fp32 output next to the scores, so the output is split in two 256-wide halves; each CTA
+// computes the full 128 x 32 score tile (M = 128 heads) and its half of P.V.
+//   warp 0       : issues tcgen05.mma (q.K^T: 36 x (128x32x16), P.V: 2 x (128x256x16)), owns TMEM
+//   warps 1..4   : softmax, one thread per head row (TMEM lane): S from TMEM, P to shared (bf16),
+//                  lazy rescale of the O accumulator in TMEM, final normalisation and store
+//   warps 5..12  : producers: 16-byte loads of the selected rows, int8 -> bf16 dequantisation in
+//                  registers, swizzled stores into the K tile (double buffered)
+// Shared memory: Q 128 x 576 bf16 as nine 64-wide K-major chunks (128-byte swizzle); two K tiles of
+// 32 rows in the same chunked layout, which serves both as the K-major B operand of q.K^T and as
+// the MN-major B operand (V) of P.V; P 128 x 32 bf16 (64-byte swizzle). All waits are bounded.
+#include "common.cuh"
+
+namespace pto {
+
+namespace {
+
+constexpr int kT = 32;
+constexpr int kChunks = 9;
+constexpr int kQChunkBytes = 128 * 128;
+constexpr int kKChunkBytes = kT * 128;
+constexpr int kKBufBytes = kChunks * kKChunkBytes;
+constexpr int kPBytes = 128 * 64;
+constexpr int kProducerWarp0 = 5;
+constexpr int kProducerWarps = 8;
+constexpr int kTcThreads = 32 * (kProducerWarp0 + kProducerWarps);  // 416
+constexpr uint32_t kTmemColsTc = 512;
+constexpr uint32_t kColO = 0;
+constexpr uint32_t kColS = 256;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8 between rescales
+
+struct TcCtl {
+  uint64_t k_full[2];
+  uint64_t s_full[2];
+  uint64_t pv_done[2];
+  uint64_t p_full;
+  uint32_t tmem_base;
+  int abort;
+  __align__(16) unsigned char k_valid[2][kT];
+};
+
+constexpr size_t kTcSmemBytes = 1024 + kChunks * kQChunkBytes + 2 * kKBufBytes + kPBytes + sizeof(TcCtl);
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint64_t desc_kmajor_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;  // 8 rows * 64 B
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;  // SWIZZLE_64B
+  return d;
+}
+
+// MN-major operand, 128-byte swizzle: 64 elements (128 B) contiguous along MN, 8 K-rows per 1024-byte
+// atom; `lbo` = bytes between 64-element groups along MN, `sbo` = bytes between 8-row groups along K
+__device__ __forceinline__ uint64_t desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// 16 int8 -> 16 bf16 of (value * scale): byte b^0x80 placed in the mantissa of 2^23 gives
+// 2^23 + 128 + x exactly; subtracting 8388736 leaves x; one fp32 multiply and one rounding to bf16,
+// i.e. bf16(fp32(x) * scale) as the golden computes it.
+__device__ __forceinline__ void dequant16(const uint4 v, const float scale, uint4& o0, uint4& o1) {
+  const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+  uint32_t o[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float f0 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7540)) - 8388736.0f) * scale;
+    const float f1 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7541)) - 8388736.0f) * scale;
+    const float f2 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7542)) - 8388736.0f) * scale;
+    const float f3 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7543)) - 8388736.0f) * scale;
+    o[2 * e] = pack_bf16x2(f0, f1);
+    o[2 * e + 1] = pack_bf16x2(f2, f3);
+  }
+  o0 = make_uint4(o[0], o[1], o[2], o[3]);
+  o1 = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__device__ __forceinline__ long long tc_physical_row(const SfaParams& p, int bi, int idx) {
+  if (idx < 0) return -1;
+  const int blk = idx / p.block_size;
+  if (blk >= p.max_blocks) {
+    set_status(p.status, PTO_ST_BAD_PAGE, idx, 20);
+    return -1;
+  }
+  const int phys = p.block_table[static_cast<int64_t>(bi) * p.max_blocks + blk];
+  const long long r = static_cast<long long>(phys) * p.block_size + idx % p.block_size;
+  if (phys < 0 || r >= p.n_rows) {
+    set_status(p.status, PTO_ST_BAD_PAGE, phys, 21);
+    return -1;
+  }
+  return r;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+sfa_tc_kernel(SfaParams p) {
+  extern __shared__ uint8_t sfa_tc_smem_raw[];
+  const uint32_t raw = smem_u32(sfa_tc_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = sfa_tc_smem_raw + (base - raw);
+  const uint32_t q_base = base;
+  const uint32_t k_base = base + kChunks * kQChunkBytes;
+  const uint32_t p_base = k_base + 2 * kKBufBytes;
+  uint8_t* q_ptr = smem;
+  uint8_t* k_ptr = smem + kChunks * kQChunkBytes;
+  uint8_t* p_ptr = k_ptr + 2 * kKBufBytes;
+  TcCtl* ctl = reinterpret_cast<TcCtl*>(p_ptr + kPBytes);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  int bid = blockIdx.x;
+  const int sp = bid % p.n_split;
+  bid /= p.n_split;
+  const int dvh = bid & 1;
+  const int ti = bid >> 1;
+  const int bi = ti / p.s1;
+  const int si = ti % p.s1;
+
+  int n = p.act_seq[bi] - p.s1 + 1 + si;
+  n = max(0, min(n, p.topk_k));
+  const int tiles_total = (n + kT - 1) / kT;
+  const int tiles_per_split = (tiles_total + p.n_split - 1) / p.n_split;
+  const int begin = min(n, sp * tiles_per_split * kT);
+  const int end = min(n, (sp + 1) * tiles_per_split * kT);
+  const int ntiles = (end - begin + kT - 1) / kT;
+  const int32_t* idx_row = p.topk + static_cast<int64_t>(ti) * p.topk_k;
+  const int64_t q_row0 = static_cast<int64_t>(ti) * p.nq_total + p.head_begin;
+
+  if (ntiles == 0) {
+    if (p.n_split == 1) {
+      for (int e = tid; e < 128 * 32; e += kTcThreads) {  // 128 rows x 32 uint4 (256 bf16)
+        const int row = e >> 5, c = e & 31;
+        *reinterpret_cast<uint4*>(p.out + (q_row0 + row) * 512 + dvh * 256 + c * 8) = make_uint4(0, 0, 0, 0);
+      }
+    } else if (dvh == 0) {
+      for (int row = tid; row < 128; row += kTcThreads) {
+        float* ml = p.part_ml + ((static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + row) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+    }
+    return;
+  }
+
+  // ---- setup ------------------------------------------------------------------------------------
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctl->k_full[i]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->s_full[i]), 1);
+      mbar_init(smem_u32(&ctl->pv_done[i]), 1);
+    }
+    mbar_init(smem_u32(&ctl->p_full), 4);
+    ctl->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemColsTc);
+    tmem_relinquish();
+  }
+  // Q: 128 heads x 576, chunk c = dims [64c, 64c+64), row h at h*128 B, 16-byte unit u at (u ^ (h & 7))
+  for (int e = tid; e < 128 * 72; e += kTcThreads) {
+    const int h = e / 72, uu = e % 72;
+    const int c = uu >> 3, u = uu & 7;
+    const uint4 v = (c < 8) ? *reinterpret_cast<const uint4*>(p.q_nope + (q_row0 + h) * 512 + c * 64 + u * 8)
+                            : *reinterpret_cast<const uint4*>(p.q_rope + (q_row0 + h) * 64 + u * 8);
+    *reinterpret_cast<uint4*>(q_ptr + c * kQChunkBytes + h * 128 + ((u ^ (h & 7)) << 4)) = v;
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ================================ MMA issuer ================================================
+    const uint32_t idesc_qk = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 0, 128, kT);
+    const uint32_t idesc_pv = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 1, 128, 256);
+    bool ok = true;
+    auto issue_qk = [&](int j) {
+      const int b = j & 1;
+      const uint32_t d = tmem_base + kColS + kT * b;
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c) {
+        const uint64_t a_desc = umma_desc_kmajor_sw128(q_base + c * kQChunkBytes);
+        const uint64_t b_desc = umma_desc_kmajor_sw128(k_base + b * kKBufBytes + c * kKChunkBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (c | k) != 0 ? 1u : 0u);
+      }
+      tc_commit(smem_u32(&ctl->s_full[b]));
+    };
+    auto issue_pv = [&](int j) {
+      const int b = j & 1;
+      const uint64_t a_desc = desc_kmajor_sw64(p_base);
+      const uint64_t b_desc = desc_mnmajor_sw128(k_base + b * kKBufBytes + dvh * 4 * kKChunkBytes, kKChunkBytes, 1024);
+#pragma unroll
+      for (int k = 0; k < kT / 16; ++k) {
+        mma_f16_ss(tmem_base + kColO, a_desc + 2 * k, b_desc + k * ((16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+      }
+      tc_commit(smem_u32(&ctl->pv_done[b]));
+    };
+    if (lane == 0) {
+      if (!mbar_wait(smem_u32(&ctl->k_full[0]), 0)) {
+        ok = false;
+      } else {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) {
+          if (!mbar_wait(smem_u32(&ctl->k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
+        if (!mbar_wait(smem_u32(&ctl->p_full), j & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        issue_pv(j);
+      }
+      if (!ok) {
+        ctl->abort = 1;
+        set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 30);
+      }
+    }
+    __syncwarp();
+  } else if (warp < kProducerWarp0) {
+    // ================================ softmax ===================================================
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(smem_u32(&ctl->s_full[b]), (j >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(lane_addr + kColS + kT * b, v);
+      tc_wait_ld();
+      mbar_wait(smem_u32(&ctl->k_full[b]), (j >> 1) & 1);  // already complete: orders the k_valid reads
+      const uint4 va = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][0]);
+      const uint4 vb = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][16]);
+      const uint32_t vw[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      float s[32];
+      float mt = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const bool valid = ((vw[c >> 2] >> ((c & 3) * 8)) & 0xffu) != 0;
+        s[c] = valid ? __uint_as_float(v[c]) * p.scale_log2 : -INFINITY;
+        mt = fmaxf(mt, s[c]);
+      }
+      const float m_new = fmaxf(m_used, mt);
+      const bool need = (m_new > m_used + kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
+      if (j > 0) {
+        ok = mbar_wait(smem_u32(&ctl->pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1);  // P buffer free, O at rest
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      float alpha = 1.f;
+      if (need) {
+        alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
+        l *= alpha;
+        m_used = m_new;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kColO + ch * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          tmem_st_32x32b_x32(lane_addr + kColO + ch * 32, o);
+        }
+        tc_wait_st();
+      }
+      const float mref = (m_used == -INFINITY) ? 0.f : m_used;
+      float lsum = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        const float p0 = ex2f(s[c] - mref), p1 = ex2f(s[c + 1] - mref);
+        lsum += p0 + p1;
+        pk[c >> 1] = pack_bf16x2(p0, p1);
+      }
+      l += lsum;
+      uint8_t* prow = p_ptr + row * 64;
+      const int sw = (row >> 1) & 3;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        *reinterpret_cast<uint4*>(prow + ((u ^ sw) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
+    }
+    if (ok) {
+      ok = mbar_wait(smem_u32(&ctl->pv_done[(ntiles - 1) & 1]), ((ntiles - 1) >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      if (p.n_split == 1) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = p.out + (q_row0 + row) * 512 + dvh * 256;
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kColO + ch * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = w;
+          }
+        }
+      } else {
+        const int64_t prow = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + row;
+        float* dst = p.part_o + prow * 512 + dvh * 256;
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kColO + ch * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+          }
+        }
+        if (dvh == 0) {
+          p.part_ml[prow * 2] = m_used;
+          p.part_ml[prow * 2 + 1] = l;
+        }
+      }
+    } else if (lane == 0) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 31);
+    }
+  } else {
+    // ================================ producers =================================================
+    const int ptid = tid - kProducerWarp0 * 32;
+    const int row = ptid >> 3;  // row of the tile
+    const int q = ptid & 7;     // 16-byte lane within the row
+    auto load_idx = [&](int j) -> int {
+      const int e = begin + j * kT + row;
+      return (j < ntiles && e < end) ? idx_row[e] : -1;
+    };
+    const uint8_t* kn_bytes = reinterpret_cast<const uint8_t*>(p.kn);
+    const uint8_t* kr_bytes = reinterpret_cast<const uint8_t*>(p.kr);
+    const uint8_t* sc_bytes = reinterpret_cast<const uint8_t*>(p.kn_scales);
+    long long phys_cur = tc_physical_row(p, bi, load_idx(0));
+    long long phys_next = tc_physical_row(p, bi, load_idx(1));
+    int idx_n2 = load_idx(2);
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      const int b = j & 1;
+      // ---- loads of tile j (registers) -------------------------------------------------------
+      uint4 d8[4], dr;
+      float4 sc;
+      const bool valid = phys_cur >= 0;
+      if (valid) {
+        if (p.packed) {
+          const uint8_t* src = kn_bytes + phys_cur * 656;
+#pragma unroll
+          for (int m = 0; m < 4; ++m) d8[m] = __ldg(reinterpret_cast<const uint4*>(src + (q + 8 * m) * 16));
+          dr = __ldg(reinterpret_cast<const uint4*>(src + 512 + q * 16));
+          sc = __ldg(reinterpret_cast<const float4*>(src + 640));
+        } else {
+#pragma unroll
+          for (int m = 0; m < 4; ++m) d8[m] = __ldg(reinterpret_cast<const uint4*>(kn_bytes + phys_cur * 512 + (q + 8 * m) * 16));
+          dr = __ldg(reinterpret_cast<const uint4*>(kr_bytes + phys_cur * 128 + q * 16));
+          sc = __ldg(reinterpret_cast<const float4*>(sc_bytes + phys_cur * 16));
+        }
+      }
+      // ---- index / page-table prefetch for the next tiles -------------------------------------
+      const long long phys_n2 = tc_physical_row(p, bi, idx_n2);
+      const int idx_n3 = load_idx(j + 3);
+      // ---- buffer free? ----------------------------------------------------------------------
+      if (j >= 2) {
+        ok = mbar_wait(smem_u32(&ctl->pv_done[b]), ((j - 2) >> 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      uint8_t* kbuf = k_ptr + b * kKBufBytes + row * 128;
+      const int sw = row & 7;
+      if (valid) {
+        const float scl[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          uint4 o0, o1;
+          dequant16(d8[m], scl[m], o0, o1);
+          const int c = 2 * m + (q >> 2);   // 64-dim chunk of int8 unit ci = q + 8m
+          const int u = 2 * (q & 3);        // first 16-byte bf16 unit inside the chunk
+          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + ((u ^ sw) << 4)) = o0;
+          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + (((u + 1) ^ sw) << 4)) = o1;
+        }
+        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + ((q ^ sw) << 4)) = dr;
+      } else {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const int c = 2 * m + (q >> 2);
+          const int u = 2 * (q & 3);
+          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + ((u ^ sw) << 4)) = z;
+          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + (((u + 1) ^ sw) << 4)) = z;
+        }
+        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + ((q ^ sw) << 4)) = z;
+      }
+      if (q == 0) ctl->k_valid[b][row] = valid ? 1 : 0;
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->k_full[b]));
+      phys_cur = phys_next;
+      phys_next = phys_n2;
+      idx_n2 = idx_n3;
+    }
+    if (!ok && lane == 0) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 32);
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemColsTc);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_sfa_tc(const SfaParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(sfa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kTcSmemBytes));
+  if (e != cudaSuccess) return e;
+  const int t = p.b * p.s1;
+  sfa_tc_kernel<<<t * 2 * p.n_split, kTcThreads, kTcSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace pto
