@@ -211,6 +211,7 @@ struct LiParams {
   void* first_mm;           // optional f16 [t*64, row_stride] (SIMT path)
   int64_t row_stride;
   int b, s1, block_num, max_blocks;
+  int debug;       // experiment switches (PTO_DEBUG environment variable), 0 in production
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
   int32_t* status;
@@ -238,6 +239,7 @@ struct SfaParams {
   float* part_o;                // [t, n_split, nq, 512]
   float* part_ml;               // [t, n_split, nq, 2]
   int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed;
+  int debug;  // experiment switches (PTO_DEBUG environment variable), 0 in production
   int64_t n_rows;
   float scale_log2;  // softmax_scale * log2(e)
   int32_t* status;

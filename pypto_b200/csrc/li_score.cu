@@ -12,8 +12,9 @@
 // 128-byte swizzle) -> four tcgen05.mma kind::i8 (M = 128 keys, N = 64*s1 heads, K = 32) into a
 // TMEM accumulator -> epilogue warps read their key's row (one TMEM lane = one key), apply
 // ReLU/2^-11/fp16 rounding and the weighted head sum, and write the fp32 score.
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2..9 epilogue (two groups
-// of four warps that take alternate pages). All waits are bounded.
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2..17 epilogue (four groups
+// of four warps that take pages round-robin; a single warp is latency-bound on the conversion chain,
+// so thread-level parallelism has to come from many warps). All waits are bounded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -22,22 +23,24 @@ namespace pto {
 
 namespace {
 
-constexpr int kLiStages = 8;
+constexpr int kLiSlots = 8;            // ring of (smem stage, TMEM accumulator) pairs
 constexpr int kPageKeys = 128;
 constexpr int kPageBytes = kPageKeys * 128;
 constexpr int kStageBytes = kPageBytes + 1024;  // key page + the page's 128 key scales (<= 512 B), 1024-aligned
 constexpr int kHeads = 64;
 constexpr int kQBytesPerToken = kHeads * 128;
-constexpr int kLiThreads = 320;
+constexpr int kLiMmaWarps = 2;         // warps 1..2: issuer for pages n with n % 2 == warp - 1
+constexpr int kLiEpilogueGroups = 4;   // groups of four warps; group g takes pages n with n % 4 == g
+constexpr int kLiEpilogueWarp0 = 1 + kLiMmaWarps;
+constexpr int kLiThreads = 32 * (kLiEpilogueWarp0 + 4 * kLiEpilogueGroups);
 constexpr int kMaxS1 = 4;
 constexpr int kMaxSeqPerLaunch = 2048;
 constexpr int kTmemCols = 512;
 
 struct LiCtl {
-  uint64_t full[kLiStages];
-  uint64_t empty[kLiStages];
-  uint64_t accfull[8];
-  uint64_t accempty[8];
+  uint64_t full[kLiSlots];     // TMA bytes of the slot's page landed
+  uint64_t accfull[kLiSlots];  // the slot's MMAs completed (tcgen05.commit)
+  uint64_t empty[kLiSlots];    // the slot's epilogue warps finished reading TMEM and the scales
   uint64_t qfull;
   uint32_t tmem_base;
   int abort;
@@ -45,7 +48,7 @@ struct LiCtl {
   __align__(16) float ws[kMaxS1 * kHeads];
 };
 
-constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiStages * kStageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
+constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
 
 __device__ __forceinline__ float load_scale(const void* base, int dtype, int64_t i) {
   if (dtype == PTO_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
@@ -93,24 +96,21 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t stage_base = base;
-  const uint32_t q_base = base + kLiStages * kStageBytes;
-  LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiStages * kStageBytes + kMaxS1 * kQBytesPerToken);
+  const uint32_t q_base = base + kLiSlots * kStageBytes;
+  LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int s1 = p.s1;
-  const int n_cols = kHeads * s1;                      // accumulator columns per page
-  const int n_acc = min(8, kTmemCols / n_cols);        // accumulator buffers
+  const int n_cols = kHeads * s1;                                // accumulator columns per page
+  const uint32_t n_slots = min(kLiSlots, kTmemCols / n_cols);   // 8, 4, 2, 2 for s1 = 1..4
 
   if (tid == 0) {
-    for (int i = 0; i < kLiStages; ++i) {
+    for (int i = 0; i < kLiSlots; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
-      mbar_init(smem_u32(&ctl->empty[i]), 1 + 4);  // MMA commit + the four epilogue warps that read the scales
-    }
-    for (int i = 0; i < 8; ++i) {
       mbar_init(smem_u32(&ctl->accfull[i]), 1);
-      mbar_init(smem_u32(&ctl->accempty[i]), 4);
+      mbar_init(smem_u32(&ctl->empty[i]), 4);
     }
     mbar_init(smem_u32(&ctl->qfull), 1);
     ctl->abort = 0;
@@ -123,7 +123,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 2) {
+  if (warp == kLiEpilogueWarp0) {
     // exclusive prefix of pages per sequence
     int carry = 0;
     for (int b0 = 0; b0 < p.b; b0 += 32) {
@@ -175,19 +175,17 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int page0 = cur - ctl->prefix[bi];
     const int npages = seg_end - cur;
     const int seq_len = p.act_seq[bi];
+    const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset;
 
     __syncthreads();  // previous segment fully drained: Q tile and ws may be overwritten
     const bool aborted = ctl->abort != 0;
     if (!aborted) {
       if (warp == 0 && lane == 0) {
         mbar_arrive_expect_tx(smem_u32(&ctl->qfull), s1 * kQBytesPerToken);
-        tma_load_2d(q_base, &tmap_q, 0, (bi * p.s1_total + p.tok_offset) * kHeads, smem_u32(&ctl->qfull));
+        tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
       }
-      if (tid >= 64 && tid - 64 < s1 * kHeads) {
-        const int e = tid - 64;
-        ctl->ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype,
-                             (static_cast<int64_t>(bi) * p.s1_total + p.tok_offset) * kHeads + e);
-      }
+      const int e = tid - 32 * kLiEpilogueWarp0;
+      if (e >= 0 && e < s1 * kHeads) ctl->ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
     }
     __syncthreads();
 
@@ -203,9 +201,9 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
             int phys = __shfl_sync(0xffffffffu, mine, jj);
             if (lane == 0) {
               const uint32_t n = n_item + j0 + jj;
-              const uint32_t stage = n % kLiStages;
-              const uint32_t ph = (n / kLiStages) & 1u;
-              if (!mbar_wait(smem_u32(&ctl->empty[stage]), ph ^ 1u)) {
+              const uint32_t slot = n % n_slots;
+              const uint32_t ph = (n / n_slots) & 1u;
+              if (!mbar_wait(smem_u32(&ctl->empty[slot]), ph ^ 1u)) {
                 ok = false;
                 ctl->abort = 1;
                 set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 1);
@@ -216,8 +214,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                   phys = p.block_num;  // out of range of the tensor map: the page reads as zeros
                   scale_page = 0;      // any valid scales: the dots are zero
                 }
-                const uint32_t bar = smem_u32(&ctl->full[stage]);
-                const uint32_t dst = stage_base + stage * kStageBytes;
+                const uint32_t bar = smem_u32(&ctl->full[slot]);
+                const uint32_t dst = stage_base + slot * kStageBytes;
                 mbar_arrive_expect_tx(bar, kPageBytes + scale_bytes);
                 tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
                 bulk_load_1d(dst + kPageBytes,
@@ -229,84 +227,80 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
             if (!ok) break;
           }
         }
-      } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        bool ok = true;
+      } else if (warp < kLiEpilogueWarp0) {
+        // ---------------- MMA issuers: warp w takes pages n with n % 2 == w - 1 ----------------
         if (lane == 0) {
-          if (!mbar_wait(smem_u32(&ctl->qfull), seg & 1u)) {
-            ok = false;
-            ctl->abort = 1;
-            set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(seg), 2);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        const uint64_t b_desc = umma_desc_kmajor_sw128(q_base);
-        for (int j = 0; j < npages && ok; ++j) {
-          if (lane == 0) {
+          bool ok = mbar_wait(smem_u32(&ctl->qfull), seg & 1u);
+          if (!ok) set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(seg), 2);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(q_base);
+          const uint64_t a_desc0 = umma_desc_kmajor_sw128(stage_base);
+          for (int j = 0; j < npages && ok; ++j) {
             const uint32_t n = n_item + j;
-            const uint32_t stage = n % kLiStages;
-            const uint32_t ph = (n / kLiStages) & 1u;
-            const uint32_t acc = n % n_acc;
-            const uint32_t aph = (n / n_acc) & 1u;
-            if (!mbar_wait(smem_u32(&ctl->full[stage]), ph) || !mbar_wait(smem_u32(&ctl->accempty[acc]), aph ^ 1u)) {
+            if (static_cast<int>(n % kLiMmaWarps) != warp - 1) continue;
+            const uint32_t slot = n % n_slots;
+            const uint32_t ph = (n / n_slots) & 1u;
+            if (!mbar_wait(smem_u32(&ctl->full[slot]), ph)) {
               ok = false;
-              ctl->abort = 1;
               set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 3);
-            } else {
-              tc_fence_after();
-              const uint64_t a_desc = umma_desc_kmajor_sw128(stage_base + stage * kStageBytes);
-              const uint32_t d = tmem_base + acc * n_cols;
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                mma_i8_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
-              }
-              tc_commit(smem_u32(&ctl->empty[stage]));
-              tc_commit(smem_u32(&ctl->accfull[acc]));
+              break;
             }
+            tc_fence_after();
+            const uint64_t a_desc = a_desc0 + ((slot * kStageBytes) >> 4);
+            const uint32_t d = tmem_base + slot * n_cols;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_i8_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+            tc_commit(smem_u32(&ctl->accfull[slot]));
           }
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) ctl->abort = 1;
         }
+        __syncwarp();
       } else {
         // ---------------- epilogue ----------------
-        const int grp = (warp - 2) >> 2;
+        const int grp = (warp - kLiEpilogueWarp0) >> 2;
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         const int row = quarter * 32 + lane;
         for (int j = 0; j < npages; ++j) {
           const uint32_t n = n_item + j;
-          if (static_cast<int>(n & 1u) != grp) continue;
-          const uint32_t acc = n % n_acc;
-          const uint32_t aph = (n / n_acc) & 1u;
-          const uint32_t stage = n % kLiStages;
-          const uint32_t ph = (n / kLiStages) & 1u;
-          if (!mbar_wait(smem_u32(&ctl->accfull[acc]), aph)) {
+          if (static_cast<int>(n % kLiEpilogueGroups) != grp) continue;
+          const uint32_t slot = n % n_slots;
+          const uint32_t ph = (n / n_slots) & 1u;
+          if (!mbar_wait(smem_u32(&ctl->accfull[slot]), ph)) {
             ctl->abort = 1;
             set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(n), 4);
             break;
           }
           tc_fence_after();
-          // the page's scales came in with the page; its `full` phase has completed (the MMA waited
-          // on it), observing it here orders this thread after the bulk copy
-          mbar_wait(smem_u32(&ctl->full[stage]), ph);
-          const uint8_t* sc_smem = smem + stage * kStageBytes + kPageBytes;
+          // the page's scales came in with the page; its `full` phase has completed (the MMA issuer
+          // waited on it); observing it here orders this thread after the bulk copy
+          mbar_wait(smem_u32(&ctl->full[slot]), ph);
+          const uint8_t* sc_smem = smem + slot * kStageBytes + kPageBytes;
           const float ks = (p.scale_dtype == PTO_DT_F16) ? __half2float(reinterpret_cast<const __half*>(sc_smem)[row])
                                                          : reinterpret_cast<const float*>(sc_smem)[row];
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[stage]));
           const int pos = (page0 + j) * kPageKeys + row;
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * n_cols;
-          for (int i = 0; i < s1; ++i) {
-            uint32_t v0[32], v1[32];
-            tmem_ld_32x32b_x32(taddr + i * kHeads, v0);
-            tmem_ld_32x32b_x32(taddr + i * kHeads + 32, v1);
-            tc_wait_ld();
-            const float s = weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32);
-            if (pos < seq_len) {
-              p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = s * ks;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * n_cols;
+          float res[kMaxS1];
+#pragma unroll
+          for (int i = 0; i < kMaxS1; ++i) {
+            if (i < s1) {
+              uint32_t v0[32], v1[32];
+              tmem_ld_32x32b_x32(taddr + i * kHeads, v0);
+              tmem_ld_32x32b_x32(taddr + i * kHeads + 32, v1);
+              tc_wait_ld();
+              if (i == s1 - 1) {
+                // TMEM and the scale row are read: hand the slot back before the arithmetic
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[slot]));
+              }
+              res[i] = (weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32)) * ks;
             }
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctl->accempty[acc]));
+          if (pos < seq_len) {
+#pragma unroll
+            for (int i = 0; i < kMaxS1; ++i) {
+              if (i < s1) p.scores[(tok0 + i) * p.row_stride + pos] = res[i];
+            }
+          }
         }
       }
     }

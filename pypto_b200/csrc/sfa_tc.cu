@@ -12,8 +12,8 @@
 //   warp 0       : issues tcgen05.mma (q.K^T: 36 x (128x32x16), P.V: 2 x (128x256x16)), owns TMEM
 //   warps 1..4   : softmax, one thread per head row (TMEM lane): S from TMEM, P to shared (bf16),
 //                  lazy rescale of the O accumulator in TMEM, final normalisation and store
-//   warps 5..12  : producers: 16-byte loads of the selected rows, int8 -> bf16 dequantisation in
-//                  registers, swizzled stores into the K tile (double buffered)
+//   warps 5..12  : producers in two groups (one per K buffer): 16-byte loads of the selected rows,
+//                  int8 -> bf16 dequantisation in registers, swizzled stores into the K tile
 // Shared memory: Q 128 x 576 bf16 as nine 64-wide K-major chunks (128-byte swizzle); two K tiles of
 // 32 rows in the same chunked layout, which serves both as the K-major B operand of q.K^T and as
 // the MN-major B operand (V) of P.V; P 128 x 32 bf16 (64-byte swizzle). All waits are bounded.
@@ -177,7 +177,7 @@ sfa_tc_kernel(SfaParams p) {
   // ---- setup ------------------------------------------------------------------------------------
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctl->k_full[i]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->k_full[i]), kProducerWarps / 2);  // one producer group per buffer
       mbar_init(smem_u32(&ctl->s_full[i]), 1);
       mbar_init(smem_u32(&ctl->pv_done[i]), 1);
     }
@@ -216,7 +216,10 @@ sfa_tc_kernel(SfaParams p) {
         const uint64_t a_desc = umma_desc_kmajor_sw128(q_base + c * kQChunkBytes);
         const uint64_t b_desc = umma_desc_kmajor_sw128(k_base + b * kKBufBytes + c * kKChunkBytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (c | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {
+          if ((p.debug & 64) && k > 0) break;
+          mma_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (c | k) != 0 ? 1u : 0u);
+        }
       }
       tc_commit(smem_u32(&ctl->s_full[b]));
     };
@@ -318,7 +321,7 @@ sfa_tc_kernel(SfaParams p) {
       uint32_t pk[16];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        const float p0 = ex2f(s[c] - mref), p1 = ex2f(s[c + 1] - mref);
+        const float p0 = (p.debug & 16) ? s[c] : ex2f(s[c] - mref), p1 = (p.debug & 16) ? s[c + 1] : ex2f(s[c + 1] - mref);
         lsum += p0 + p1;
         pk[c >> 1] = pack_bf16x2(p0, p1);
       }
@@ -382,81 +385,109 @@ sfa_tc_kernel(SfaParams p) {
     }
   } else {
     // ================================ producers =================================================
+    // Two groups of four warps; group g fills the tiles j with j % 2 == g (always K buffer g). Each
+    // thread owns a quarter of one row: ten 16-byte units (8 of int8 latent, 2 of bf16 rope) and the
+    // row's four scales. The loads of the group's next tile are issued into a second register set
+    // before the current tile is converted, so up to four tiles are in flight per CTA.
     const int ptid = tid - kProducerWarp0 * 32;
-    const int row = ptid >> 3;  // row of the tile
-    const int q = ptid & 7;     // 16-byte lane within the row
-    auto load_idx = [&](int j) -> int {
-      const int e = begin + j * kT + row;
-      return (j < ntiles && e < end) ? idx_row[e] : -1;
+    const int grp = ptid >> 7;
+    const int gt = ptid & 127;
+    const int row = gt >> 2;  // row of the tile
+    const int q = gt & 3;     // 16-byte lane: units q, q+4, ..., q+36 of the 41-unit row
+    const int n_mine = (ntiles - grp + 1) / 2;  // tiles grp, grp+2, ...
+    auto load_idx = [&](int i) -> int {  // i-th tile of this group
+      const int e = begin + (grp + 2 * i) * kT + row;
+      return (i < n_mine && e < end) ? idx_row[e] : -1;
     };
     const uint8_t* kn_bytes = reinterpret_cast<const uint8_t*>(p.kn);
     const uint8_t* kr_bytes = reinterpret_cast<const uint8_t*>(p.kr);
     const uint8_t* sc_bytes = reinterpret_cast<const uint8_t*>(p.kn_scales);
-    long long phys_cur = tc_physical_row(p, bi, load_idx(0));
-    long long phys_next = tc_physical_row(p, bi, load_idx(1));
-    int idx_n2 = load_idx(2);
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      const int b = j & 1;
-      // ---- loads of tile j (registers) -------------------------------------------------------
-      uint4 d8[4], dr;
+    struct RowRegs {
+      uint4 d[10];
       float4 sc;
-      const bool valid = phys_cur >= 0;
-      if (valid) {
-        if (p.packed) {
-          const uint8_t* src = kn_bytes + phys_cur * 656;
+      bool valid;
+    };
+    auto issue_loads = [&](RowRegs& r, long long phys) {
+      r.valid = phys >= 0;
+      if (!r.valid) return;
+      if (p.debug & 8) {  // experiment: no global loads
 #pragma unroll
-          for (int m = 0; m < 4; ++m) d8[m] = __ldg(reinterpret_cast<const uint4*>(src + (q + 8 * m) * 16));
-          dr = __ldg(reinterpret_cast<const uint4*>(src + 512 + q * 16));
-          sc = __ldg(reinterpret_cast<const float4*>(src + 640));
-        } else {
-#pragma unroll
-          for (int m = 0; m < 4; ++m) d8[m] = __ldg(reinterpret_cast<const uint4*>(kn_bytes + phys_cur * 512 + (q + 8 * m) * 16));
-          dr = __ldg(reinterpret_cast<const uint4*>(kr_bytes + phys_cur * 128 + q * 16));
-          sc = __ldg(reinterpret_cast<const float4*>(sc_bytes + phys_cur * 16));
-        }
+        for (int m = 0; m < 10; ++m) r.d[m] = make_uint4(0x01010101u * q, 2, 3, 4);
+        r.sc = make_float4(1.f, 1.f, 1.f, 1.f);
+        return;
       }
-      // ---- index / page-table prefetch for the next tiles -------------------------------------
-      const long long phys_n2 = tc_physical_row(p, bi, idx_n2);
-      const int idx_n3 = load_idx(j + 3);
-      // ---- buffer free? ----------------------------------------------------------------------
-      if (j >= 2) {
-        ok = mbar_wait(smem_u32(&ctl->pv_done[b]), ((j - 2) >> 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
-      uint8_t* kbuf = k_ptr + b * kKBufBytes + row * 128;
-      const int sw = row & 7;
-      if (valid) {
-        const float scl[4] = {sc.x, sc.y, sc.z, sc.w};
+      if (p.packed) {
+        const uint8_t* src = kn_bytes + phys * 656;
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
+        for (int m = 0; m < 10; ++m) r.d[m] = __ldg(reinterpret_cast<const uint4*>(src + (q + 4 * m) * 16));
+        r.sc = __ldg(reinterpret_cast<const float4*>(src + 640));
+      } else {
+#pragma unroll
+        for (int m = 0; m < 8; ++m) r.d[m] = __ldg(reinterpret_cast<const uint4*>(kn_bytes + phys * 512 + (q + 4 * m) * 16));
+        r.d[8] = __ldg(reinterpret_cast<const uint4*>(kr_bytes + phys * 128 + q * 16));
+        r.d[9] = __ldg(reinterpret_cast<const uint4*>(kr_bytes + phys * 128 + (q + 4) * 16));
+        r.sc = __ldg(reinterpret_cast<const float4*>(sc_bytes + phys * 16));
+      }
+    };
+    uint8_t* kbuf = k_ptr + grp * kKBufBytes + row * 128;
+    const int sw = row & 7;
+    auto convert_store = [&](const RowRegs& r) {
+      if (r.valid) {
+        const float scl[4] = {r.sc.x, r.sc.y, r.sc.z, r.sc.w};
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {  // int8 unit q + 4m: chunk m, bf16 units 2q and 2q+1, scale m / 2
           uint4 o0, o1;
-          dequant16(d8[m], scl[m], o0, o1);
-          const int c = 2 * m + (q >> 2);   // 64-dim chunk of int8 unit ci = q + 8m
-          const int u = 2 * (q & 3);        // first 16-byte bf16 unit inside the chunk
-          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + ((u ^ sw) << 4)) = o0;
-          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + (((u + 1) ^ sw) << 4)) = o1;
+          if (p.debug & 32) { o0 = r.d[m]; o1 = r.d[m]; } else
+          dequant16(r.d[m], scl[m >> 1], o0, o1);
+          *reinterpret_cast<uint4*>(kbuf + m * kKChunkBytes + (((2 * q) ^ sw) << 4)) = o0;
+          *reinterpret_cast<uint4*>(kbuf + m * kKChunkBytes + (((2 * q + 1) ^ sw) << 4)) = o1;
         }
-        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + ((q ^ sw) << 4)) = dr;
+        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + ((q ^ sw) << 4)) = r.d[8];
+        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + (((q + 4) ^ sw) << 4)) = r.d[9];
       } else {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          const int c = 2 * m + (q >> 2);
-          const int u = 2 * (q & 3);
-          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + ((u ^ sw) << 4)) = z;
-          *reinterpret_cast<uint4*>(kbuf + c * kKChunkBytes + (((u + 1) ^ sw) << 4)) = z;
+        for (int m = 0; m < 8; ++m) {
+          *reinterpret_cast<uint4*>(kbuf + m * kKChunkBytes + (((2 * q) ^ sw) << 4)) = z;
+          *reinterpret_cast<uint4*>(kbuf + m * kKChunkBytes + (((2 * q + 1) ^ sw) << 4)) = z;
         }
         *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + ((q ^ sw) << 4)) = z;
+        *reinterpret_cast<uint4*>(kbuf + 8 * kKChunkBytes + (((q + 4) ^ sw) << 4)) = z;
       }
-      if (q == 0) ctl->k_valid[b][row] = valid ? 1 : 0;
+      if (q == 0) ctl->k_valid[grp][row] = r.valid ? 1 : 0;
+    };
+    bool ok = true;
+    // i-th tile of the group: wait for the buffer (P.V of the group's previous tile), convert, publish
+    auto finish_tile = [&](int i, const RowRegs& r) -> bool {
+      if (i >= 1) {
+        bool w = mbar_wait(smem_u32(&ctl->pv_done[grp]), (i - 1) & 1);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) return false;
+      }
+      convert_store(r);
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->k_full[b]));
-      phys_cur = phys_next;
-      phys_next = phys_n2;
-      idx_n2 = idx_n3;
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->k_full[grp]));
+      return true;
+    };
+    if (n_mine > 0) {
+      RowRegs ra, rb;
+      long long phys_next = tc_physical_row(p, bi, load_idx(1));
+      int idx_n2 = load_idx(2);
+      issue_loads(ra, tc_physical_row(p, bi, load_idx(0)));
+      for (int i = 0; i < n_mine && ok; i += 2) {
+        // tile i lives in ra; start tile i+1 into rb, then finish tile i
+        if (i + 1 < n_mine) issue_loads(rb, phys_next);
+        long long phys_n2 = tc_physical_row(p, bi, idx_n2);
+        int idx_n3 = load_idx(i + 3);
+        ok = finish_tile(i, ra);
+        if (!ok || i + 1 >= n_mine) break;
+        // tile i+1 lives in rb; start tile i+2 into ra, then finish tile i+1
+        if (i + 2 < n_mine) issue_loads(ra, phys_n2);
+        phys_next = tc_physical_row(p, bi, idx_n3);
+        idx_n2 = load_idx(i + 4);
+        ok = finish_tile(i + 1, rb);
+      }
     }
     if (!ok && lane == 0) {
       ctl->abort = 1;
