@@ -99,6 +99,31 @@ int pto_li_scores(const int8_t* idx_query, const void* idx_query_scale, const in
                   int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
                   int max_blocks, int flags, void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
+/* Lightning indexer for callers that cannot allocate device memory. No counterpart in the
+ * reference: it exists for hosts of this library that run where cudaMalloc is off limits - inside
+ * a serving engine whose memory pool owns all of HBM, or in a process that must not touch the
+ * allocator while another component is capturing a CUDA graph. Same arguments and results as
+ * `pto_li_decode`, minus the workspace: the fp32 score rows and the status words live in a
+ * file-scope `static __device__` array of PTO_LI_STATIC_SCRATCH_BYTES that every GPU loading the
+ * library holds until the process exits.
+ *   - limit: 256 + t * max_blocks * block_size * 4 bytes must fit in the array, otherwise
+ *     PTO_ERR_WORKSPACE is returned and nothing is launched (t = 16 tokens at 131072 keys, or 64
+ *     tokens at 32768 keys, fit);
+ *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress, with
+ *     that device current) and caches it; make that first call outside of any stream capture;
+ *   - all calls share the one array and it keeps the previous call's contents; the status words
+ *     are cleared at the start of each call, every score that is read is written first. Two calls
+ *     that overlap on the GPU (different streams) race on it: serialise them;
+ *   - `status_out` (host, PTO_STATUS_WORDS ints, may be NULL) receives the status words after the
+ *     call; passing it synchronises the stream. */
+#define PTO_LI_STATIC_SCRATCH_BYTES (8u << 20)
+int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
+                         const void* idx_key_scale, const void* idx_weight, int scale_dtype,
+                         const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res,
+                         int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
+                         int max_blocks, int selected_count, int flags, int32_t* status_out,
+                         pto_stream_t stream);
+
 /* Top-k stage alone over f32 score rows with row stride `row_stride` elements
  * (TopKSort/Merge/Extract semantics, lightning_indexer_quant_impl.py:196-312: exact, -1 padded). */
 int pto_li_topk(const float* scores, int64_t row_stride, const int32_t* act_seq_key, int32_t* topk_res,

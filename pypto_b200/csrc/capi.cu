@@ -270,6 +270,30 @@ int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, co
   return PTO_OK;
 }
 
+// Scratch of `pto_li_decode_static`: status words + fp32 score rows. In host code this name is only
+// a stand-in for the device object; its device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_li_static_scratch[PTO_LI_STATIC_SCRATCH_BYTES];
+
+// Device address of the static scratch on the current device, resolved once per device.
+int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  PTO_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(PTO_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_li_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      return fail(PTO_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    }
+    cache[dev] = ptr;
+  }
+  *out = cache[dev];
+  return PTO_OK;
+}
+
 int check_workspace(void* ws, size_t have, size_t need) {
   if (ws == nullptr) return fail(PTO_ERR_WORKSPACE, "workspace is null");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return fail(PTO_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -359,6 +383,41 @@ int pto_li_decode(const int8_t* idx_query, const void* idx_query_scale, const in
   if (rc != PTO_OK) return rc;
   return run_li_topk(scores, static_cast<int64_t>(max_blocks) * block_size, act_seq_key, topk_res, b, s1,
                      selected_count, flags, status, stream);
+}
+
+int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
+                         const void* idx_key_scale, const void* idx_weight, int scale_dtype,
+                         const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res, int b, int s1,
+                         int n_heads, int head_dim, int block_size, int block_num, int max_blocks,
+                         int selected_count, int flags, int32_t* status_out, pto_stream_t stream) {
+  int rc = check_li_common(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, scale_dtype,
+                           act_seq_key, block_table, b, s1, n_heads, head_dim, block_size, block_num, max_blocks);
+  if (rc != PTO_OK) return rc;
+  PTO_REQUIRE(topk_res != nullptr, "topk_res is null");
+  const size_t need = pto_li_workspace_bytes(b * s1, max_blocks, block_size);
+  if (need == 0 || need > PTO_LI_STATIC_SCRATCH_BYTES) {
+    return fail(PTO_ERR_WORKSPACE,
+                "%d tokens x %d keys need %zu bytes of scratch, the static array holds %u: use pto_li_decode with "
+                "a caller-allocated workspace",
+                b * s1, max_blocks * block_size, need, static_cast<unsigned>(PTO_LI_STATIC_SCRATCH_BYTES));
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);  // first call on this device: resolves and caches the address
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(cudaMemsetAsync(scratch, 0, kStatusBytes, stream));  // the status words must start at zero
+  int32_t* status = reinterpret_cast<int32_t*>(scratch);
+  float* scores = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + kStatusBytes);
+  rc = run_li_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, scale_dtype, act_seq_key,
+                     block_table, scores, nullptr, b, s1, block_num, max_blocks, flags, status, stream);
+  if (rc != PTO_OK) return rc;
+  rc = run_li_topk(scores, static_cast<int64_t>(max_blocks) * block_size, act_seq_key, topk_res, b, s1,
+                   selected_count, flags, status, stream);
+  if (rc != PTO_OK) return rc;
+  if (status_out != nullptr) {
+    PTO_CUDA(cudaMemcpyAsync(status_out, scratch, PTO_STATUS_WORDS * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    PTO_CUDA(cudaStreamSynchronize(stream));
+  }
+  return PTO_OK;
 }
 
 size_t pto_sfa_workspace_bytes(int t, int nq) {
