@@ -103,8 +103,7 @@ def _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weigh
     sd = _scale_dtype(qs, ks, w)
     _need(n_heads == 64 and head_dim == 128 and block_size == 128,
           "indexer geometry: 64 heads x 128 dims, 128-token blocks")
-    dev = _same_device([q, qs, kc, ks, w, act, bt])
-    return dev, (q, qs, kc, ks, w, act, bt), dict(t=t, b=b, s1=t // b, n_heads=n_heads, head_dim=head_dim,
+    return None, (q, qs, kc, ks, w, act, bt), dict(t=t, b=b, s1=t // b, n_heads=n_heads, head_dim=head_dim,
                                                    block_size=block_size, block_num=block_num,
                                                    max_blocks=bt.shape[1], scale_dtype=sd)
 
@@ -119,7 +118,7 @@ def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_
     _need(out.dtype == torch.int32 and out.numel() == m["t"] * selected_count,
           "topk_res: int32 [t, 1, selected_count]")
     _need(1 <= selected_count <= 2048, "selected_count must be in [1, 2048]")
-    _need(out.device == dev, "topk_res must be on the same device")
+    dev = _same_device([q, qs, kc, ks, w, act, bt, out])
     lib = _lib.load()
     nbytes = lib.pto_li_workspace_bytes(m["t"], m["max_blocks"], m["block_size"])
     flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_SCORE_SIMT if _simt_scores else 0)
@@ -142,15 +141,18 @@ def lightning_indexer_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_
                                                     idx_weight, act_seq_key, block_table)
     sc = unwrap(scores, "scores")
     stride = m["max_blocks"] * m["block_size"]
-    _need(sc.device == dev and sc.dtype == torch.float32 and tuple(sc.shape) == (m["t"], stride),
+    _need(sc.dtype == torch.float32 and tuple(sc.shape) == (m["t"], stride),
           "scores: float32 [t, max_blocks*block_size]")
     fm_ptr = None
+    devs = [q, qs, kc, ks, w, act, bt, sc]
     if first_mm is not None:
         fm = unwrap(first_mm, "first_mm")
         _need(simt, "first_mm needs simt=True")
-        _need(fm.device == dev and fm.dtype == torch.float16 and tuple(fm.shape) == (m["t"] * m["n_heads"], stride),
+        _need(fm.dtype == torch.float16 and tuple(fm.shape) == (m["t"] * m["n_heads"], stride),
               "first_mm: float16 [t*n_heads, max_blocks*block_size]")
         fm_ptr = fm.data_ptr()
+        devs.append(fm)
+    dev = _same_device(devs)
     lib = _lib.load()
     with torch.cuda.device(dev):
         ws = _workspace(dev, 256)
@@ -301,13 +303,13 @@ def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, id
     kn = unwrap(key_nope_2d, "key_nope_2d")
     kr = unwrap(key_rope_2d, "key_rope_2d")
     sc = unwrap(k_nope_scales, "k_nope_scales")
-    _same_device([q, qn, qr, kn, kr, sc, out_idx, out])
     _need(t == m["t"], "indexer and attention query token counts differ")
     _need(m["block_size"] == 128, "block_size must be 128")
     n_rows = m["block_num"] * 128
     _need(kn.dtype == torch.int8 and tuple(kn.shape) == (n_rows, 512), "key_nope_2d: int8 [block_num*128, 512]")
     _need(kr.dtype == torch.bfloat16 and tuple(kr.shape) == (n_rows, 64), "key_rope_2d: bfloat16 [block_num*128, 64]")
     _need(sc.dtype == torch.float32 and tuple(sc.shape) == (n_rows, 4), "k_nope_scales: float32 [block_num*128, 4]")
+    dev = _same_device([q, qs, kc, ks, w, act, bt, qn, qr, kn, kr, sc, out_idx, out])
     lib = _lib.load()
     nbytes = lib.pto_decode_workspace_bytes(t, m["max_blocks"], 128, int(nq))
     flags = 0 if sort else _lib.PTO_LI_UNSORTED

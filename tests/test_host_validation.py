@@ -1,0 +1,108 @@
+"""Host-side validation of the operator wrappers: every bad call is refused with a Python exception
+before anything is launched (failures are injected on the host only)."""
+import pytest
+import torch
+
+import pypto_b200 as pto
+from pypto_b200 import inputs as gen
+
+
+@pytest.fixture(scope="module")
+def d():
+    return gen.make_inputs([300, 129], s1=1, seed=1, with_topk=True)
+
+
+def li_args(d, **over):
+    a = dict(idx_query=d.idx_query, idx_query_scale=d.idx_query_scale, idx_key_cache=d.idx_key_cache,
+             idx_key_scale=d.idx_key_scale, idx_weight=d.idx_weight, act_seq_key=d.act_seq_key,
+             block_table=d.block_table, topk_res=torch.zeros((d.t, 1, 2048), dtype=torch.int32))
+    a.update(over)
+    return list(a.values()) + [None, None, 2048]
+
+
+def sfa_args(d, **over):
+    a = dict(query_nope=d.query_nope, query_rope=d.query_rope, key_nope_2d=d.key_nope_2d, key_rope_2d=d.key_rope_2d,
+             k_nope_scales=d.k_nope_scales, topk_indices=d.topk_indices, block_table=d.block_table,
+             kv_act_seqs=d.act_seq_key, attention_out=torch.zeros((d.b, 1, 128, 512), dtype=torch.bfloat16))
+    a.update(over)
+    return list(a.values()) + [128, 1, 576 ** -0.5, 2048, 128, d.max_blocks, None]
+
+
+def test_from_torch_mirrors_the_reference_rules():
+    t = torch.zeros(4, 6)
+    h = pto.from_torch(t, name="x", dynamic_axis=[0])
+    assert h.shape == [-1, 6] and h.ori_shape == [4, 6] and h.data_ptr == t.data_ptr() and h.dtype == torch.float32
+    with pytest.raises(TypeError):
+        pto.from_torch([1, 2, 3])
+    with pytest.raises(RuntimeError, match="not all tensors are contiguous"):
+        pto.from_torch(t.t())
+    assert pto.from_torch(torch.tensor(3.0)).shape == [1]
+
+
+def test_cpu_tensors_are_refused_there_is_no_cpu_path(d):
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pto.lightning_indexer_decode(*li_args(d))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pto.sparse_flash_attention_quant_d(*sfa_args(d))
+
+
+@pytest.mark.parametrize("field,bad,exc", [
+    ("idx_query", lambda d: d.idx_query.to(torch.int32), ValueError),
+    ("idx_query", lambda d: d.idx_query[:, :32].contiguous(), ValueError),
+    ("idx_query_scale", lambda d: d.idx_query_scale.to(torch.float16), ValueError),  # mixed scale dtypes
+    ("idx_key_cache", lambda d: d.idx_key_cache.reshape(-1, 128), ValueError),
+    ("idx_weight", lambda d: d.idx_weight[:, :10].contiguous(), ValueError),
+    ("act_seq_key", lambda d: d.act_seq_key.to(torch.int64), ValueError),
+    ("block_table", lambda d: d.block_table[:1].contiguous(), ValueError),
+    ("topk_res", lambda d: torch.zeros((d.t, 1, 100), dtype=torch.int32), ValueError),
+    ("idx_query", lambda d: d.idx_query.transpose(1, 2), RuntimeError),  # non-contiguous
+    ("idx_query", lambda d: "not a tensor", TypeError),
+])
+def test_indexer_rejects_bad_arguments(d, field, bad, exc):
+    with pytest.raises(exc):
+        pto.lightning_indexer_decode(*li_args(d, **{field: bad(d)}))
+
+
+@pytest.mark.parametrize("field,bad,exc", [
+    ("query_nope", lambda d: d.query_nope.to(torch.float16), ValueError),
+    ("query_rope", lambda d: d.query_rope[:, :32].contiguous(), ValueError),
+    ("key_nope_2d", lambda d: d.key_nope_2d.to(torch.bfloat16), ValueError),  # bf16 cache: not this path
+    ("k_nope_scales", lambda d: d.k_nope_scales[:, :2].contiguous(), ValueError),
+    ("topk_indices", lambda d: d.topk_indices.to(torch.int64), ValueError),
+    ("kv_act_seqs", lambda d: d.act_seq_key.float(), ValueError),
+    ("attention_out", lambda d: torch.zeros((d.b, 1, 128, 256), dtype=torch.bfloat16), ValueError),
+    ("block_table", lambda d: d.block_table.t(), RuntimeError),
+])
+def test_attention_rejects_bad_arguments(d, field, bad, exc):
+    with pytest.raises(exc):
+        pto.sparse_flash_attention_quant_d(*sfa_args(d, **{field: bad(d)}))
+
+
+def test_scalar_arguments(d):
+    a = sfa_args(d)
+    a[10] = 2  # n_kv
+    with pytest.raises(ValueError):
+        pto.sparse_flash_attention_quant_p(*a)
+    a = li_args(d)
+    a[-1] = 4096  # selected_count
+    a[7] = torch.zeros((d.t, 1, 4096), dtype=torch.int32)
+    with pytest.raises(ValueError):
+        pto.lightning_indexer_decode(*a)
+
+
+def test_packed_cache_shape(d):
+    cache = gen.pack_kv_rows(d.key_nope_2d, d.key_rope_2d, d.k_nope_scales)
+    assert cache.shape == (d.block_num * 128, 656)
+    with pytest.raises(ValueError):
+        pto.sparse_attention_antiquant_d(d.query_nope, d.query_rope, cache[:, :640].contiguous(), d.topk_indices,
+                                         d.block_table, d.act_seq_key,
+                                         torch.zeros((d.t * 128, 512), dtype=torch.bfloat16), 128, 1, 0.04, 2048, 128,
+                                         d.max_blocks, None)
+
+
+def test_tiling_dataclasses_are_accepted_and_inert():
+    c = pto.LightningIndexerConfigs()
+    assert c.extend_param["scale"] == 1 / 2048.0
+    s = pto.SaTileShapeConfig(g_tile=128, s_kv_tile=2048, c1_tile_shape=[128] * 6, v1_tile_shape=[8, 2048],
+                              c2_tile_shape=[128] * 6, v2_tile_shape=[64, 128])
+    assert s.s_kv_tile == 2048
