@@ -89,6 +89,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
 }
 
+// Same bound, but polling with the non-blocking probe: a blocked try_wait was measured to resume
+// about a microsecond after the phase completes, which is too slow for per-tile hand-offs.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      if (mbar_test_wait(bar, parity)) return true;
+    }
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: tiled 2-D load global -> shared, completion on an mbarrier. No multicast anywhere.
 // x is the innermost (contiguous) coordinate and must make x * elem_size a multiple of 16 bytes.
@@ -263,6 +277,7 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
 cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
-cudaError_t launch_sfa_tc(const SfaParams& p, cudaStream_t stream);  // nq == 128 only
+cudaError_t launch_sfa_tc(const SfaParams& p, cudaStream_t stream);       // nq == 128 only, one CTA per value half
+cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster
 
 }  // namespace pto

@@ -292,6 +292,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[slot]));
               }
+              if (p.debug & 2) res[i] = __uint_as_float(v0[0] ^ v1[31]) * ks; else
               res[i] = (weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32)) * ks;
             }
           }

@@ -18,6 +18,7 @@
 // 32 rows in the same chunked layout, which serves both as the K-major B operand of q.K^T and as
 // the MN-major B operand (V) of P.V; P 128 x 32 bf16 (64-byte swizzle). All waits are bounded.
 #include "common.cuh"
+#include "sfa_common.cuh"
 
 namespace pto {
 
@@ -48,81 +49,6 @@ struct TcCtl {
 };
 
 constexpr size_t kTcSmemBytes = 1024 + kChunks * kQChunkBytes + 2 * kKBufBytes + kPBytes + sizeof(TcCtl);
-
-__device__ __forceinline__ float ex2f(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-__device__ __forceinline__ uint64_t desc_kmajor_sw64(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(512 >> 4) << 32;  // 8 rows * 64 B
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(4) << 61;  // SWIZZLE_64B
-  return d;
-}
-
-// MN-major operand, 128-byte swizzle: 64 elements (128 B) contiguous along MN, 8 K-rows per 1024-byte
-// atom; `lbo` = bytes between 64-element groups along MN, `sbo` = bytes between 8-row groups along K
-__device__ __forceinline__ uint64_t desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(lbo >> 4) << 16;
-  d |= static_cast<uint64_t>(sbo >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-// 16 int8 -> 16 bf16 of (value * scale): byte b^0x80 placed in the mantissa of 2^23 gives
-// 2^23 + 128 + x exactly; subtracting 8388736 leaves x; one fp32 multiply and one rounding to bf16,
-// i.e. bf16(fp32(x) * scale) as the golden computes it.
-__device__ __forceinline__ void dequant16(const uint4 v, const float scale, uint4& o0, uint4& o1) {
-  const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
-  uint32_t o[8];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float f0 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7540)) - 8388736.0f) * scale;
-    const float f1 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7541)) - 8388736.0f) * scale;
-    const float f2 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7542)) - 8388736.0f) * scale;
-    const float f3 = (__uint_as_float(__byte_perm(w[e], 0x4B000000u, 0x7543)) - 8388736.0f) * scale;
-    o[2 * e] = pack_bf16x2(f0, f1);
-    o[2 * e + 1] = pack_bf16x2(f2, f3);
-  }
-  o0 = make_uint4(o[0], o[1], o[2], o[3]);
-  o1 = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
-__device__ __forceinline__ long long tc_physical_row(const SfaParams& p, int bi, int idx) {
-  if (idx < 0) return -1;
-  const int blk = idx / p.block_size;
-  if (blk >= p.max_blocks) {
-    set_status(p.status, PTO_ST_BAD_PAGE, idx, 20);
-    return -1;
-  }
-  const int phys = p.block_table[static_cast<int64_t>(bi) * p.max_blocks + blk];
-  const long long r = static_cast<long long>(phys) * p.block_size + idx % p.block_size;
-  if (phys < 0 || r >= p.n_rows) {
-    set_status(p.status, PTO_ST_BAD_PAGE, phys, 21);
-    return -1;
-  }
-  return r;
-}
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 sfa_tc_kernel(SfaParams p) {
