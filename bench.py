@@ -194,10 +194,6 @@ def run_stage(args, dev):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / max(args.steps, 1)
     by = gen.algorithmic_bytes(d)
-    if os.environ.get("PTO_DEBUG"):
-        from pypto_b200 import ops as _ops
-        words = _ops._workspace(dev, 256)[:256].view(torch.int32).cpu().tolist()
-        print("debug words 16..31:", words[16:32], flush=True)
     print(json.dumps({"stage": args.stage, "batch": args.batch, "ctx": args.ctx, "s1": args.s1, "ms": ms,
                       "score_stage_bytes": gen.score_stage_bytes(d), "algorithmic_bytes": by,
                       "status": pto.workspace_status(dev)[0]}), flush=True)

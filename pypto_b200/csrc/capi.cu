@@ -6,7 +6,6 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -42,11 +41,6 @@ int fail(int code, const char* fmt, ...) {
 
 constexpr size_t kStatusBytes = 256;
 static_assert(PTO_STATUS_WORDS * sizeof(int32_t) <= kStatusBytes, "status area");
-
-inline int debug_flags() {
-  const char* e = std::getenv("PTO_DEBUG");
-  return e ? std::atoi(e) : 0;
-}
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -170,7 +164,6 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
   p.block_num = block_num;
   p.max_blocks = max_blocks;
   p.status = status;
-  p.debug = debug_flags();
   const bool simt = (flags & PTO_LI_SCORE_SIMT) != 0;
   PTO_REQUIRE(simt || first_mm == nullptr, "first_mm is only produced with PTO_LI_SCORE_SIMT");
   DeviceInfo di;
@@ -264,7 +257,6 @@ int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, co
   p.packed = packed;
   p.n_rows = n_rows;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
-  p.debug = debug_flags();
   p.status = status;
   PTO_CUDA(pto::launch_sfa(p, stream));
   return PTO_OK;

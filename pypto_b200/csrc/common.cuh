@@ -204,6 +204,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // misc
 // ---------------------------------------------------------------------------------------------
@@ -238,7 +248,6 @@ struct LiParams {
   void* first_mm;           // optional f16 [t*64, row_stride] (SIMT path)
   int64_t row_stride;
   int b, s1, block_num, max_blocks;
-  int debug;       // experiment switches (PTO_DEBUG environment variable), 0 in production
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
   int32_t* status;
@@ -266,7 +275,6 @@ struct SfaParams {
   float* part_o;                // [t, n_split, nq, 512]
   float* part_ml;               // [t, n_split, nq, 2]
   int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed;
-  int debug;  // experiment switches (PTO_DEBUG environment variable), 0 in production
   int64_t n_rows;
   float scale_log2;  // softmax_scale * log2(e)
   int32_t* status;
@@ -277,7 +285,6 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
 cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
-cudaError_t launch_sfa_tc(const SfaParams& p, cudaStream_t stream);       // nq == 128 only, one CTA per value half
 cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster
 
 }  // namespace pto

@@ -12,9 +12,10 @@
 // 128-byte swizzle) -> four tcgen05.mma kind::i8 (M = 128 keys, N = 64*s1 heads, K = 32) into a
 // TMEM accumulator -> epilogue warps read their key's row (one TMEM lane = one key), apply
 // ReLU/2^-11/fp16 rounding and the weighted head sum, and write the fp32 score.
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2..17 epilogue (four groups
-// of four warps that take pages round-robin; a single warp is latency-bound on the conversion chain,
-// so thread-level parallelism has to come from many warps). All waits are bounded.
+// Warp roles: warp 0 TMA producer, warps 1..2 MMA issuers (alternate pages; warp 1 owns TMEM),
+// warps 3..18 epilogue (four groups of four warps that take pages round-robin; a single warp is
+// latency-bound on the conversion chain, so thread-level parallelism has to come from many warps).
+// A ring of 8 slots pairs one shared-memory stage with one TMEM accumulator. All waits are bounded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -292,7 +293,6 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[slot]));
               }
-              if (p.debug & 2) res[i] = __uint_as_float(v0[0] ^ v1[31]) * ks; else
               res[i] = (weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32)) * ks;
             }
           }

@@ -316,22 +316,19 @@ sfa_cluster_kernel(SfaParams p) {
       if (!ok) break;
       tc_fence_after();
       float s[64];
-      {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + kClColS + kCT * b, v);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {  // 16 columns at a time keeps the register peak low
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(lane_addr + kClColS + kCT * b + 16 * g, v);
         tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v[c]);
-        tmem_ld_32x32b_x32(lane_addr + kClColS + kCT * b + 32, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(v[c]);
+        for (int c = 0; c < 16; ++c) s[16 * g + c] = __uint_as_float(v[c]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->s_free[b]));
       // ---- exchange the partial scores with the peer CTA (per warp: 32 rows, 8 KB) ------------------
-      if (!(p.debug & 1024)) {
+      {
         if (lane == 0) bulk_wait_read_all();  // the previous tile's copy has finished reading the send slice
         __syncwarp();
 #pragma unroll
@@ -367,30 +364,38 @@ sfa_cluster_kernel(SfaParams p) {
       }
       // ---- scale, mask, tile max -----------------------------------------------------------------
       mbar_wait_spin(smem_u32(&ctl->k_full[b]), (j >> 1) & 1);  // already complete: orders the k_valid reads
-      float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // Fast path when every row of the tile is valid (always, except in a token's last tile or
+      // after a rejected index): max on the raw sums, scale folded into the exponent's FMA.
+      const uint4 va = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][0]);
+      const uint4 vb = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][16]);
+      const uint4 vc = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][32]);
+      const uint4 vd = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][48]);
+      const uint32_t all_and = va.x & va.y & va.z & va.w & vb.x & vb.y & vb.z & vb.w & vc.x & vc.y & vc.z & vc.w &
+                               vd.x & vd.y & vd.z & vd.w;
+      if (all_and != 0x01010101u) {
+        const uint32_t vw[16] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w,
+                                 vc.x, vc.y, vc.z, vc.w, vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint4 vv = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][16 * g]);
-        const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 64; ++c) {
           const bool valid = ((vw[c >> 2] >> ((c & 3) * 8)) & 0xffu) != 0;
-          const float x = valid ? s[16 * g + c] * p.scale_log2 : -INFINITY;
-          s[16 * g + c] = x;
-          mt4[c & 3] = fmaxf(mt4[c & 3], x);
+          if (!valid) s[c] = -INFINITY;
         }
       }
-      const float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3]));
+      float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; ++c) mt4[c & 3] = fmaxf(mt4[c & 3], s[c]);
+      const float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3])) * p.scale_log2;  // scale > 0
       // ---- exponentials against a speculative reference -------------------------------------------
       // The previous tile's P.V may still be running; rescales are rare, so exp2 is taken now
       // against the row's current reference (never more than 2^8 below the tile max) and the
       // reference is only moved, together with O, once that P.V is done.
       float m_spec = (m_seen == -INFINITY || mt > m_seen + kClRescale) ? mt : m_seen;
       if (m_spec == -INFINITY) m_spec = 0.f;
+      const float neg_spec = -m_spec;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        s[c] = ex2f(s[c] - m_spec);
+        s[c] = ex2f(fmaf(s[c], p.scale_log2, neg_spec));
         ls4[c & 3] += s[c];
       }
       const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
@@ -413,13 +418,13 @@ sfa_cluster_kernel(SfaParams p) {
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         tc_fence_after();
 #pragma unroll 1
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_addr + kClColO + ch * 32, o);
+        for (int ch = 0; ch < 16; ++ch) {
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(lane_addr + kClColO + ch * 16, o);
           tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-          tmem_st_32x32b_x32(lane_addr + kClColO + ch * 32, o);
+          for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          tmem_st_32x32b_x16(lane_addr + kClColO + ch * 16, o);
         }
         tc_wait_st();
       }
@@ -515,13 +520,6 @@ sfa_cluster_kernel(SfaParams p) {
     auto issue_loads = [&](RowRegs& r, long long phys) {
       r.valid = phys >= 0;
       if (!r.valid) return;
-      if (p.debug & 2048) {
-#pragma unroll
-        for (int m = 0; m < 4; ++m) r.d[m] = make_uint4(1, 2, 3, 4);
-        r.r = make_uint4(0, 0, 0, 0);
-        r.sc = make_float2(1.f, 1.f);
-        return;
-      }
       const uint8_t* nope = p.packed ? kn_bytes + phys * 656 : kn_bytes + phys * 512;
       const uint8_t* rope = p.packed ? kn_bytes + phys * 656 + 512 : kr_bytes + phys * 128;
       const uint8_t* scl = p.packed ? kn_bytes + phys * 656 + 640 : sc_bytes + phys * 16;

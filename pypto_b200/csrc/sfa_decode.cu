@@ -450,8 +450,8 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
   const int t = p.b * p.s1;
   const int n_hb = (p.nq + kHB - 1) / kHB;
   if (p.nq == 128) {
-    // all 128 heads of a token: tcgen05 kernel (M = 128); narrower head slices use mma.sync below
-    e = (p.debug & 512) ? launch_sfa_tc(p, stream) : launch_sfa_cluster(p, stream);
+    // all 128 heads of a token: tcgen05 cluster kernel (M = 128); narrower head slices use mma.sync below
+    e = launch_sfa_cluster(p, stream);
   } else {
     sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);
     e = cudaGetLastError();

@@ -49,11 +49,17 @@ __device__ __forceinline__ int key_pos(unsigned long long key) {
   return static_cast<int>(~static_cast<unsigned int>(key & 0xffffffffull));
 }
 
-// descending bitonic sort of n (power of two) keys in shared memory; all threads of the CTA call it
+// descending bitonic sort of n (power of two) keys in shared memory; all threads of the CTA call it.
+// Pair t of a stage is handled by thread t (and t + blockDim, ...), so for strides below 64 warp w only
+// touches the 64-key blocks w, w + 32, ...: those stages need a warp barrier only, unless the previous
+// stage had a larger stride and other warps wrote into the block.
 __device__ void bitonic_sort_desc(unsigned long long* buf, int n) {
+  __syncthreads();
+  int prev_stride = 64;
   for (int size = 2; size <= n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      __syncthreads();
+      if (stride >= 64 || prev_stride >= 64) __syncthreads(); else __syncwarp();
+      prev_stride = stride;
       for (int t = threadIdx.x; t < (n >> 1); t += blockDim.x) {
         const int lo = 2 * t - (t & (stride - 1));  // index with the `stride` bit clear
         const int hi = lo + stride;
@@ -110,18 +116,33 @@ __device__ void find_threshold_bin(TopkSmem* sm, unsigned int need) {
   __syncthreads();
 }
 
+// Applies f(value, position) to every element of row[0, eff). Loads go through the read-only path
+// and are issued four 16-byte loads at a time before the bodies run, so the latency of one batch is
+// paid once (the bodies contain shared-memory atomics the compiler will not move loads across).
 template <typename F>
 __device__ __forceinline__ void for_each_element(const float* row, int eff, F&& f) {
   const int tid = threadIdx.x;
   const int n4 = eff & ~3;
-  for (int j = tid * 4; j < n4; j += kTopkThreads * 4) {
-    const float4 v = *reinterpret_cast<const float4*>(row + j);
-    f(v.x, j);
-    f(v.y, j + 1);
-    f(v.z, j + 2);
-    f(v.w, j + 3);
+  constexpr int kStep = kTopkThreads * 4;
+  for (int j0 = tid * 4; j0 < n4; j0 += 4 * kStep) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * kStep;
+      if (j < n4) v[u] = __ldg(reinterpret_cast<const float4*>(row + j));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * kStep;
+      if (j < n4) {
+        f(v[u].x, j);
+        f(v[u].y, j + 1);
+        f(v[u].z, j + 2);
+        f(v[u].w, j + 3);
+      }
+    }
   }
-  for (int j = n4 + tid; j < eff; j += kTopkThreads) f(row[j], j);
+  for (int j = n4 + tid; j < eff; j += kTopkThreads) f(__ldg(row + j), j);
 }
 
 __global__ void __launch_bounds__(kTopkThreads, 1)
