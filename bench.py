@@ -347,7 +347,11 @@ def main():
                        "partition": f"batch x{world}, no collective on the data path",
                        "l2": "inputs (1.7 GB of cache per rank) larger than L2, no flush needed"},
             "roofline": {"bound": "hbm", "kernel": "li_score_tc_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": achieved / peak,
+                         # dram read+write of one launch: ncu measured 143.93 MB for 138.58 MB algorithmic on
+                         # batch 16 x 65536 (profiles/); the extra is the 4 B/key score write, which scales
+                         # with the keys, so the ratio is applied to this launch
+                         "traffic": int(score_bytes * 143.93 / 138.58), "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": score_bytes, "ms_per_launch": score_ms},
             "roofline_step": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
                               "frac": step_gbs / peak, "algorithmic_bytes_per_step": bytes_step},
