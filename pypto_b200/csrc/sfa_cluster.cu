@@ -15,8 +15,8 @@
 // addition commutes, so both CTAs get bit-identical scores, maxima and P). Nothing is computed
 // twice except the softmax itself.
 //   warp 0        MMA issuer (owns TMEM: O 256 columns + two 64-column score buffers)
-//   warps 1..4    softmax, one thread per head row
-//   warps 5..12   producers: 16-byte gathers, int8 -> bf16 in registers, swizzled stores (2 K buffers)
+//   warps 1..8    softmax, two threads per head row (32 of the tile's 64 columns each)
+//   warps 9..16   producers: 16-byte gathers, int8 -> bf16 in registers, swizzled stores (2 K buffers)
 // All waits are bounded; local waits that order peer writes use cluster-scope acquire.
 #include "common.cuh"
 #include "sfa_common.cuh"
@@ -36,7 +36,8 @@ constexpr int kKBuf = 4 * kKNopeChunk + kKRope;  // 36,864
 constexpr int kPBuf = 128 * 128;                 // 128 heads x 64 rows bf16
 constexpr int kXBuf = 128 * 256;                 // 128 heads x 64 fp32 partial scores
 constexpr int kClSoftmaxWarp0 = 1;
-constexpr int kClProducerWarp0 = 5;
+constexpr int kClSoftmaxWarps = 8;   // two warps per TMEM lane quarter: columns 0-31 and 32-63 of the tile
+constexpr int kClProducerWarp0 = 1 + kClSoftmaxWarps;
 constexpr int kClProducerWarps = 8;
 constexpr int kClThreads = 32 * (kClProducerWarp0 + kClProducerWarps);  // 544
 constexpr uint32_t kClTmemCols = 512;
@@ -47,17 +48,20 @@ constexpr float kClRescale = 8.0f;
 struct ClCtl {
   uint64_t k_full[2];   // producers filled K buffer b                      (count: producer warps)
   uint64_t s_full[2];   // partial scores of buffer b complete               (tcgen05.commit)
-  uint64_t s_free[2];   // softmax set has read score buffer b               (count 4 warps)
+  uint64_t s_free[2];   // softmax warps have read score buffer b             (count 8 warps)
   uint64_t pv_done[2];  // P.V of a tile with parity b complete              (tcgen05.commit)
-  uint64_t p_full;      // P tile written                                    (count 4 warps)
-  uint64_t x_full[4];   // peer's partials of lane quarter w landed in my receive buffer (1 arming arrive + 8192 tx bytes)
-  uint64_t x_free[4];   // peer's warp w has consumed what my warp w sent             (1 remote arrival)
+  uint64_t p_full;      // P tile written                                    (count 8 warps)
+  uint64_t x_full[8];   // peer's partials of softmax warp w landed in my receive buffer (1 arming arrive + 4096 tx bytes)
+  uint64_t x_free[8];   // peer's warp w has consumed what my warp w sent             (1 remote arrival)
   uint32_t tmem_base;
   int abort;
   __align__(16) unsigned char k_valid[2][kCT];
+  uint64_t pair_bar[4];  // the two softmax warps of a lane quarter meet here (count 2), bounded like every wait
+  float pair_mt[2][2][128];  // [tile parity][column half][row]: tile max of each half; the halves' sums at the end
 };
 
-constexpr size_t kClSmemBytes = 1024 + kQBytes + 2 * kKBuf + kPBuf + 2 * kXBuf + sizeof(ClCtl);
+constexpr size_t kClSmemBytes = kQBytes + 2 * kKBuf + kPBuf + 2 * kXBuf + sizeof(ClCtl);
+static_assert(kClSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -138,10 +142,15 @@ __device__ __forceinline__ bool mbar_wait_cluster_blocking(uint32_t bar, uint32_
 
 __global__ void __launch_bounds__(kClThreads, 1)
 sfa_cluster_kernel(SfaParams p) {
-  extern __shared__ uint8_t sfa_cl_smem_raw[];
-  const uint32_t raw = smem_u32(sfa_cl_smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* smem = sfa_cl_smem_raw + (base - raw);
+  // the swizzled operand tiles need a 1024-byte aligned base: the kernel has no static shared memory,
+  // so the dynamic window starts aligned; a misaligned base is reported instead of computing garbage
+  extern __shared__ __align__(1024) uint8_t sfa_cl_smem_raw[];
+  const uint32_t base = smem_u32(sfa_cl_smem_raw);
+  uint8_t* smem = sfa_cl_smem_raw;
+  if ((base & 1023u) != 0) {
+    if (threadIdx.x == 0) set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(base), 43);
+    return;
+  }
   const uint32_t q_base = base;
   const uint32_t k_base = q_base + kQBytes;
   const uint32_t p_base = k_base + 2 * kKBuf;
@@ -193,15 +202,16 @@ sfa_cluster_kernel(SfaParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctl->k_full[i]), kClProducerWarps);
       mbar_init(smem_u32(&ctl->s_full[i]), 1);
-      mbar_init(smem_u32(&ctl->s_free[i]), 4);
+      mbar_init(smem_u32(&ctl->s_free[i]), kClSoftmaxWarps);
       mbar_init(smem_u32(&ctl->pv_done[i]), 1);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
       mbar_init(smem_u32(&ctl->x_full[i]), 1);
       mbar_init(smem_u32(&ctl->x_free[i]), 1);
-      mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i]), 32 * 256);  // armed for the first tile
+      mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i]), 32 * 128);  // armed for the first tile
     }
-    mbar_init(smem_u32(&ctl->p_full), 4);
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->pair_bar[i]), 2);
+    mbar_init(smem_u32(&ctl->p_full), kClSoftmaxWarps);
     ctl->abort = 0;
     fence_mbar_init();
   }
@@ -292,47 +302,57 @@ sfa_cluster_kernel(SfaParams p) {
     __syncwarp();
   } else if (warp < kClProducerWarp0) {
     // ================================ softmax ===================================================
+    // Thread (row, half): head row = TMEM lane, columns [32*half, 32*half+32) of the 64-row tile.
+    const int half = (warp - kClSoftmaxWarp0) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    const int wslot = half * 4 + quarter;  // this warp's exchange slice and barriers
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    // exchange: send buffer = first half of the X area, receive buffer = second half; a warp owns
-    // the 8 KB slice of its 32 rows in both. Row = 16 units of 16 bytes, unit u stored at u ^ (r & 15).
-    uint8_t* send_row = x_ptr + row * 256;
-    const uint8_t* recv_row = x_ptr + kXBuf + row * 256;
-    const uint32_t send_slice = x_base + quarter * (32 * 256);
-    const uint32_t recv_slice_peer = map_to_peer(x_base + kXBuf + quarter * (32 * 256), peer);
-    const uint32_t xfull_local = smem_u32(&ctl->x_full[quarter]);
+    // exchange: send area = first half of X, receive area = second half; a warp owns a 4 KB slice
+    // (32 rows x 128 B) in both. A row is 8 units of 16 bytes, unit u stored at u ^ (lane & 7).
+    uint8_t* send_row = x_ptr + wslot * 4096 + lane * 128;
+    const uint8_t* recv_row = x_ptr + kXBuf + wslot * 4096 + lane * 128;
+    const uint32_t send_slice = x_base + wslot * 4096;
+    const uint32_t recv_slice_peer = map_to_peer(x_base + kXBuf + wslot * 4096, peer);
+    const uint32_t xfull_local = smem_u32(&ctl->x_full[wslot]);
     const uint32_t xfull_peer = map_to_peer(xfull_local, peer);
-    const uint32_t xfree_local = smem_u32(&ctl->x_free[quarter]);
+    const uint32_t xfree_local = smem_u32(&ctl->x_free[wslot]);
     const uint32_t xfree_peer = map_to_peer(xfree_local, peer);
-    const int xsw = row & 15;
-    float m_seen = -INFINITY;  // the row's reference max
-    float l_run = 0.f;
+    const int xsw = lane & 7;
+    float m_seen = -INFINITY;  // the row's reference max (identical in both halves)
+    float l_run = 0.f;         // this half's share of the row sum
     bool ok = true;
+    uint32_t pair_phase = 0;
+    auto pair_sync = [&]() -> bool {  // orders the pair_mt writes of both warps before the reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->pair_bar[quarter]));
+      const bool w = mbar_wait_spin(smem_u32(&ctl->pair_bar[quarter]), pair_phase & 1u);
+      ++pair_phase;
+      return __all_sync(0xffffffffu, w);
+    };
     for (int j = 0; j < ntiles; ++j) {
       const int b = j & 1;
       ok = mbar_wait_spin(smem_u32(&ctl->s_full[b]), (j >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float s[64];
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {  // 16 columns at a time keeps the register peak low
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(lane_addr + kClColS + kCT * b + 16 * g, v);
+      float s[32];
+      {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + kClColS + kCT * b + 32 * half, v);
         tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) s[16 * g + c] = __uint_as_float(v[c]);
+        for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v[c]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->s_free[b]));
-      // ---- exchange the partial scores with the peer CTA (per warp: 32 rows, 8 KB) ------------------
+      // ---- exchange the partial scores with the peer CTA (per warp: 32 rows x 32 columns, 4 KB) ------
       {
         if (lane == 0) bulk_wait_read_all();  // the previous tile's copy has finished reading the send slice
         __syncwarp();
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
+        for (int u = 0; u < 8; ++u) {
           *reinterpret_cast<float4*>(send_row + ((u ^ xsw) << 4)) = make_float4(s[4 * u], s[4 * u + 1], s[4 * u + 2], s[4 * u + 3]);
         }
         fence_proxy_async();
@@ -341,7 +361,7 @@ sfa_cluster_kernel(SfaParams p) {
           // the peer's warp must have consumed the previous tile before its receive slice is overwritten
           if (j >= 1 && !mbar_wait_cluster(xfree_local, (j - 1) & 1)) ok = false;
           if (ok) {
-            bulk_copy_to_peer(recv_slice_peer, send_slice, 32 * 256, xfull_peer);
+            bulk_copy_to_peer(recv_slice_peer, send_slice, 4096, xfull_peer);
             bulk_commit();
           }
         }
@@ -349,7 +369,7 @@ sfa_cluster_kernel(SfaParams p) {
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const float4 o = *reinterpret_cast<const float4*>(recv_row + ((u ^ xsw) << 4));
           s[4 * u] += o.x;
           s[4 * u + 1] += o.y;
@@ -358,48 +378,46 @@ sfa_cluster_kernel(SfaParams p) {
         }
         __syncwarp();
         if (lane == 31) {
-          mbar_arrive_expect_tx(xfull_local, 32 * 256);  // arm the receive barrier for the next tile, then
-          mbar_arrive_remote_relaxed(xfree_peer);         // tell the peer this warp's slice has been consumed
+          mbar_arrive_expect_tx(xfull_local, 4096);  // arm the receive barrier for the next tile, then
+          mbar_arrive_remote_relaxed(xfree_peer);     // tell the peer this warp's slice has been consumed
         }
       }
-      // ---- scale, mask, tile max -----------------------------------------------------------------
+      // ---- scale, mask, max of this half ------------------------------------------------------------
       mbar_wait_spin(smem_u32(&ctl->k_full[b]), (j >> 1) & 1);  // already complete: orders the k_valid reads
-      // Fast path when every row of the tile is valid (always, except in a token's last tile or
-      // after a rejected index): max on the raw sums, scale folded into the exponent's FMA.
-      const uint4 va = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][0]);
-      const uint4 vb = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][16]);
-      const uint4 vc = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][32]);
-      const uint4 vd = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][48]);
-      const uint32_t all_and = va.x & va.y & va.z & va.w & vb.x & vb.y & vb.z & vb.w & vc.x & vc.y & vc.z & vc.w &
-                               vd.x & vd.y & vd.z & vd.w;
-      if (all_and != 0x01010101u) {
-        const uint32_t vw[16] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w,
-                                 vc.x, vc.y, vc.z, vc.w, vd.x, vd.y, vd.z, vd.w};
+      // all rows valid (always, except in a token's last tile or after a rejected index): max on
+      // the raw sums, scale folded into the exponent's FMA
+      const uint4 va = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][32 * half]);
+      const uint4 vb = *reinterpret_cast<const uint4*>(&ctl->k_valid[b][32 * half + 16]);
+      if ((va.x & va.y & va.z & va.w & vb.x & vb.y & vb.z & vb.w) != 0x01010101u) {
+        const uint32_t vw[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const bool valid = ((vw[c >> 2] >> ((c & 3) * 8)) & 0xffu) != 0;
-          if (!valid) s[c] = -INFINITY;
+        for (int c = 0; c < 32; ++c) {
+          if (((vw[c >> 2] >> ((c & 3) * 8)) & 0xffu) == 0) s[c] = -INFINITY;
         }
       }
       float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mt4[c & 3] = fmaxf(mt4[c & 3], s[c]);
-      const float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3])) * p.scale_log2;  // scale > 0
-      // ---- exponentials against a speculative reference -------------------------------------------
-      // The previous tile's P.V may still be running; rescales are rare, so exp2 is taken now
-      // against the row's current reference (never more than 2^8 below the tile max) and the
-      // reference is only moved, together with O, once that P.V is done.
-      float m_spec = (m_seen == -INFINITY || mt > m_seen + kClRescale) ? mt : m_seen;
+      for (int c = 0; c < 32; ++c) mt4[c & 3] = fmaxf(mt4[c & 3], s[c]);
+      const float mt_half = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3])) * p.scale_log2;  // scale > 0
+      ctl->pair_mt[b][half][row] = mt_half;
+      // ---- exponentials against a speculative reference ---------------------------------------------
+      // The previous tile's P.V may still be running and the other half's maximum is not known yet;
+      // rescales are rare, so exp2 is taken now against the row's current reference (never more than
+      // 2^8 below this half's maximum) and corrected by one factor once the reference is final.
+      float m_spec = (m_seen == -INFINITY || mt_half > m_seen + kClRescale) ? mt_half : m_seen;
       if (m_spec == -INFINITY) m_spec = 0.f;
       const float neg_spec = -m_spec;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         s[c] = ex2f(fmaf(s[c], p.scale_log2, neg_spec));
         ls4[c & 3] += s[c];
       }
       const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      // ---- join the row's state: previous tile's P.V done => P buffer free, O at rest ---------------
+      // ---- join: the other half's maximum, then the previous tile's P.V (P buffer free, O at rest) -----
+      ok = pair_sync();
+      if (!ok) break;
+      const float mt = fmaxf(mt_half, ctl->pair_mt[b][half ^ 1][row]);
       if (j > 0) {
         ok = mbar_wait_spin(smem_u32(&ctl->pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1);
         ok = __all_sync(0xffffffffu, ok);
@@ -418,27 +436,27 @@ sfa_cluster_kernel(SfaParams p) {
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         tc_fence_after();
 #pragma unroll 1
-        for (int ch = 0; ch < 16; ++ch) {
+        for (int ch = 0; ch < 8; ++ch) {  // this half's 128 of the 256 output columns
           uint32_t o[16];
-          tmem_ld_32x32b_x16(lane_addr + kClColO + ch * 16, o);
+          tmem_ld_32x32b_x16(lane_addr + kClColO + half * 128 + ch * 16, o);
           tc_wait_ld();
 #pragma unroll
           for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-          tmem_st_32x32b_x16(lane_addr + kClColO + ch * 16, o);
+          tmem_st_32x32b_x16(lane_addr + kClColO + half * 128 + ch * 16, o);
         }
         tc_wait_st();
       }
-      // ---- P row (bf16, 128-byte row, unit u at u ^ (row & 7)) --------------------------------------
+      // ---- P row (bf16, 128-byte row, unit u at u ^ (row & 7)); this half owns units 4*half .. +3 ------
       uint8_t* prow = p_ptr + row * 128;
       const int psw = row & 7;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 4; ++u) {
         uint4 w;
         w.x = pack_bf16x2(s[8 * u] * factor, s[8 * u + 1] * factor);
         w.y = pack_bf16x2(s[8 * u + 2] * factor, s[8 * u + 3] * factor);
         w.z = pack_bf16x2(s[8 * u + 4] * factor, s[8 * u + 5] * factor);
         w.w = pack_bf16x2(s[8 * u + 6] * factor, s[8 * u + 7] * factor);
-        *reinterpret_cast<uint4*>(prow + ((u ^ psw) << 4)) = w;
+        *reinterpret_cast<uint4*>(prow + (((4 * half + u) ^ psw) << 4)) = w;
       }
       fence_proxy_async();
       tc_fence_before();
@@ -446,48 +464,53 @@ sfa_cluster_kernel(SfaParams p) {
       if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
     }
     if (lane == 0) bulk_wait_read_all();
-    const float l_last = l_run;
-    // ---- output: the set that handled the last tile holds the final (m, l) ---------------------------
+    // ---- output: row sum = both halves' shares; each half stores 128 of the CTA's 256 columns ---------
     if (ok) {
       ok = mbar_wait_spin(smem_u32(&ctl->pv_done[(ntiles - 1) & 1]), ((ntiles - 1) >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        tc_fence_after();
-        if (p.n_split == 1) {
-          const float inv = l_last > 0.f ? 1.f / l_last : 0.f;
-          __nv_bfloat16* dst = p.out + (q_row0 + row) * 512 + crank * 256;
+    }
+    float l_last = 0.f;
+    if (ok) {
+      ctl->pair_mt[ntiles & 1][half][row] = l_run;
+      ok = pair_sync();
+      l_last = l_run + ctl->pair_mt[ntiles & 1][half ^ 1][row];
+    }
+    if (ok) {
+      tc_fence_after();
+      if (p.n_split == 1) {
+        const float inv = l_last > 0.f ? 1.f / l_last : 0.f;
+        __nv_bfloat16* dst = p.out + (q_row0 + row) * 512 + crank * 256 + half * 128;
 #pragma unroll 1
-          for (int ch = 0; ch < 8; ++ch) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_addr + kClColO + ch * 32, o);
-            tc_wait_ld();
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kClColO + half * 128 + ch * 32, o);
+          tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-              w.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-              w.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-              w.w = pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + ch * 32 + c) = w;
-            }
+          for (int c = 0; c < 32; c += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = w;
           }
-        } else {
-          const int64_t prow_i = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + row;
-          float* dst = p.part_o + prow_i * 512 + crank * 256;
+        }
+      } else {
+        const int64_t prow_i = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + row;
+        float* dst = p.part_o + prow_i * 512 + crank * 256 + half * 128;
 #pragma unroll 1
-          for (int ch = 0; ch < 8; ++ch) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_addr + kClColO + ch * 32, o);
-            tc_wait_ld();
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kClColO + half * 128 + ch * 32, o);
+          tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-              *reinterpret_cast<uint4*>(dst + ch * 32 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-            }
+          for (int c = 0; c < 32; c += 4) {
+            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
           }
-          if (crank == 0) {
-            p.part_ml[prow_i * 2] = m_seen;
-            p.part_ml[prow_i * 2 + 1] = l_last;
-          }
+        }
+        if (crank == 0 && half == 0) {
+          p.part_ml[prow_i * 2] = m_seen;
+          p.part_ml[prow_i * 2 + 1] = l_last;
         }
       }
     }
@@ -499,8 +522,8 @@ sfa_cluster_kernel(SfaParams p) {
     // ================================ producers =================================================
     // 256 threads, four per row: thread (row, q) owns latent units q, q+4, q+8, q+12 of this CTA's
     // 256-dim half (unit = 16 int8 -> 16 bf16 = two 16-byte stores), rope unit q of the 32-dim
-    // half, and the half's two scales. Loads of the next tile are in flight while the current one
-    // is dequantised; only the stores sit behind the buffer wait.
+    // half, and the half's two scales. The next tile's loads are issued as soon as the current
+    // registers are dequantised; only the stores sit behind the buffer wait.
     const int ptid = tid - kClProducerWarp0 * 32;
     const int row = ptid >> 2;
     const int q = ptid & 3;
@@ -531,32 +554,29 @@ sfa_cluster_kernel(SfaParams p) {
     const int sw = row & 7;
     const int rsw = (row >> 1) & 3;
     bool ok = true;
-    RowRegs ra, rb;
-    // tile j in `ra`, tile j+1 in `rb` (both in flight), swapped every iteration by unrolling twice
-    long long phys2 = tc_physical_row(p, bi, load_idx(2));
-    int idx3 = load_idx(3);
+    RowRegs ra;
+    long long phys_next = tc_physical_row(p, bi, load_idx(1));
+    int idx_n2 = load_idx(2);
     issue_loads(ra, tc_physical_row(p, bi, load_idx(0)));
-    issue_loads(rb, tc_physical_row(p, bi, load_idx(1)));
-    auto finish = [&](int j, RowRegs& cur) -> bool {
+    for (int j = 0; j < ntiles; ++j) {
       const int b = j & 1;
       uint4 cv[8];
-      const bool valid = cur.valid;
+      const bool valid = ra.valid;
       if (valid) {
 #pragma unroll
-        for (int m = 0; m < 4; ++m) dequant16(cur.d[m], (m < 2) ? cur.sc.x : cur.sc.y, cv[2 * m], cv[2 * m + 1]);
+        for (int m = 0; m < 4; ++m) dequant16(ra.d[m], (m < 2) ? ra.sc.x : ra.sc.y, cv[2 * m], cv[2 * m + 1]);
       } else {
 #pragma unroll
         for (int m = 0; m < 8; ++m) cv[m] = make_uint4(0, 0, 0, 0);
       }
-      const uint4 rr = valid ? cur.r : make_uint4(0, 0, 0, 0);
-      // the registers of `cur` are free: start tile j+2 into them
-      if (j + 2 < ntiles) issue_loads(cur, phys2);
-      phys2 = tc_physical_row(p, bi, idx3);
-      idx3 = load_idx(j + 4);
+      const uint4 rr = valid ? ra.r : make_uint4(0, 0, 0, 0);
+      if (j + 1 < ntiles) issue_loads(ra, phys_next);
+      phys_next = tc_physical_row(p, bi, idx_n2);
+      idx_n2 = load_idx(j + 3);
       if (j >= 2) {
-        bool w = mbar_wait_spin(smem_u32(&ctl->pv_done[b]), ((j - 2) >> 1) & 1);
-        w = __all_sync(0xffffffffu, w);
-        if (!w) return false;
+        ok = mbar_wait_spin(smem_u32(&ctl->pv_done[b]), ((j - 2) >> 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
       uint8_t* kbuf = k_ptr + b * kKBuf;
 #pragma unroll
@@ -569,11 +589,6 @@ sfa_cluster_kernel(SfaParams p) {
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->k_full[b]));
-      return true;
-    };
-    for (int j = 0; j < ntiles && ok; j += 2) {
-      ok = finish(j, ra);
-      if (ok && j + 1 < ntiles) ok = finish(j + 1, rb);
     }
     if (!ok && lane == 0) {
       ctl->abort = 1;
