@@ -50,3 +50,66 @@ def test_fused_is_deterministic_and_idempotent():
     i2, o2 = _fused(d, sort=True)
     assert torch.equal(i1, i2)
     assert torch.equal(o1, o2)
+
+
+def test_prefill_chunk_many_query_tokens_per_sequence():
+    """A prefill chunk: one sequence, 12 new query tokens at the end of a 5000-token context
+    (query i sees the first S - 11 + i positions). The indexer runs the tokens in groups of four
+    per launch; the attention entry is the prefill one."""
+    s1, S = 12, 5000
+    d = gen.make_inputs([S], s1=s1, seed=91)
+    g = d.to(DEV)
+    idx = torch.zeros((d.t, 1, 2048), dtype=torch.int32, device=DEV)
+    pto.lightning_indexer_decode(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                 g.act_seq_key, g.block_table, idx, None, None, 2048)
+    out = torch.zeros((d.b, s1, 128, 512), dtype=torch.bfloat16, device=DEV)
+    pto.sparse_flash_attention_quant_p(g.query_nope, g.query_rope, g.key_nope_2d, g.key_rope_2d, g.k_nope_scales,
+                                       idx.reshape(d.t, 2048), g.block_table, g.act_seq_key, out, 128, 1, 576 ** -0.5,
+                                       2048, 128, d.max_blocks, pto.SaTileShapeConfig())
+    torch.cuda.synchronize()
+    assert pto.workspace_status()[0] == 0
+    want_idx, _, rows = oracle.lightning_indexer(d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale,
+                                                 d.idx_weight, d.act_seq, d.block_table, s1)
+    idx = idx.cpu()
+    for ti in range(d.t):
+        untied, _ = oracle.topk_set_diff(idx[ti], want_idx[ti], rows[ti])
+        assert untied == 0, f"token {ti}"
+        assert int(idx[ti].max()) < S - (s1 - 1 - ti)  # causal cut
+    want = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                   want_idx.reshape(d.t, 2048), d.block_table, d.act_seq, s1)
+    e = oracle.attention_errors(out.cpu(), want)
+    assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, e
+
+
+def test_mtp_long_context_properties():
+    """Configuration-3-like shape at reduced batch: 4 sequences of 131072 keys, two query tokens
+    each. Size-independent checks: every index inside the causal range, indices distinct, the
+    selected scores dominate a sample of unselected ones, attention rows finite and normalised
+    (each output element within the min/max of the dequantised values of its column is too weak;
+    instead the output equals the oracle attention evaluated on the kernel's own indices)."""
+    d = gen.make_inputs([131072] * 4, s1=2, seed=333)
+    g = d.to(DEV)
+    idx = torch.zeros((d.t, 1, 2048), dtype=torch.int32, device=DEV)
+    out = torch.zeros((d.b, 2, 128, 512), dtype=torch.bfloat16, device=DEV)
+    pto.decode_indexer_attention_quant(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                       g.query_nope, g.query_rope, g.key_nope_2d, g.key_rope_2d, g.k_nope_scales,
+                                       g.act_seq_key, g.block_table, idx, out)
+    sc = torch.zeros((d.t, d.max_blocks * 128), dtype=torch.float32, device=DEV)
+    pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                 g.act_seq_key, g.block_table, sc)
+    torch.cuda.synchronize()
+    assert pto.workspace_status()[0] == 0
+    idx_c, sc_c = idx.cpu().reshape(d.t, 2048), sc.cpu()
+    for ti in range(d.t):
+        eff = 131072 - (1 - ti % 2)
+        row = idx_c[ti]
+        assert int(row.min()) >= 0 and int(row.max()) < eff
+        assert len(set(row.tolist())) == 2048
+        kth = sc_c[ti][row.long()].min()
+        mask = torch.ones(eff, dtype=torch.bool)
+        mask[row.long()] = False
+        assert float(sc_c[ti][:eff][mask].max()) <= float(kth)  # exact top-k of the kernel's own scores
+    want = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                   idx_c, d.block_table, d.act_seq, 2)
+    e = oracle.attention_errors(out.cpu(), want)
+    assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, e
