@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Generate the committed golden vectors by running the REFERENCE's own torch goldens.
 
-Run once, in a container that has the reference checkout (default /root/reference, or
-$PYPTO_REFERENCE):
+Run once, where the reference checkout is available ($PYPTO_REFERENCE, default: a directory
+`reference` next to this repository):
 
     python tests/golden/make_golden.py
 
@@ -39,7 +39,7 @@ sys.path.insert(0, str(ROOT))
 
 from pypto_b200 import inputs as gen  # noqa: E402
 
-REF = Path(os.environ.get("PYPTO_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("PYPTO_REFERENCE", str(ROOT.parent / "reference")))
 
 
 class _Anything(types.ModuleType):
