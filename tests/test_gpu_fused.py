@@ -10,10 +10,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _fused(d, sort=False):
+def _fused(d, sort=False, fill=0):
     g = d.to(DEV)
-    idx = torch.zeros((d.t, 1, 2048), dtype=torch.int32, device=DEV)
-    out = torch.zeros((d.b, d.s1, 128, 512), dtype=torch.bfloat16, device=DEV)
+    idx = torch.full((d.t, 1, 2048), fill, dtype=torch.int32, device=DEV)
+    out = torch.full((d.b, d.s1, 128, 512), float(fill), dtype=torch.bfloat16, device=DEV)
     pto.decode_indexer_attention_quant(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
                                        g.query_nope, g.query_rope, g.key_nope_2d, g.key_rope_2d, g.k_nope_scales,
                                        g.act_seq_key, g.block_table, idx, out, sort=sort)
@@ -112,4 +112,20 @@ def test_mtp_long_context_properties():
     want = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
                                    idx_c, d.block_table, d.act_seq, 2)
     e = oracle.attention_errors(out.cpu(), want)
+    assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, e
+
+
+def test_empty_and_tiny_sequences():
+    """A sequence of length 0 selects nothing (all -1) and its attention row stays zero; lengths
+    1 and 5 select every position."""
+    d = gen.make_inputs([0, 1, 5, 300], s1=1, seed=8)
+    idx, out = _fused(d, sort=True, fill=7)   # outputs pre-filled: every element must be overwritten
+    assert torch.all(idx[0] == -1) and torch.all(out[0] == 0)
+    assert idx[1, 0, 0] == 0 and torch.all(idx[1, 0, 1:] == -1)
+    assert sorted(idx[2, 0, :5].tolist()) == [0, 1, 2, 3, 4] and torch.all(idx[2, 0, 5:] == -1)
+    want_idx, _, _ = oracle.lightning_indexer(d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale,
+                                              d.idx_weight, d.act_seq, d.block_table, d.s1)
+    want = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                   want_idx.reshape(d.t, 2048), d.block_table, d.act_seq, d.s1)
+    e = oracle.attention_errors(out, want)
     assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, e
