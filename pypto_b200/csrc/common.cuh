@@ -103,6 +103,13 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
   }
 }
 
+// Warp-wide form (all 32 lanes call it, converged): every lane polls and the verdict is made uniform.
+// Polling from one lane while the others wait at a shuffle was measured slower (the divergent
+// section costs more than the 31 extra probes).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait_spin(bar, parity));
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: tiled 2-D load global -> shared, completion on an mbarrier. No multicast anywhere.
 // x is the innermost (contiguous) coordinate and must make x * elem_size a multiple of 16 bytes.

@@ -1,6 +1,7 @@
 // Helpers shared by the tcgen05 sparse-attention kernels: descriptors for the 64-byte-swizzled and
 // MN-major operands, TMEM store, int8 -> bf16 dequantisation, paged row lookup.
 #pragma once
+#include <climits>
 
 #include "common.cuh"
 
@@ -78,5 +79,84 @@ __device__ __forceinline__ long long tc_physical_row(const SfaParams& p, int bi,
   return r;
 }
 
+// tcgen05.mma with the A operand in tensor memory (row m of A = TMEM lane m, 32-bit column c holds the
+// K elements 2c and 2c+1 of a 16-bit type), B in shared memory.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Shared-memory accesses by 32-bit shared-window address: a generic pointer costs two registers and an
+// address conversion per access, and the softmax and producer loops have no register to spare.
+__device__ __forceinline__ float4 lds_v4f(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 lds_v4u(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_v4f(uint32_t a, float x, float y, float z, float w) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void sts_v4u(uint32_t a, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+__device__ __forceinline__ void sts_u8(uint32_t a, uint32_t v) { asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+
+// Read-only global loads that stay where they are written. The compiler treats `__ldg` as a load of
+// invariant memory and is free to sink it to its first use, across waits and barriers, which turns a
+// software prefetch into a load-then-stall; volatile asm keeps the issue point. The gathers do not
+// allocate in L1: beside ~220 KB of shared memory the L1 is a few KB, and it is needed for the stack
+// (a spilled register or a by-value argument re-read in a loop otherwise costs a trip to L2).
+__device__ __forceinline__ uint4 ldg_pinned_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float2 ldg_pinned_v2f(const void* p) {
+  float2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int ldg_pinned_i32(const void* p) {
+  int v;
+  asm volatile("ld.global.nc.L1::no_allocate.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+// The same lookup in two steps, so that a caller can fetch the block-table entry a tile ahead and
+// only branch on it once it has arrived.
+constexpr int kTableSkip = INT_MIN;  // nothing to fetch: padding index, or an index already reported
+__device__ __forceinline__ int tc_table_entry(const SfaParams& p, int bi, int idx) {
+  if (idx < 0) return kTableSkip;
+  const int blk = idx / p.block_size;
+  if (blk >= p.max_blocks) {
+    set_status(p.status, PTO_ST_BAD_PAGE, idx, 20);
+    return kTableSkip;
+  }
+  return ldg_pinned_i32(p.block_table + static_cast<int64_t>(bi) * p.max_blocks + blk);
+}
+__device__ __forceinline__ long long tc_row_from_entry(const SfaParams& p, int idx, int entry) {
+  if (entry == kTableSkip) return -1;
+  const long long r = static_cast<long long>(entry) * p.block_size + idx % p.block_size;
+  if (entry < 0 || r >= p.n_rows) {
+    set_status(p.status, PTO_ST_BAD_PAGE, entry, 21);
+    return -1;
+  }
+  return r;
+}
 
 }  // namespace pto
