@@ -52,7 +52,6 @@ constexpr int kKBuf = 4 * kKNopeChunk + kKRope;  // 36,864
 constexpr int kNK = 3;                           // K buffers
 constexpr int kXSlice = 32 * 256;                // 32 head rows x 64 fp32 partial scores
 constexpr int kXBuf = 4 * kXSlice;               // send area; two receive areas of the same size follow it
-constexpr int kClXWarp0 = 1;   // exchange warps: 1, 2, 3 and the last warp of the CTA
 constexpr int kClXWarps = 4;
 constexpr int kClSoftmaxWarp0 = 4;
 constexpr int kClSoftmaxWarps = 8;   // two warps per TMEM lane quarter: columns 0-31 and 32-63 of the tile
@@ -136,6 +135,22 @@ struct ClCtx {
   uint32_t k_base, x_base, tmem_base, crank, peer;
   int ntiles, begin, end, ti, sp, bi;
 };
+
+// One 128-byte line of a selected row per thread of the row's four (q = 0..3): two lines of this CTA's
+// latent half, the rope half, the scales.
+__device__ __forceinline__ void cl_prefetch_row(const SfaParams& p, long long phys, uint32_t crank, int q) {
+  if (phys < 0) return;
+  const uint8_t* kn_bytes = reinterpret_cast<const uint8_t*>(p.kn);
+  const uint8_t* a;
+  if (q < 2) {
+    a = (p.packed ? kn_bytes + phys * 656 : kn_bytes + phys * 512) + crank * 256 + q * 128;
+  } else if (q == 2) {
+    a = (p.packed ? kn_bytes + phys * 656 + 512 : reinterpret_cast<const uint8_t*>(p.kr) + phys * 128) + crank * 64;
+  } else {
+    a = (p.packed ? kn_bytes + phys * 656 + 640 : reinterpret_cast<const uint8_t*>(p.kn_scales) + phys * 16) + crank * 8;
+  }
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+}
 
 // ================================ MMA issuer ====================================================
 // One thread, an event loop: P.V of the oldest tile whose P is written, else q.K^T of the next tile
@@ -426,49 +441,81 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
     if (ok) {
       ok = mbar_wait_warp(smem_u32(&ctl->pv_done), (ntiles - 1) & 1);
     }
+    if (tid == 32 * kClSoftmaxWarp0) TLM(10);
     float l_last = 0.f;
     if (ok) {
       ctl->pair_mt[ntiles & 1][half][row] = l_run;
       ok = pair_sync();
       l_last = l_run + ctl->pair_mt[ntiles & 1][half ^ 1][row];
     }
-    if (ok) {
-      tc_fence_after();
-      if (p.n_split == 1) {
+    if (tid == 32 * kClSoftmaxWarp0) TLM(11);
+    // The rows go out through shared memory (the K buffers are idle now): a thread owns a row, so direct
+    // stores would touch 32 rows per instruction; staged, every store instruction writes 512 contiguous
+    // bytes of one row. Staging row = 32 units of 16 bytes, unit u stored at u ^ (row & 31).
+    // All eight softmax warps reach the barriers below whether or not their waits succeeded.
+    const uint32_t stage = c.k_base;
+    const int ws = warp - kClSoftmaxWarp0;
+    if (ok) tc_fence_after();
+    if (p.n_split == 1) {
+      if (ok) {
         const float inv = l_last > 0.f ? 1.f / l_last : 0.f;
-        __nv_bfloat16* dst = p.out + (q_row0 + row) * 512 + crank * 256 + half * 128;
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t o[32];
           tmem_ld_32x32b_x32(lane_addr + kClColO + half * 128 + ch * 32, o);
           tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
+          for (int cc = 0; cc < 32; cc += 8) {
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = w;
+            w.x = pack_bf16x2(__uint_as_float(o[cc]) * inv, __uint_as_float(o[cc + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[cc + 2]) * inv, __uint_as_float(o[cc + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[cc + 4]) * inv, __uint_as_float(o[cc + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[cc + 6]) * inv, __uint_as_float(o[cc + 7]) * inv);
+            const int unit = 16 * half + ch * 4 + (cc >> 3);
+            sts_v4u(stage + row * 512 + ((unit ^ (row & 31)) << 4), w);
           }
         }
-      } else {
-        const int64_t prow_i = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + row;
-        float* dst = p.part_o + prow_i * 512 + crank * 256 + half * 128;
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (ok) {
+#pragma unroll 4
+        for (int rr = 0; rr < 16; ++rr) {
+          const int r = ws * 16 + rr;
+          const uint4 w = lds_v4u(stage + r * 512 + ((lane ^ (r & 31)) << 4));
+          *reinterpret_cast<uint4*>(p.out + (q_row0 + r) * 512 + crank * 256 + lane * 8) = w;
+        }
+      }
+    } else {
+      const int64_t prow0 = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq;
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_addr + kClColO + half * 128 + ch * 32, o);
-          tc_wait_ld();
+      for (int h = 0; h < 2; ++h) {  // fp32 partials: one column half (128 floats = 512 bytes per row) per pass
+        if (ok && half == h) {
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_addr + kClColO + half * 128 + ch * 32, o);
+            tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            *reinterpret_cast<uint4*>(dst + ch * 32 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+            for (int cc = 0; cc < 32; cc += 4) {
+              const int unit = ch * 8 + (cc >> 2);
+              sts_v4u(stage + row * 512 + ((unit ^ (row & 31)) << 4), make_uint4(o[cc], o[cc + 1], o[cc + 2], o[cc + 3]));
+            }
           }
         }
-        if (crank == 0 && half == 0) {
-          p.part_ml[prow_i * 2] = m_seen;
-          p.part_ml[prow_i * 2 + 1] = l_last;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (ok) {
+#pragma unroll 4
+          for (int rr = 0; rr < 16; ++rr) {
+            const int r = ws * 16 + rr;
+            const uint4 w = lds_v4u(stage + r * 512 + ((lane ^ (r & 31)) << 4));
+            *reinterpret_cast<uint4*>(p.part_o + (prow0 + r) * 512 + crank * 256 + h * 128 + lane * 4) = w;
+          }
         }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+      }
+      if (ok && crank == 0 && half == 0) {
+        p.part_ml[(prow0 + row) * 2] = m_seen;
+        p.part_ml[(prow0 + row) * 2 + 1] = l_last;
       }
     }
     if (!ok && lane == 0) {
@@ -518,19 +565,7 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
     r.r = ldg_pinned_v4(rope + crank * 64 + q * 16);
     r.sc = ldg_pinned_v2f(scl + crank * 8);
   };
-  // one 128-byte line of the row per thread of its four: two of the latent half, the rope half, the scales
-  auto prefetch_row = [&](long long phys) {
-    if (phys < 0) return;
-    const uint8_t* a;
-    if (q < 2) {
-      a = (p.packed ? kn_bytes + phys * 656 : kn_bytes + phys * 512) + crank * 256 + q * 128;
-    } else if (q == 2) {
-      a = (p.packed ? kn_bytes + phys * 656 + 512 : kr_bytes + phys * 128) + crank * 64;
-    } else {
-      a = (p.packed ? kn_bytes + phys * 656 + 640 : sc_bytes + phys * 16) + crank * 8;
-    }
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-  };
+  auto prefetch_row = [&](long long phys) { cl_prefetch_row(p, phys, crank, q); };
   const int sw = row & 7;
   const int rsw = (row >> 1) & 3;
   bool ok = true;
@@ -649,6 +684,18 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
     return;
   }
 
+  // ---- before the setup: the softmax threads touch the Q rows they will copy into tensor memory, so
+  // that the copy finds them in L2 (prefetches do not block; anything that waits here would hold up
+  // the whole CTA's first barrier)
+  if (warp >= kClSoftmaxWarp0 && warp < kClProducerWarp0) {
+    const int qhalf = (warp - kClSoftmaxWarp0) >> 2;
+    const int qrow = (warp & 3) * 32 + lane;
+    const uint8_t* a = reinterpret_cast<const uint8_t*>(p.q_nope + (q_row0 + qrow) * 512 + crank * 256 + qhalf * 128);
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 128));
+    if (qhalf == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q_rope + (q_row0 + qrow) * 64 + crank * 32));
+  }
+
   // ---- setup ------------------------------------------------------------------------------------
   if (tid == 0) {
     for (int i = 0; i < kNK; ++i) {
@@ -676,13 +723,17 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kClTmemCols);
     tmem_relinquish();
   }
+  if (tid == 0) TLM(7);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) TLM(8);
   cluster_sync_all();  // the peer's barriers are initialised before anything is sent to them
+  if (tid == 0) TLM(9);
   tc_fence_after();
   c.tmem_base = ctl->tmem_base;
   const uint32_t tmem_base = c.tmem_base;
   // Q half into tensor memory (A operand of q.K^T): lane = head row, column c = dims 2c, 2c+1
+  static_assert(32 * (kClSoftmaxWarps + 1) == 288, "named barrier 1: softmax warps + the MMA warp");
   if (warp >= kClSoftmaxWarp0 && warp < kClProducerWarp0) {
     const int qhalf = (warp - kClSoftmaxWarp0) >> 2;
     const int qrow = (warp & 3) * 32 + lane;
@@ -715,10 +766,14 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
       tmem_st_32x32b_x16(tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + kClColQR, v);
     }
     tc_wait_st();
+    tc_fence_before();
+    asm volatile("bar.sync 1, 288;" ::: "memory");  // with the MMA warp: Q is in place
+  } else if (warp == 0) {
+    // only the MMA warp waits for Q; producers and exchange warps go straight to work, so the first
+    // tile's index -> block-table -> row chain overlaps the Q loads instead of following them
+    asm volatile("bar.sync 1, 288;" ::: "memory");
+    tc_fence_after();
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   if (tid == 0) TLM(1);
 
   if (warp < kClSoftmaxWarp0) {
