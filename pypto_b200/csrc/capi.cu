@@ -205,7 +205,10 @@ int run_li_topk(const float* scores, int64_t row_stride, const int32_t* act, int
   p.k = k;
   p.flags = flags;
   p.status = status;
-  PTO_CUDA(pto::launch_li_topk(p, stream));
+  DeviceInfo di;
+  const int rc = get_device_info(&di);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_li_topk(p, di.num_sms, stream));
   return PTO_OK;
 }
 

@@ -302,7 +302,7 @@ struct SfaParams {
 cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void* tmap_q, int num_sms,
                                cudaStream_t stream);
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
-cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream);
+cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
 cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster
 

@@ -6,7 +6,13 @@
 // are valid and the rest is -1; eff <= 0 gives all -1. Ties are broken toward the smaller position,
 // which makes the result deterministic (torch.topk leaves tie order unspecified).
 //
-// One CTA per row. Every element is mapped to a unique 64-bit key (order-preserving image of the
+// One cluster of 1, 2, 4 or 8 CTAs per row (as many as keep the grid within one wave of SMs). The
+// scanning passes (1-3) are split over the CTAs of the cluster by position range; what they must agree
+// on travels through distributed shared memory: the range's min/max, the histogram (added into rank
+// every other rank's with remote atomics), the per-rank counts. In the unordered mode every rank writes
+// the positions it selected straight to the output at its offset and pushes only its candidates of
+// the threshold bucket into rank 0's list; in the ordered mode the selected keys are pushed too.
+// Every element is mapped to a unique 64-bit key (order-preserving image of the
 // float in the high word, ~position in the low word), so "the k largest keys" is well defined.
 //   1. min/max of the row                    2. 2048-bin histogram over a monotone linear bucket map
 //   3. bucket above the threshold bucket -> selected; threshold bucket -> candidate buffer (shared)
@@ -33,10 +39,43 @@ struct TopkSmem {
   float red_max[32];
   unsigned int n_sel;
   unsigned int n_cand;
+  // values every rank of the cluster publishes into every other rank's copy (remote stores, made visible
+  // by the next cluster barrier), so that nobody waits for a chain of remote loads
+  float all_min[8], all_max[8];
+  unsigned int all_sel[8], all_cand[8];
   int thr_bin;
   unsigned int thr_above;
   unsigned int thr_count;
 };
+
+__device__ __forceinline__ unsigned int cluster_rank() {
+  unsigned int r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned int cluster_size() {
+  unsigned int r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// all threads of all CTAs of the cluster; orders shared-memory accesses across the cluster
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_addr(const void* local, unsigned int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_peer_u64(uint32_t a, unsigned long long v) {
+  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(a), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_peer_u32(uint32_t a, unsigned int v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_peer_add_u32(uint32_t a, unsigned int v) {
+  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ unsigned int float_order(float f) {
   unsigned int u = __float_as_uint(f);
@@ -120,11 +159,11 @@ __device__ void find_threshold_bin(TopkSmem* sm, unsigned int need) {
 // and are issued four 16-byte loads at a time before the bodies run, so the latency of one batch is
 // paid once (the bodies contain shared-memory atomics the compiler will not move loads across).
 template <typename F>
-__device__ __forceinline__ void for_each_element(const float* row, int eff, F&& f) {
+__device__ __forceinline__ void for_each_element(const float* row, int begin, int end, F&& f) {
   const int tid = threadIdx.x;
-  const int n4 = eff & ~3;
+  const int n4 = begin + ((end - begin) & ~3);  // begin is a multiple of 4
   constexpr int kStep = kTopkThreads * 4;
-  for (int j0 = tid * 4; j0 < n4; j0 += 4 * kStep) {
+  for (int j0 = begin + tid * 4; j0 < n4; j0 += 4 * kStep) {
     float4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -142,7 +181,7 @@ __device__ __forceinline__ void for_each_element(const float* row, int eff, F&& 
       }
     }
   }
-  for (int j = n4 + tid; j < eff; j += kTopkThreads) f(__ldg(row + j), j);
+  for (int j = n4 + tid; j < end; j += kTopkThreads) f(__ldg(row + j), j);
 }
 
 __global__ void __launch_bounds__(kTopkThreads, 1)
@@ -151,7 +190,9 @@ li_topk_kernel(TopkParams p) {
   TopkSmem* sm = reinterpret_cast<TopkSmem*>(topk_smem_raw);
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-  const int row_id = blockIdx.x;
+  const unsigned int csize = cluster_size();
+  const unsigned int rank = cluster_rank();
+  const int row_id = blockIdx.x / csize;
   const int bi = row_id / p.s1;
   const int i = row_id % p.s1;
   const int k = p.k;
@@ -159,24 +200,33 @@ li_topk_kernel(TopkParams p) {
   const float* row = p.scores + static_cast<int64_t>(row_id) * p.row_stride;
   int eff = p.act_seq[bi] - (p.s1 - 1 - i);
   if (eff > p.row_stride) eff = static_cast<int>(p.row_stride);
+  const bool unsorted = (p.flags & PTO_LI_UNSORTED) != 0;
 
-  if (eff <= 0) {
-    for (int j = tid; j < k; j += kTopkThreads) out[j] = -1;
+  // short rows: rank 0 alone, no cluster barrier on this path (every CTA of the cluster takes it)
+  if (eff <= k) {
+    if (rank != 0) return;
+    if (eff <= 0) {
+      for (int j = tid; j < k; j += kTopkThreads) out[j] = -1;
+      return;
+    }
+    int kpow2 = 1;
+    while (kpow2 < k) kpow2 <<= 1;
+    for (int j = tid; j < kpow2; j += kTopkThreads) sm->sel[j] = (j < eff) ? make_key(row[j], j) : 0ull;
+    if (!unsorted) bitonic_sort_desc(sm->sel, kpow2); else __syncthreads();
+    for (int j = tid; j < k; j += kTopkThreads) out[j] = (j < eff) ? key_pos(sm->sel[j]) : -1;
     return;
   }
   int kpow2 = 1;
   while (kpow2 < k) kpow2 <<= 1;
 
-  if (eff <= k) {
-    for (int j = tid; j < kpow2; j += kTopkThreads) sm->sel[j] = (j < eff) ? make_key(row[j], j) : 0ull;
-    if ((p.flags & PTO_LI_UNSORTED) == 0) bitonic_sort_desc(sm->sel, kpow2); else __syncthreads();
-    for (int j = tid; j < k; j += kTopkThreads) out[j] = (j < eff) ? key_pos(sm->sel[j]) : -1;
-    return;
-  }
+  // this rank's share of the positions (a multiple of 4 so that 16-byte loads stay aligned)
+  const int chunk = (((eff + static_cast<int>(csize) - 1) / static_cast<int>(csize)) + 3) & ~3;
+  const int begin = min(eff, static_cast<int>(rank) * chunk);
+  const int end = min(eff, begin + chunk);
 
   // ---- 1. row min / max -------------------------------------------------------------------
   float vmin = INFINITY, vmax = -INFINITY;
-  for_each_element(row, eff, [&](float v, int) {
+  for_each_element(row, begin, end, [&](float v, int) {
     vmin = fminf(vmin, v);
     vmax = fmaxf(vmax, v);
   });
@@ -202,6 +252,17 @@ li_topk_kernel(TopkParams p) {
     vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
     vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
   }
+  if (csize > 1) {
+    if (tid < csize) {  // thread r tells rank r
+      st_peer_u32(peer_addr(&sm->all_min[rank], tid), __float_as_uint(vmin));
+      st_peer_u32(peer_addr(&sm->all_max[rank], tid), __float_as_uint(vmax));
+    }
+    cluster_barrier();
+    for (unsigned int r = 0; r < csize; ++r) {  // every rank arrives at the same pair
+      vmin = fminf(vmin, sm->all_min[r]);
+      vmax = fmaxf(vmax, sm->all_max[r]);
+    }
+  }
   // monotone bucket map: floor((v - vmin) * inv), clamped. Non-finite range -> everything in bin 0
   // and the radix fallback resolves it.
   float inv = 0.f;
@@ -218,17 +279,34 @@ li_topk_kernel(TopkParams p) {
   };
 
   // ---- 2. histogram -----------------------------------------------------------------------
-  for_each_element(row, eff, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
+  for_each_element(row, begin, end, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
   __syncthreads();
-  find_threshold_bin(sm, static_cast<unsigned int>(k));
+  if (csize > 1) {
+    // every rank adds its counts into every other rank's histogram; a rank must not receive additions
+    // before its own pass is over (they would be indistinguishable from its own counts only after it)
+    unsigned int mine[kBins / kTopkThreads];
+#pragma unroll
+    for (int u = 0; u < kBins / kTopkThreads; ++u) mine[u] = sm->hist[tid + u * kTopkThreads];
+    cluster_barrier();  // all local histograms complete and read into registers
+#pragma unroll
+    for (int u = 0; u < kBins / kTopkThreads; ++u) {
+      if (mine[u] != 0) {
+        for (unsigned int r = 0; r < csize; ++r) {
+          if (r != rank) red_peer_add_u32(peer_addr(&sm->hist[tid + u * kTopkThreads], r), mine[u]);
+        }
+      }
+    }
+    cluster_barrier();  // every rank holds the row's histogram
+  }
+  find_threshold_bin(sm, static_cast<unsigned int>(k));  // the same answer in every rank
   const int thr_bin = sm->thr_bin;
   const unsigned int above = sm->thr_above;
   const unsigned int thr_count = sm->thr_count;
   const unsigned int need = static_cast<unsigned int>(k) - above;  // to take from the threshold bucket
 
   if (thr_count <= static_cast<unsigned int>(kCandCap)) {
-    // ---- 3. collect -------------------------------------------------------------------------
-    for_each_element(row, eff, [&](float v, int pos) {
+    // ---- 3. collect (this rank's positions) ---------------------------------------------------
+    for_each_element(row, begin, end, [&](float v, int pos) {
       const int bkt = bucket(v);
       if (bkt > thr_bin) {
         sm->sel[atomicAdd(&sm->n_sel, 1u)] = make_key(v, pos);
@@ -237,19 +315,54 @@ li_topk_kernel(TopkParams p) {
       }
     });
     __syncthreads();
-    // ---- 4. best `need` of the candidates ---------------------------------------------------
-    if (need == thr_count) {
-      for (unsigned int j = tid; j < need; j += kTopkThreads) sm->sel[above + j] = sm->cand[j];
-    } else {
+    if (csize > 1) {
+      if (tid < csize) {
+        st_peer_u32(peer_addr(&sm->all_sel[rank], tid), sm->n_sel);
+        st_peer_u32(peer_addr(&sm->all_cand[rank], tid), sm->n_cand);
+      }
+      cluster_barrier();  // every rank's lists are complete and all counts are known everywhere
+      // offsets of this rank's lists in the row's lists
+      unsigned int sel_off = 0, cand_off = 0;
+      for (unsigned int r = 0; r < rank; ++r) {
+        sel_off += sm->all_sel[r];
+        cand_off += sm->all_cand[r];
+      }
+      // the candidates (and, for ordered output, the selected keys) of ranks 1.. are pushed into rank 0's
+      // lists at their offsets: remote stores from all ranks at once, completed by the barrier below
+      if (rank != 0) {
+        const unsigned int my_cand = sm->n_cand;
+        for (unsigned int j = tid; j < my_cand; j += kTopkThreads) st_peer_u64(peer_addr(&sm->cand[cand_off + j], 0), sm->cand[j]);
+      }
+      const unsigned int my_sel = sm->n_sel;
+      if (unsorted) {
+        // the selected positions go straight to the output
+        for (unsigned int j = tid; j < my_sel; j += kTopkThreads) out[sel_off + j] = key_pos(sm->sel[j]);
+      } else if (rank != 0) {
+        for (unsigned int j = tid; j < my_sel; j += kTopkThreads) st_peer_u64(peer_addr(&sm->sel[sel_off + j], 0), sm->sel[j]);
+      }
+      cluster_barrier();  // rank 0's lists are complete; the other ranks are done
+      if (rank != 0) return;
+      __syncthreads();
+    }
+    // ---- 4. best `need` of the candidates (rank 0) --------------------------------------------
+    if (need != thr_count) {
       int cpow2 = 1;
       while (cpow2 < static_cast<int>(thr_count)) cpow2 <<= 1;
       for (int j = thr_count + tid; j < cpow2; j += kTopkThreads) sm->cand[j] = 0ull;
       bitonic_sort_desc(sm->cand, cpow2);
-      for (unsigned int j = tid; j < need; j += kTopkThreads) sm->sel[above + j] = sm->cand[j];
     }
+    if (unsorted && csize > 1) {
+      for (unsigned int j = tid; j < need; j += kTopkThreads) out[above + j] = key_pos(sm->cand[j]);
+      return;
+    }
+    for (unsigned int j = tid; j < need; j += kTopkThreads) sm->sel[above + j] = sm->cand[j];
     __syncthreads();
   } else {
     // ---- 4'. massive ties: MSB-first radix select on the 64-bit keys of the threshold bucket ----
+    // (rank 0 alone, over the whole row; the decision above is the same in every rank)
+    if (rank != 0) return;
+    if (tid == 0) sm->n_sel = 0;
+    __syncthreads();
     // digits: 11/11/10 bits of the value word, then 11/11/10 bits of the inverted position.
     // invariant: keys in the bucket with (key >> shift) > prefix are selected; `remaining` more are
     // needed among those with (key >> shift) == prefix.
@@ -263,7 +376,7 @@ li_topk_kernel(TopkParams p) {
       const int new_shift = shift - w;
       for (int j = tid; j < kBins; j += kTopkThreads) sm->hist[j] = 0;
       __syncthreads();
-      for_each_element(row, eff, [&](float v, int pos) {
+      for_each_element(row, 0, eff, [&](float v, int pos) {
         if (bucket(v) != thr_bin) return;
         const unsigned long long key = make_key(v, pos);
         if (shift < 64 && (key >> shift) != prefix) return;
@@ -278,7 +391,7 @@ li_topk_kernel(TopkParams p) {
       __syncthreads();
     }
     // every key with (key >> shift) >= prefix inside the bucket, plus all higher buckets
-    for_each_element(row, eff, [&](float v, int pos) {
+    for_each_element(row, 0, eff, [&](float v, int pos) {
       const int bkt = bucket(v);
       if (bkt < thr_bin) return;
       const unsigned long long key = make_key(v, pos);
@@ -291,7 +404,7 @@ li_topk_kernel(TopkParams p) {
   }
 
   // ---- 5. order and write -------------------------------------------------------------------
-  if ((p.flags & PTO_LI_UNSORTED) == 0) {
+  if (!unsorted) {
     for (int j = k + tid; j < kpow2; j += kTopkThreads) sm->sel[j] = 0ull;
     bitonic_sort_desc(sm->sel, kpow2);
   }
@@ -300,12 +413,30 @@ li_topk_kernel(TopkParams p) {
 
 }  // namespace
 
-cudaError_t launch_li_topk(const TopkParams& p, cudaStream_t stream) {
+cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(li_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(TopkSmem)));
   if (e != cudaSuccess) return e;
-  li_topk_kernel<<<p.b * p.s1, kTopkThreads, sizeof(TopkSmem), stream>>>(p);
-  return cudaGetLastError();
+  // as many CTAs per row as keep the grid within one wave (portable cluster sizes: up to 8)
+  const int rows = p.b * p.s1;
+  int csize = 1;
+  while (csize < 8 && rows * csize * 2 <= num_sms) csize *= 2;
+  // ordered output ends in a 2048-key sort on rank 0 that dwarfs the scans of short rows: measured, a
+  // cluster only pays there for rows beyond ~40 K positions
+  if ((p.flags & PTO_LI_UNSORTED) == 0 && p.row_stride <= 40960) csize = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * csize), 1, 1);
+  cfg.blockDim = dim3(kTopkThreads, 1, 1);
+  cfg.dynamicSmemBytes = sizeof(TopkSmem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, li_topk_kernel, p);
 }
 
 int topk_max_k() { return kMaxK; }
