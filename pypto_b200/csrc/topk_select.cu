@@ -88,11 +88,11 @@ __device__ __forceinline__ int key_pos(unsigned long long key) {
   return static_cast<int>(~static_cast<unsigned int>(key & 0xffffffffull));
 }
 
-// descending bitonic sort of n (power of two) keys in shared memory; all threads of the CTA call it.
-// Pair t of a stage is handled by thread t (and t + blockDim, ...), so for strides below 64 warp w only
-// touches the 64-key blocks w, w + 32, ...: those stages need a warp barrier only, unless the previous
-// stage had a larger stride and other warps wrote into the block.
-__device__ void bitonic_sort_desc(unsigned long long* buf, int n) {
+// Descending bitonic sort of n (power of two) keys in shared memory; all threads of the CTA call it.
+// Shared-memory version: pair t of a stage is handled by thread t (and t + blockDim, ...), so for strides
+// below 64 warp w only touches the 64-key blocks w, w + 32, ...: those stages need a warp barrier only,
+// unless the previous stage had a larger stride and other warps wrote into the block.
+__device__ void bitonic_sort_desc_smem(unsigned long long* buf, int n) {
   __syncthreads();
   int prev_stride = 64;
   for (int size = 2; size <= n; size <<= 1) {
@@ -110,6 +110,67 @@ __device__ void bitonic_sort_desc(unsigned long long* buf, int n) {
         }
       }
     }
+  }
+  __syncthreads();
+}
+
+// Register version for n <= 2 * blockDim: thread t keeps keys 2t and 2t+1. Stride 1 is a compare inside
+// the thread, strides 2..32 exchange with lane (t ^ stride/2) by shuffle (a warp holds 64 consecutive
+// keys), and only strides >= 64 (15 of the 66 stages at n = 2048) go through shared memory and a block
+// barrier. Lanes beyond n/2 carry zeros and are never paired with a real key (i ^ stride < n).
+__device__ void bitonic_sort_desc(unsigned long long* buf, int n) {
+  if (n > 2 * static_cast<int>(blockDim.x) || n < 2) {
+    bitonic_sort_desc_smem(buf, n);
+    return;
+  }
+  __syncthreads();
+  const int t = threadIdx.x;
+  const int i0 = 2 * t;
+  const bool live = i0 < n;
+  unsigned long long e0 = live ? buf[i0] : 0ull, e1 = live ? buf[i0 + 1] : 0ull;
+  for (int size = 2; size <= n; size <<= 1) {
+    int stride = size >> 1;
+    if (stride >= 64) {
+      if (live) {
+        buf[i0] = e0;
+        buf[i0 + 1] = e1;
+      }
+      for (; stride >= 64; stride >>= 1) {
+        __syncthreads();
+        if (t < (n >> 1)) {
+          const int lo = 2 * t - (t & (stride - 1));
+          const int hi = lo + stride;
+          const bool desc = (lo & size) == 0;
+          const unsigned long long a = buf[lo], b = buf[hi];
+          if ((a < b) == desc) {
+            buf[lo] = b;
+            buf[hi] = a;
+          }
+        }
+      }
+      __syncthreads();
+      if (live) {
+        e0 = buf[i0];
+        e1 = buf[i0 + 1];
+      }
+    }
+    const bool desc = (i0 & size) == 0;  // the same for both keys of the thread (size >= 2)
+    for (; stride >= 2; stride >>= 1) {
+      const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, e0, stride >> 1);
+      const unsigned long long o1 = __shfl_xor_sync(0xffffffffu, e1, stride >> 1);
+      const bool keep_max = ((i0 & stride) == 0) == desc;
+      e0 = keep_max ? (e0 > o0 ? e0 : o0) : (e0 < o0 ? e0 : o0);
+      e1 = keep_max ? (e1 > o1 ? e1 : o1) : (e1 < o1 ? e1 : o1);
+    }
+    {
+      const unsigned long long hi = e0 > e1 ? e0 : e1, lo = e0 > e1 ? e1 : e0;
+      e0 = desc ? hi : lo;
+      e1 = desc ? lo : hi;
+    }
+  }
+  if (live) {
+    buf[i0] = e0;
+    buf[i0 + 1] = e1;
   }
   __syncthreads();
 }
