@@ -78,8 +78,10 @@ struct ClCtl {
   uint64_t xs_free[4][2];   // both softmax warps of the quarter have read that send slice             (2 arrivals)
   uint64_t xr_full[4];      // the peer's partials landed in receive slice q            (1 arming arrival + tx bytes)
   uint64_t xr_cons[4];      // both softmax warps of the quarter have read receive slice q             (2 arrivals)
-  uint64_t xr_free[4];      // the PEER has read what I copied into its receive slice q (1 remote arrival, forwarded
-                            // by the peer's exchange warp from its xr_cons)
+  uint64_t xr_free[4];      // the PEER has read what I copied into its receive slice q: 1 arming arrival + the 4 bytes
+                            // of an asynchronous remote store issued by the peer's exchange warp (a remote
+                            // mbarrier arrive blocks the issuing thread for ~1400 cycles; st.async does not)
+  uint32_t xr_sig[4];       // where those 4 bytes land
   uint64_t pair_bar[4];  // the two softmax warps of a lane quarter meet here (count 2), bounded like every wait
   uint32_t tmem_base;
   int abort;
@@ -111,9 +113,11 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// no ordering of this thread's earlier writes is needed (the peer only waits for reads to have happened)
-__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// asynchronous 4-byte store into the peer's shared memory that completes 4 tx bytes on the peer's mbarrier
+__device__ __forceinline__ void signal_peer_async(uint32_t dst_cluster, uint32_t value, uint32_t bar_cluster) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
+               ::"r"(dst_cluster), "r"(value), "r"(bar_cluster)
+               : "memory");
 }
 // Waits on barriers that a peer CTA completes (bulk-copy bytes, remote arrivals): polled with the
 // plain CTA-scope test like any other barrier - a cluster-scope acquire in the polling loop slows the
@@ -250,6 +254,7 @@ __device__ __forceinline__ void cl_role_exchange(const SfaParams& p, const ClCtx
   const uint32_t recv_peer = map_to_peer(x_base + 2 * kXBuf + quarter * kXSlice, peer);
   const uint32_t xr_full_peer = map_to_peer(smem_u32(&ctl->xr_full[quarter]), peer);
   const uint32_t xr_free_peer = map_to_peer(smem_u32(&ctl->xr_free[quarter]), peer);
+  const uint32_t xr_sig_peer = map_to_peer(smem_u32(&ctl->xr_sig[quarter]), peer);
   const int xsw = lane & 7;
   auto ready = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_test_wait(bar, parity)); };
   bool ok = true;
@@ -259,9 +264,9 @@ __device__ __forceinline__ void cl_role_exchange(const SfaParams& p, const ClCtx
     bool progressed = false;
     // ---- forward ----
     if (t_fwd < ntiles && ready(smem_u32(&ctl->xr_cons[quarter]), t_fwd & 1)) {
-      if (lane == 0) {
-        if (t_fwd + 1 < ntiles) mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[quarter]), kXSlice);  // for the next tile, then
-        mbar_arrive_remote_relaxed(xr_free_peer);  // the peer may overwrite the slice
+      if (lane == 0 && t_fwd + 1 < ntiles) {  // (nothing follows the last tile)
+        mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[quarter]), kXSlice);             // for the next tile, then
+        signal_peer_async(xr_sig_peer, static_cast<uint32_t>(t_fwd), xr_free_peer);  // the peer may overwrite the slice
       }
       ++t_fwd;
       progressed = true;
@@ -269,6 +274,7 @@ __device__ __forceinline__ void cl_role_exchange(const SfaParams& p, const ClCtx
     // ---- send ----
     if (t_send < t_out && (t_send == 0 || ready(smem_u32(&ctl->xr_free[quarter]), (t_send - 1) & 1))) {
       if (lane == 0) {
+        if (t_send >= 1 && t_send + 1 < ntiles) mbar_arrive_expect_tx(smem_u32(&ctl->xr_free[quarter]), 4);  // next signal
         asm volatile("fence.acquire.sync_restrict::shared::cluster.cluster;" ::: "memory");
         bulk_copy_to_peer(recv_peer, x_base + (t_send & 1) * kXBuf + quarter * kXSlice, kXSlice, xr_full_peer);
         bulk_commit();
@@ -744,6 +750,7 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
       mbar_init(smem_u32(&ctl->xr_cons[i]), 2);
       mbar_init(smem_u32(&ctl->xr_free[i]), 1);
       mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[i]), kXSlice);  // armed for tile 0
+      mbar_arrive_expect_tx(smem_u32(&ctl->xr_free[i]), 4);        // armed for the peer's first signal
       mbar_init(smem_u32(&ctl->pair_bar[i]), 2);
     }
     ctl->abort = 0;
