@@ -51,7 +51,7 @@ constexpr int kKRope = kCT * 64;
 constexpr int kKBuf = 4 * kKNopeChunk + kKRope;  // 36,864
 constexpr int kNK = 3;                           // K buffers
 constexpr int kXSlice = 32 * 256;                // 32 head rows x 64 fp32 partial scores
-constexpr int kXBuf = 4 * kXSlice;               // one area: two send areas, then the receive area
+constexpr int kXBuf = 4 * kXSlice;               // send area; two receive areas of the same size follow it
 constexpr int kClXWarps = 4;
 constexpr int kClSoftmaxWarp0 = 4;
 constexpr int kClSoftmaxWarps = 8;   // two warps per TMEM lane quarter: columns 0-31 and 32-63 of the tile
@@ -74,14 +74,10 @@ struct ClCtl {
   uint64_t s_free;       // exchange warps have copied the scores out           (count 4 warps)
   uint64_t pv_done;      // P.V of a tile complete: P may be overwritten, O is at rest (tcgen05.commit)
   uint64_t p_full;       // P written                                           (count 8 warps)
-  uint64_t xs_full[4][2];   // own partials of lane quarter q staged in send slice [q][tile parity]   (1 arrival)
-  uint64_t xs_free[4][2];   // both softmax warps of the quarter have read that send slice             (2 arrivals)
-  uint64_t xr_full[4];      // the peer's partials landed in receive slice q            (1 arming arrival + tx bytes)
-  uint64_t xr_cons[4];      // both softmax warps of the quarter have read receive slice q             (2 arrivals)
-  uint64_t xr_free[4];      // the PEER has read what I copied into its receive slice q: 1 arming arrival + the 4 bytes
-                            // of an asynchronous remote store issued by the peer's exchange warp (a remote
-                            // mbarrier arrive blocks the issuing thread for ~1400 cycles; st.async does not)
-  uint32_t xr_sig[4];       // where those 4 bytes land
+  uint64_t xs_full[4];      // own partials of lane quarter q staged in the send slice   (1 arrival)
+  uint64_t xs_free[4];      // both softmax warps of the quarter have read the send slice (2 arrivals)
+  uint64_t xr_full[4][2];   // the peer's partials landed in receive slice [q][tile parity] (1 arming arrival + tx bytes)
+  uint64_t xr_free[4][2];   // the PEER's two softmax warps have read what I copied into its slice [q][parity] (2 remote arrivals)
   uint64_t pair_bar[4];  // the two softmax warps of a lane quarter meet here (count 2), bounded like every wait
   uint32_t tmem_base;
   int abort;
@@ -113,11 +109,9 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// asynchronous 4-byte store into the peer's shared memory that completes 4 tx bytes on the peer's mbarrier
-__device__ __forceinline__ void signal_peer_async(uint32_t dst_cluster, uint32_t value, uint32_t bar_cluster) {
-  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
-               ::"r"(dst_cluster), "r"(value), "r"(bar_cluster)
-               : "memory");
+// no ordering of this thread's earlier writes is needed (the peer only waits for reads to have happened)
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Waits on barriers that a peer CTA completes (bulk-copy bytes, remote arrivals): polled with the
 // plain CTA-scope test like any other barrier - a cluster-scope acquire in the polling loop slows the
@@ -235,98 +229,66 @@ __device__ __forceinline__ void cl_role_mma(const SfaParams& p, const ClCtx c) {
 }
 
 // ================================ exchange ======================================================
-// Warp of lane quarter q, three steps per tile, each taken as soon as its condition holds:
-//   copy-out  partial scores TMEM -> send slice [q][tile parity] (scores complete; the slice's previous
-//             content, two tiles old, read by this CTA's softmax) - releases the score columns
-//   send      bulk copy of the slice into the peer's receive slice q (the peer has read the previous one)
-//   forward   this CTA's softmax has read receive slice q: re-arm its barrier and tell the peer
-// Two send slices let the q.K^T / copy-out loop run ahead of the softmax; the remote signalling lives
-// here so that no softmax thread waits on a remote operation.
-// A slice row is 16 units of 16 bytes, unit u stored at u ^ (lane & 7).
+// Warp of lane quarter q: partial scores of each tile, TMEM -> 8 KB send slice -> the peer CTA's
+// receive slice. A slice row is 16 units of 16 bytes, unit u stored at u ^ (lane & 7).
 __device__ __forceinline__ void cl_role_exchange(const SfaParams& p, const ClCtx c) {
   ClCtl* ctl = c.ctl;
   const uint32_t tmem_base = c.tmem_base, x_base = c.x_base, peer = c.peer;
   uint8_t* x_ptr = c.x_ptr;
   const int ntiles = c.ntiles;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int quarter = warp & 3;
-  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-  const uint32_t recv_peer = map_to_peer(x_base + 2 * kXBuf + quarter * kXSlice, peer);
-  const uint32_t xr_full_peer = map_to_peer(smem_u32(&ctl->xr_full[quarter]), peer);
-  const uint32_t xr_free_peer = map_to_peer(smem_u32(&ctl->xr_free[quarter]), peer);
-  const uint32_t xr_sig_peer = map_to_peer(smem_u32(&ctl->xr_sig[quarter]), peer);
-  const int xsw = lane & 7;
-  auto ready = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_test_wait(bar, parity)); };
-  bool ok = true;
-  int t_out = 0, t_send = 0, t_fwd = 0;
-  long long t_last = clock64();
-  while (t_fwd < ntiles || t_send < ntiles) {
-    bool progressed = false;
-    // ---- forward ----
-    if (t_fwd < ntiles && ready(smem_u32(&ctl->xr_cons[quarter]), t_fwd & 1)) {
-      if (lane == 0 && t_fwd + 1 < ntiles) {  // (nothing follows the last tile)
-        mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[quarter]), kXSlice);             // for the next tile, then
-        signal_peer_async(xr_sig_peer, static_cast<uint32_t>(t_fwd), xr_free_peer);  // the peer may overwrite the slice
-      }
-      ++t_fwd;
-      progressed = true;
-    }
-    // ---- send ----
-    if (t_send < t_out && (t_send == 0 || ready(smem_u32(&ctl->xr_free[quarter]), (t_send - 1) & 1))) {
-      if (lane == 0) {
-        if (t_send >= 1 && t_send + 1 < ntiles) mbar_arrive_expect_tx(smem_u32(&ctl->xr_free[quarter]), 4);  // next signal
-        asm volatile("fence.acquire.sync_restrict::shared::cluster.cluster;" ::: "memory");
-        bulk_copy_to_peer(recv_peer, x_base + (t_send & 1) * kXBuf + quarter * kXSlice, kXSlice, xr_full_peer);
-        bulk_commit();
-      }
-      if (warp == 1) TL(9, t_send);
-      ++t_send;
-      progressed = true;
-    }
-    // ---- copy-out ----
-    if (t_out < ntiles && ready(smem_u32(&ctl->s_full), t_out & 1) &&
-        (t_out < 2 || ready(smem_u32(&ctl->xs_free[quarter][t_out & 1]), ((t_out - 2) >> 1) & 1))) {
-      const int sb = t_out & 1;
-      // the copy that last read this slice (two tiles ago) is older than the most recent one
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    const int quarter = warp & 3;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint8_t* send_row = x_ptr + quarter * kXSlice + lane * 256;
+    const uint32_t send_slice = x_base + quarter * kXSlice;
+    const int xsw = lane & 7;
+    bool ok = true;
+    for (int t = 0; t < ntiles; ++t) {
+      // the scores are complete and this CTA's softmax warps have read the previous tile's send slice
+      ok = mbar_wait_warp(smem_u32(&ctl->s_full), t & 1);
+      if (ok && t >= 1) ok = mbar_wait_warp(smem_u32(&ctl->xs_free[quarter]), (t - 1) & 1);
+      if (!ok) break;
+      if (lane == 0) bulk_wait_read_all();  // the previous copy has finished reading the send slice
       __syncwarp();
-      if (warp == 1) TL(7, t_out);
+      if (warp == 1) TL(7, t);
       tc_fence_after();
-      uint8_t* send_row = x_ptr + sb * kXBuf + quarter * kXSlice + lane * 256;
 #pragma unroll 1
-      for (int g = 0; g < 4; ++g) {
-        uint32_t v[16];
-        tmem_ld_32x32b_x16(lane_addr + kClColS + 16 * g, v);
+      for (int g = 0; g < 2; ++g) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + kClColS + 32 * g, v);
         tc_wait_ld();
-        if (g == 3) {  // all 64 columns have left tensor memory: the next q.K^T may overwrite them
+        if (g == 1) {  // all 64 columns are in registers: the next q.K^T may overwrite them
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ctl->s_free));
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          *reinterpret_cast<uint4*>(send_row + (((4 * g + u) ^ xsw) << 4)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+        for (int u = 0; u < 8; ++u) {
+          *reinterpret_cast<uint4*>(send_row + (((8 * g + u) ^ xsw) << 4)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
         }
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->xs_full[quarter][sb]));  // own partials staged
-      if (warp == 1) TL(8, t_out);
-      ++t_out;
-      progressed = true;
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&ctl->xs_full[quarter]));    // own partials staged
+        if (warp == 1) TL(8, t);
+        // the peer has read what went into this receive slice two tiles ago
+        if (t >= 2) ok = mbar_wait_peer(smem_u32(&ctl->xr_free[quarter][t & 1]), ((t - 2) >> 1) & 1);
+        if (ok) {
+          bulk_copy_to_peer(map_to_peer(x_base + (1 + (t & 1)) * kXBuf + quarter * kXSlice, peer), send_slice, kXSlice,
+                            map_to_peer(smem_u32(&ctl->xr_full[quarter][t & 1]), peer));
+          bulk_commit();
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (warp == 1) TL(9, t);
     }
-    if (progressed) {
-      t_last = clock64();
-    } else if (clock64() - t_last > kWaitBudgetCycles) {
-      ok = false;
-      break;
+    if (lane == 0) bulk_wait_read_all();
+    if (!ok && lane == 0) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 44);
     }
-  }
-  if (lane == 0) bulk_wait_read_all();
-  if (!ok && lane == 0) {
-    ctl->abort = 1;
-    set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 44);
-  }
 }
 
 // ================================ softmax =======================================================
@@ -344,8 +306,8 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     // exchange slices of the lane quarter: own partials (send area) and the peer's (receive area);
     // a row is 16 units of 16 bytes, unit u stored at u ^ (lane & 7); this half reads units 8*half..+7
-    const uint8_t* send_row0 = x_ptr + quarter * kXSlice + lane * 256;  // + kXBuf for odd tiles
-    const uint8_t* recv_row = x_ptr + 2 * kXBuf + quarter * kXSlice + lane * 256;
+    const uint8_t* send_row = x_ptr + quarter * kXSlice + lane * 256;
+    const uint8_t* recv_row0 = x_ptr + kXBuf + quarter * kXSlice + lane * 256;  // + kXBuf for odd tiles
     const int xsw = lane & 7;
     float m_seen = -INFINITY;  // the row's reference max (identical in both halves)
     float l_run = 0.f;         // this half's share of the row sum
@@ -362,10 +324,10 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
       const int b = j & 1;
       const int kb = j % kNK;
       // ---- scores = own partials (staged by an exchange warp) + the peer CTA's ----------------------
-      ok = mbar_wait_warp(smem_u32(&ctl->xs_full[quarter][b]), (j >> 1) & 1) &&
-           mbar_wait_peer_warp(smem_u32(&ctl->xr_full[quarter]), j & 1);
+      ok = mbar_wait_warp(smem_u32(&ctl->xs_full[quarter]), j & 1) &&
+           mbar_wait_peer_warp(smem_u32(&ctl->xr_full[quarter][b]), (j >> 1) & 1);
       if (!ok) break;
-      const uint8_t* send_row = send_row0 + b * kXBuf;
+      const uint8_t* recv_row = recv_row0 + b * kXBuf;
       if (tid == 32 * kClSoftmaxWarp0) TL(10, j);
       float s[32];
 #pragma unroll
@@ -385,10 +347,7 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
         s[4 * u + 3] += o.w;
       }
       __syncwarp();
-      if (lane == 31) {  // both slices may be refilled (the exchange warp passes the second on to the peer)
-        mbar_arrive(smem_u32(&ctl->xs_free[quarter][b]));
-        mbar_arrive(smem_u32(&ctl->xr_cons[quarter]));
-      }
+      if (lane == 31) mbar_arrive(smem_u32(&ctl->xs_free[quarter]));  // the send slice may be refilled
       if (tid == 32 * kClSoftmaxWarp0) TL(11, j);
       // ---- scale, mask, max of this half ------------------------------------------------------------
       // (k_valid was written before the producers' arrival on k_full, which the MMA thread observed before
@@ -470,6 +429,12 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
       if (tid == 32 * kClSoftmaxWarp0) TL(15, j);
+      if (lane == 31) {
+        // off the chain: arm this receive slice for the tile after next, then tell the peer that what it
+        // copied into the slice has been read (it needs to know only two tiles from now)
+        if (half == 0) mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[quarter][b]), kXSlice);
+        mbar_arrive_remote_relaxed(map_to_peer(smem_u32(&ctl->xr_free[quarter][b]), peer));
+      }
     }
     // ---- output: row sum = both halves' shares; each half stores 128 of the CTA's 256 columns ---------
     if (tid == 32 * kClSoftmaxWarp0) TLM(4);
@@ -742,15 +707,13 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
     mbar_init(smem_u32(&ctl->pv_done), 1);
     mbar_init(smem_u32(&ctl->p_full), kClSoftmaxWarps);
     for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&ctl->xs_full[i]), 1);
+      mbar_init(smem_u32(&ctl->xs_free[i]), 2);
       for (int b = 0; b < 2; ++b) {
-        mbar_init(smem_u32(&ctl->xs_full[i][b]), 1);
-        mbar_init(smem_u32(&ctl->xs_free[i][b]), 2);
+        mbar_init(smem_u32(&ctl->xr_full[i][b]), 1);
+        mbar_init(smem_u32(&ctl->xr_free[i][b]), 2);
+        mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[i][b]), kXSlice);  // armed for tiles 0 and 1
       }
-      mbar_init(smem_u32(&ctl->xr_full[i]), 1);
-      mbar_init(smem_u32(&ctl->xr_cons[i]), 2);
-      mbar_init(smem_u32(&ctl->xr_free[i]), 1);
-      mbar_arrive_expect_tx(smem_u32(&ctl->xr_full[i]), kXSlice);  // armed for tile 0
-      mbar_arrive_expect_tx(smem_u32(&ctl->xr_free[i]), 4);        // armed for the peer's first signal
       mbar_init(smem_u32(&ctl->pair_bar[i]), 2);
     }
     ctl->abort = 0;
