@@ -131,6 +131,9 @@ def test_topk_stage_exact_on_kernel_scores():
         want = torch.topk(key, k).indices
         assert set(out[r, 0, :k].tolist()) == set(want.tolist()), f"row {r}"
         assert torch.all(out[r, 0, k:] == -1)
+        # value-descending, ties toward the smaller position (rows this long are scanned by a cluster of CTAs)
+        got_keys = key[out[r, 0, :k].long()]
+        assert torch.all(got_keys[:-1] >= got_keys[1:]), f"row {r} not ordered"
     # unsorted variant selects the same sets
     out2 = torch.zeros_like(out, device=DEV)
     pto.lightning_indexer_topk(sc.to(DEV), act.to(DEV), out2, s1=1, selected_count=2048, sort=False)
