@@ -13,6 +13,8 @@ _OPS = (
 
 
 def __getattr__(name):
+    if name == "CapturedCall":
+        return importlib.import_module(".graph", __name__).CapturedCall
     # operators resolve lazily so that `pypto_b200.inputs` / `pypto_b200.build` import before the library is built
     if name in _OPS:
         return getattr(importlib.import_module(".ops", __name__), name)
