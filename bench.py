@@ -173,6 +173,10 @@ def run_stage(args, dev):
     out = torch.zeros((d.b, d.s1, 128, 512), dtype=torch.bfloat16, device=dev)
     sc = torch.randn((t, d.max_blocks * 128), dtype=torch.float32, device=dev)
     li = (d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale, d.idx_weight, d.act_seq_key, d.block_table)
+    kn_bf16 = None
+    if args.stage == "sfa_bf16":  # the non-quantised latent cache holding the values the int8 one dequantises to
+        kn_bf16 = (d.key_nope_2d.to(torch.float32).reshape(-1, 4, 128) * d.k_nope_scales.reshape(-1, 4, 1)
+                   ).reshape(-1, 512).to(torch.bfloat16)
     fns = {
         "li_score": lambda: pto.lightning_indexer_scores(*li, sc),
         "li_decode": lambda: pto.lightning_indexer_decode(*li, idx, None, None, 2048),
@@ -180,6 +184,10 @@ def run_stage(args, dev):
         "sfa": lambda: pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d,
                                                           d.k_nope_scales, d.topk_indices, d.block_table,
                                                           d.act_seq_key, out, 128, 1, SCALE, 2048, 128, d.max_blocks),
+        "sfa_bf16": lambda: pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, kn_bf16, d.key_rope_2d,
+                                                               d.k_nope_scales, d.topk_indices, d.block_table,
+                                                               d.act_seq_key, out, 128, 1, SCALE, 2048, 128,
+                                                               d.max_blocks),
         "fused": lambda: pto.decode_indexer_attention_quant(*li[:5], d.query_nope, d.query_rope, d.key_nope_2d,
                                                             d.key_rope_2d, d.k_nope_scales, d.act_seq_key,
                                                             d.block_table, idx, out),
@@ -209,7 +217,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
-    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "fused"],
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

@@ -153,6 +153,17 @@ int pto_sfa_quant(const void* query_nope, const void* query_rope, const int8_t* 
                   int64_t n_rows, int max_blocks, int nq_total, int head_begin,
                   void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
+/* Non-quantised latent cache: the same operator called with a bf16 `key_nope_2d` [n_rows, 512]
+ * (sparse_flash_attention_quant_impl.py:149-153 and :199-202 take the rows as they are when the dtype
+ * is not int8; golden deepseekv32_sparse_flash_attention_quant.py:216-221 with is_kn_quant = 0). No
+ * scales. Only nq == 128 (all heads of a token); other widths return PTO_ERR_UNSUPPORTED. */
+int pto_sfa_bf16(const void* query_nope, const void* query_rope, const void* key_nope_2d,
+                 const void* key_rope_2d, const int32_t* topk_indices, const int32_t* block_table,
+                 const int32_t* kv_act_seqs, void* attention_out, int b, int s1, int nq, int n_kv,
+                 float softmax_scale, int topk, int block_size, int64_t n_rows, int max_blocks,
+                 int nq_total, int head_begin, void* workspace, size_t workspace_bytes,
+                 pto_stream_t stream);
+
 /* Packed-row variant. Replaces `sparse_attention_antiquant_d/_p`
  * (examples/models/deepseek_v32_exp/sparse_attention_antiquant_impl.py:246-358; golden
  * deepseekv32_sparse_attention_antiquant.py:49-136). nope_cache: int8 [n_rows, 656] =

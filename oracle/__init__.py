@@ -9,5 +9,6 @@ reference's own golden functions, produced by importing the reference's example 
 tests/golden/make_golden.py and committed under tests/golden/.
 """
 from .li_oracle import li_scores, li_topk, lightning_indexer  # noqa: F401
-from .sfa_oracle import sparse_attention, sparse_attention_online, sparse_attention_packed  # noqa: F401
+from .sfa_oracle import (dequantised_cache, sparse_attention, sparse_attention_online,  # noqa: F401
+                         sparse_attention_packed)
 from .compare import attention_errors, topk_set_diff  # noqa: F401

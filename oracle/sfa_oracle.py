@@ -7,6 +7,7 @@ example asserts against (:375):
   n   = clamp(S_b - s1 + 1 + i, 0, topk)                                   (:197)
   r_j = block_table[b, idx_j // bs] * bs + idx_j % bs   for the first n indices  (:213-217)
   kn  = bf16( fp32(int8 row) * scale[r, c // 128] )                         (:226-230)
+        (a bf16 `key_nope_2d` is the golden's is_kn_quant = 0 branch, :231-232: kn = the row itself)
   s   = ( fp32(q) @ fp32([kn | kr]).T ) * softmax_scale                     (:238-240)
   P   = bf16( exp(s - max) / sum )                                          (:241-245)
   O   = bf16( fp32(P) @ fp32(kn) )                                          (:246, :248)
@@ -24,6 +25,12 @@ import torch
 def _physical_rows(idx_row, table_row, n, block_size):
     idx = idx_row[:n].long()
     return table_row[idx // block_size].long() * block_size + idx % block_size
+
+
+def _latent_rows(key_nope_2d, k_nope_scales, rows):
+    if key_nope_2d.dtype == torch.bfloat16:  # non-quantised cache: rows are used as they are (:231-232)
+        return key_nope_2d[rows]
+    return _dequant(key_nope_2d[rows], k_nope_scales[rows])
 
 
 def _dequant(kn_rows_i8, scales):
@@ -50,7 +57,7 @@ def sparse_attention(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_sc
         if n == 0:
             continue
         rows = _physical_rows(topk_indices[ti], block_table[bi], n, block_size)
-        kn = _dequant(key_nope_2d[rows], k_nope_scales[rows])
+        kn = _latent_rows(key_nope_2d, k_nope_scales, rows)
         k = torch.cat([kn, key_rope_2d[rows]], dim=-1).to(torch.float32)
         q = torch.cat([qn[ti], qr[ti]], dim=-1).to(torch.float32)
         s = (q @ k.T) * softmax_scale
@@ -75,7 +82,7 @@ def sparse_attention_online(query_nope, query_rope, key_nope_2d, key_rope_2d, k_
         if n == 0:
             continue
         rows = _physical_rows(topk_indices[ti], block_table[bi], n, block_size)
-        kn = _dequant(key_nope_2d[rows], k_nope_scales[rows])
+        kn = _latent_rows(key_nope_2d, k_nope_scales, rows)
         k = torch.cat([kn, key_rope_2d[rows]], dim=-1).to(torch.float32)
         q = torch.cat([qn[ti], qr[ti]], dim=-1).to(torch.float32)
         m = torch.full((nq, 1), float("-inf"))
@@ -91,6 +98,11 @@ def sparse_attention_online(query_nope, query_rope, key_nope_2d, key_rope_2d, k_
             m = m_new
         out[bi, i] = (o / l).to(torch.bfloat16)
     return out
+
+
+def dequantised_cache(key_nope_2d, k_nope_scales):
+    """The bf16 latent cache that holds exactly the values the int8 cache dequantises to."""
+    return _dequant(key_nope_2d, k_nope_scales)
 
 
 def unpack_kv_rows(nope_cache):

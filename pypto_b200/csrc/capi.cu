@@ -212,12 +212,16 @@ int run_li_topk(const float* scores, int64_t row_stride, const int32_t* act, int
   return PTO_OK;
 }
 
-int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, const float* sc, int packed,
+// `layout`: how the latent cache is stored
+enum { kSfaSplitInt8 = 0, kSfaPackedInt8 = 1, kSfaSplitBf16 = 2 };
+
+int run_sfa(const void* qn, const void* qr, const void* kn, const void* kr, const float* sc, int layout,
             const int32_t* topk_idx, const int32_t* bt, const int32_t* act, void* out, int b, int s1, int nq, int n_kv,
             float softmax_scale, int topk, int block_size, int64_t n_rows, int max_blocks, int nq_total, int head_begin,
             uint8_t* part_base, size_t part_bytes, int32_t* status, cudaStream_t stream) {
   PTO_REQUIRE(qn && qr && kn && topk_idx && bt && act && out, "null tensor pointer");
-  PTO_REQUIRE(packed || (kr && sc), "null tensor pointer");
+  const bool packed = layout == kSfaPackedInt8, bf16 = layout == kSfaSplitBf16;
+  PTO_REQUIRE(packed || (kr && (sc || bf16)), "null tensor pointer");
   PTO_REQUIRE(n_kv == 1, "n_kv %d: only 1 (MLA latent cache)", n_kv);
   PTO_REQUIRE(b >= 1 && s1 >= 1, "b %d / s1 %d", b, s1);
   PTO_REQUIRE(nq >= 1 && nq % 16 == 0, "nq %d must be a positive multiple of 16", nq);
@@ -225,8 +229,12 @@ int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, co
               head_begin + nq, nq_total);
   PTO_REQUIRE(topk >= 1 && block_size >= 1 && max_blocks >= 1 && n_rows >= 1, "topk/block_size/max_blocks/n_rows");
   PTO_REQUIRE(softmax_scale > 0.f, "softmax_scale %f", softmax_scale);
-  PTO_REQUIRE(aligned16(qn) && aligned16(qr) && aligned16(kn) && aligned16(out) && (packed || (aligned16(kr) && aligned16(sc))),
+  PTO_REQUIRE(aligned16(qn) && aligned16(qr) && aligned16(kn) && aligned16(out) &&
+                  (packed || (aligned16(kr) && (bf16 || aligned16(sc)))),
               "attention tensors must be 16-byte aligned");
+  if (bf16 && nq != 128) {
+    return fail(PTO_ERR_UNSUPPORTED, "bf16 latent cache: nq %d, only all 128 heads of a token are supported", nq);
+  }
   DeviceInfo di;
   int rc = get_device_info(&di);
   if (rc != PTO_OK) return rc;
@@ -236,7 +244,7 @@ int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, co
   pto::SfaParams p{};
   p.q_nope = reinterpret_cast<const __nv_bfloat16*>(qn);
   p.q_rope = reinterpret_cast<const __nv_bfloat16*>(qr);
-  p.kn = kn;
+  p.kn = reinterpret_cast<const int8_t*>(kn);
   p.kr = reinterpret_cast<const __nv_bfloat16*>(kr);
   p.kn_scales = sc;
   p.topk = topk_idx;
@@ -257,7 +265,8 @@ int run_sfa(const void* qn, const void* qr, const int8_t* kn, const void* kr, co
   p.block_size = block_size;
   p.max_blocks = max_blocks;
   p.n_split = ns;
-  p.packed = packed;
+  p.packed = packed ? 1 : 0;
+  p.kn_bf16 = bf16 ? 1 : 0;
   p.n_rows = n_rows;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
@@ -428,6 +437,19 @@ int pto_sfa_quant(const void* query_nope, const void* query_rope, const int8_t* 
   int rc = check_workspace(workspace, workspace_bytes, kStatusBytes);
   if (rc != PTO_OK) return rc;
   return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, 0, topk_indices, block_table,
+                 kv_act_seqs, attention_out, b, s1, nq, n_kv, softmax_scale, topk, block_size, n_rows, max_blocks,
+                 nq_total, head_begin, reinterpret_cast<uint8_t*>(workspace) + kStatusBytes,
+                 workspace_bytes - kStatusBytes, reinterpret_cast<int32_t*>(workspace), stream);
+}
+
+int pto_sfa_bf16(const void* query_nope, const void* query_rope, const void* key_nope_2d, const void* key_rope_2d,
+                 const int32_t* topk_indices, const int32_t* block_table, const int32_t* kv_act_seqs,
+                 void* attention_out, int b, int s1, int nq, int n_kv, float softmax_scale, int topk, int block_size,
+                 int64_t n_rows, int max_blocks, int nq_total, int head_begin, void* workspace,
+                 size_t workspace_bytes, pto_stream_t stream) {
+  int rc = check_workspace(workspace, workspace_bytes, kStatusBytes);
+  if (rc != PTO_OK) return rc;
+  return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, nullptr, kSfaSplitBf16, topk_indices, block_table,
                  kv_act_seqs, attention_out, b, s1, nq, n_kv, softmax_scale, topk, block_size, n_rows, max_blocks,
                  nq_total, head_begin, reinterpret_cast<uint8_t*>(workspace) + kStatusBytes,
                  workspace_bytes - kStatusBytes, reinterpret_cast<int32_t*>(workspace), stream);

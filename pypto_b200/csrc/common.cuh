@@ -284,16 +284,16 @@ struct TopkParams {
 struct SfaParams {
   const __nv_bfloat16* q_nope;  // [t*nq_total, 512]
   const __nv_bfloat16* q_rope;  // [t*nq_total, 64]
-  const int8_t* kn;             // [n_rows, 512]   (or packed rows when packed != 0)
+  const int8_t* kn;             // [n_rows, 512]   (packed rows when packed != 0; bf16 [n_rows, 512] when kn_bf16 != 0)
   const __nv_bfloat16* kr;      // [n_rows, 64]
-  const float* kn_scales;       // [n_rows, 4]
+  const float* kn_scales;       // [n_rows, 4]     (unused when kn_bf16 != 0)
   const int32_t* topk;          // [t, topk]
   const int32_t* block_table;   // [b, max_blocks]
   const int32_t* act_seq;       // [b]
   __nv_bfloat16* out;           // [t, nq_total, 512]
   float* part_o;                // [t, n_split, nq, 512]
   float* part_ml;               // [t, n_split, nq, 2]
-  int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed;
+  int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed, kn_bf16;
   int64_t n_rows;
   float scale_log2;  // softmax_scale * log2(e)
   int32_t* status;

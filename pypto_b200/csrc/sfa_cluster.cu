@@ -137,10 +137,17 @@ struct ClCtx {
 };
 
 // One 128-byte line of a selected row per thread of the row's four (q = 0..3): two lines of this CTA's
-// latent half, the rope half, the scales.
+// latent half, the rope half, the scales. With a bf16 latent cache the half is four lines, one per thread,
+// and thread 0 also takes the rope half (there are no scales).
+template <bool kBf16>
 __device__ __forceinline__ void cl_prefetch_row(const SfaParams& p, long long phys, uint32_t crank, int q) {
   if (phys < 0) return;
   const uint8_t* kn_bytes = reinterpret_cast<const uint8_t*>(p.kn);
+  if (kBf16) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kn_bytes + phys * 1024 + crank * 512 + q * 128));
+    if (q == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(p.kr) + phys * 128 + crank * 64));
+    return;
+  }
   const uint8_t* a;
   if (q < 2) {
     a = (p.packed ? kn_bytes + phys * 656 : kn_bytes + phys * 512) + crank * 256 + q * 128;
@@ -531,6 +538,11 @@ __device__ __forceinline__ void cl_role_softmax(const SfaParams& p, const ClCtx 
 // branched on before it has had a tile's time to arrive: the selected index four tiles ahead, its
 // block-table entry three tiles ahead, an L2 prefetch of the row two tiles ahead, the row itself one
 // tile ahead (into the registers the current tile has just been dequantised out of).
+// kBf16: the latent cache already holds bf16 (the operator's non-quantised key_nope_2d); thread (row, q)
+// then owns bf16 units 2q and 2q+1 of each of the half's four 64-dim chunks. Nothing has to pass through
+// registers: once the K buffer is free the nine 16-byte pieces go from L2 (the row was prefetched two
+// tiles ago) to their swizzled places with `cp.async`, zero-filled for a padding row.
+template <bool kBf16>
 __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx c) {
   ClCtl* ctl = c.ctl;
   uint8_t* k_ptr = c.k_ptr;
@@ -545,9 +557,10 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
   const uint8_t* kr_bytes = reinterpret_cast<const uint8_t*>(p.kr);
   const uint8_t* sc_bytes = reinterpret_cast<const uint8_t*>(p.kn_scales);
   struct RowRegs {
-    uint4 d[4];
+    uint4 d[kBf16 ? 1 : 4];
     uint4 r;
     float2 sc;
+    long long phys;  // kBf16 only: the row to copy
     bool valid;
   };
   auto load_idx = [&](int j) -> int {
@@ -557,6 +570,10 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
   auto issue_loads = [&](RowRegs& r, long long phys) {
     r.valid = phys >= 0;
     if (!r.valid) return;
+    if (kBf16) {
+      r.phys = phys;
+      return;
+    }
     const uint8_t* nope = p.packed ? kn_bytes + phys * 656 : kn_bytes + phys * 512;
     const uint8_t* rope = p.packed ? kn_bytes + phys * 656 + 512 : kr_bytes + phys * 128;
     const uint8_t* scl = p.packed ? kn_bytes + phys * 656 + 640 : sc_bytes + phys * 16;
@@ -565,7 +582,7 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
     r.r = ldg_pinned_v4(rope + crank * 64 + q * 16);
     r.sc = ldg_pinned_v2f(scl + crank * 8);
   };
-  auto prefetch_row = [&](long long phys) { cl_prefetch_row(p, phys, crank, q); };
+  auto prefetch_row = [&](long long phys) { cl_prefetch_row<kBf16>(p, phys, crank, q); };
   const int sw = row & 7;
   const int rsw = (row >> 1) & 3;
   bool ok = true;
@@ -596,14 +613,28 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
     // (a spilled register costs a trip to L2 here: the L1 left beside 219 KB of shared memory is tiny)
     uint8_t* kbuf = k_ptr + kb * kKBuf;
     const bool valid = ra.valid;
+    if (kBf16) {
+      const uint32_t kaddr = c.k_base + kb * kKBuf;
+      const uint32_t nbytes = valid ? 16u : 0u;  // 0: the 16 bytes are written as zeros, nothing is read
+      const uint8_t* nope = kn_bytes + (valid ? ra.phys : 0) * 1024 + crank * 512 + q * 32;
+      const uint8_t* rope = kr_bytes + (valid ? ra.phys : 0) * 128 + crank * 64 + q * 16;
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {  // latent unit q + 4m of the half: chunk m, bf16 units 2q, 2q+1
-      uint4 c0 = make_uint4(0, 0, 0, 0), c1 = make_uint4(0, 0, 0, 0);
-      if (valid) dequant16(ra.d[m], (m < 2) ? ra.sc.x : ra.sc.y, c0, c1);
-      *reinterpret_cast<uint4*>(kbuf + m * kKNopeChunk + row * 128 + (((2 * q) ^ sw) << 4)) = c0;
-      *reinterpret_cast<uint4*>(kbuf + m * kKNopeChunk + row * 128 + (((2 * q + 1) ^ sw) << 4)) = c1;
+      for (int m = 0; m < 4; ++m) {
+        cp_async_16(kaddr + m * kKNopeChunk + row * 128 + (((2 * q) ^ sw) << 4), nope + m * 128, nbytes);
+        cp_async_16(kaddr + m * kKNopeChunk + row * 128 + (((2 * q + 1) ^ sw) << 4), nope + m * 128 + 16, nbytes);
+      }
+      cp_async_16(kaddr + 4 * kKNopeChunk + row * 64 + ((q ^ rsw) << 4), rope, nbytes);
+      asm volatile("cp.async.wait_all;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {  // latent unit q + 4m of the half: chunk m, bf16 units 2q, 2q+1
+        uint4 c0 = make_uint4(0, 0, 0, 0), c1 = make_uint4(0, 0, 0, 0);
+        if (valid) dequant16(ra.d[m], (m < 2) ? ra.sc.x : ra.sc.y, c0, c1);
+        *reinterpret_cast<uint4*>(kbuf + m * kKNopeChunk + row * 128 + (((2 * q) ^ sw) << 4)) = c0;
+        *reinterpret_cast<uint4*>(kbuf + m * kKNopeChunk + row * 128 + (((2 * q + 1) ^ sw) << 4)) = c1;
+      }
+      *reinterpret_cast<uint4*>(kbuf + 4 * kKNopeChunk + row * 64 + ((q ^ rsw) << 4)) = valid ? ra.r : make_uint4(0, 0, 0, 0);
     }
-    *reinterpret_cast<uint4*>(kbuf + 4 * kKNopeChunk + row * 64 + ((q ^ rsw) << 4)) = valid ? ra.r : make_uint4(0, 0, 0, 0);
     if (q == 0) ctl->k_valid[kb][row] = valid ? 1 : 0;
     fence_proxy_async();
     __syncwarp();
@@ -627,6 +658,7 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
 
 // 21 warps: six share one scheduler partition and 6 x 32 x 80 registers fit its file; bounds of 768 threads
 // make the compiler start from 80 registers without capping the regions that raise their share
+template <bool kBf16>
 __global__ void __launch_bounds__(768, 1)
 sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
   // the swizzled operand tiles need a 1024-byte aligned base: the kernel has no static shared memory,
@@ -787,7 +819,7 @@ sfa_cluster_kernel(const __grid_constant__ SfaParams p) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 88;");
     cl_role_softmax(p, c);
   } else if (warp < kClLastXWarp) {
-    cl_role_producer(p, c);
+    cl_role_producer<kBf16>(p, c);
   } else {
     cl_role_exchange(p, c);
   }
@@ -817,7 +849,9 @@ extern "C" int pto_debug_sfa_timeline(long long* host, int n) {
 #endif
 
 cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(sfa_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  // two instances of one kernel: int8 latent rows dequantised by the producers, or bf16 rows copied as they are
+  void (*kernel)(SfaParams) = p.kn_bf16 ? sfa_cluster_kernel<true> : sfa_cluster_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kClSmemBytes));
   if (e != cudaSuccess) return e;
   const int t = p.b * p.s1;
@@ -833,7 +867,7 @@ cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, sfa_cluster_kernel, p);
+  return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
 }  // namespace pto

@@ -137,6 +137,11 @@ __device__ __forceinline__ int ldg_pinned_i32(const void* p) {
   return v;
 }
 
+// 16 bytes global -> shared without a register in between (L2 only); `src_bytes` 0 writes zeros
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+
 // The same lookup in two steps, so that a caller can fetch the block-table entry a tile ahead and
 // only branch on it once it has arrived.
 constexpr int kTableSkip = INT_MIN;  // nothing to fetch: padding index, or an index already reported

@@ -210,31 +210,42 @@ def _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_
                                                  attention_out, nq, n_kv, topk)
     kn = unwrap(key_nope_2d, "key_nope_2d")
     kr = unwrap(key_rope_2d, "key_rope_2d")
-    sc = unwrap(k_nope_scales, "k_nope_scales")
-    _need(kn.dtype == torch.int8 and kn.dim() == 2 and kn.shape[1] == 512,
-          "key_nope_2d: int8 [block_num*block_size, 512] (the quantized cache)")
+    _need(kn.dtype in (torch.int8, torch.bfloat16) and kn.dim() == 2 and kn.shape[1] == 512,
+          "key_nope_2d: int8 (quantized cache) or bfloat16 [block_num*block_size, 512]")
     n_rows = kn.shape[0]
     _need(kr.dtype == torch.bfloat16 and tuple(kr.shape) == (n_rows, 64), "key_rope_2d: bfloat16 [rows, 64]")
-    _need(sc.dtype == torch.float32 and tuple(sc.shape) == (n_rows, 4), "k_nope_scales: float32 [rows, 4]")
     _need(bt.shape[1] >= int(max_blocknum_perbatch), "block_table narrower than max_blocknum_perbatch")
     _need(int(nq) % 16 == 0, "nq must be a multiple of 16")
-    dev = _same_device([qn, qr, kn, kr, sc, ti, bt, act, out])
     lib = _lib.load()
     nbytes = lib.pto_sfa_workspace_bytes(t, int(nq))
+    tail = (b, t // b, int(nq), int(n_kv), float(softmax_scale), int(topk), int(block_size), n_rows, bt.shape[1],
+            int(nq), 0)
+    if kn.dtype == torch.bfloat16:
+        # the reference takes the latent rows as they are when the cache is not int8
+        # (sparse_flash_attention_quant_impl.py:149-153, :199-202); the scales are not read
+        dev = _same_device([qn, qr, kn, kr, ti, bt, act, out])
+        with torch.cuda.device(dev):
+            ws = _workspace(dev, nbytes)
+            _lib.check(lib.pto_sfa_bf16(qn.data_ptr(), qr.data_ptr(), kn.data_ptr(), kr.data_ptr(), ti.data_ptr(),
+                                        bt.data_ptr(), act.data_ptr(), out.data_ptr(), *tail, ws.data_ptr(),
+                                        ws.numel(), torch.cuda.current_stream(dev).cuda_stream))
+        return None
+    sc = unwrap(k_nope_scales, "k_nope_scales")
+    _need(sc.dtype == torch.float32 and tuple(sc.shape) == (n_rows, 4), "k_nope_scales: float32 [rows, 4]")
+    dev = _same_device([qn, qr, kn, kr, sc, ti, bt, act, out])
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         _lib.check(lib.pto_sfa_quant(qn.data_ptr(), qr.data_ptr(), kn.data_ptr(), kr.data_ptr(), sc.data_ptr(),
-                                     ti.data_ptr(), bt.data_ptr(), act.data_ptr(), out.data_ptr(), b, t // b, int(nq),
-                                     int(n_kv), float(softmax_scale), int(topk), int(block_size), n_rows, bt.shape[1],
-                                     int(nq), 0, ws.data_ptr(), ws.numel(),
-                                     torch.cuda.current_stream(dev).cuda_stream))
+                                     ti.data_ptr(), bt.data_ptr(), act.data_ptr(), out.data_ptr(), *tail,
+                                     ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream))
     return None
 
 
 def sparse_flash_attention_quant_d(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
                                    block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
                                    max_blocknum_perbatch, tile_config=None):
-    """Decode entry: attention_out[b, s1, nq, 512] over the selected int8 latent + bf16 rope rows."""
+    """Decode entry: attention_out[b, s1, nq, 512] over the selected int8 latent + bf16 rope rows
+    (or bf16 latent rows: a bfloat16 `key_nope_2d` selects the non-quantised branch, nq = 128 only)."""
     return _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales,
                                          topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv,
                                          softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config)

@@ -139,6 +139,12 @@ def make_sfa(sfa_mod, aq_mod, name, act_seq, s1):
     params = [128, scale, 2048, 512, 1]
     out_nf, _ = sfa_mod.compute_attention_no_flash(data, params, 2048)
     out_fl, _ = sfa_mod.compute_attention(data, params, 2048)
+    # non-quantised branch (is_kn_quant = 0) over the bf16 cache holding the dequantised values
+    kn_bf16 = (d.key_nope_2d.to(torch.float32).reshape(-1, 4, 128) * d.k_nope_scales.reshape(-1, 4, 1)
+               ).reshape(-1, 512).to(torch.bfloat16)
+    out_bf, _ = sfa_mod.compute_attention_no_flash(
+        [q, kn_bf16, d.key_rope_2d, d.k_nope_scales, d.topk_indices, d.block_table, list(act_seq)],
+        [128, scale, 2048, 512, 0], 2048)
     packed = gen.pack_kv_rows(d.key_nope_2d, d.key_rope_2d, d.k_nope_scales)
     out_aq, _ = aq_mod.compute_attention_aq(
         [d.query_nope, d.query_rope, packed, d.topk_indices, d.block_table, list(act_seq)],
@@ -151,6 +157,7 @@ def make_sfa(sfa_mod, aq_mod, name, act_seq, s1):
         # the packed-row golden and the single-tile online golden are stored as digests plus one head
         out_packed_sha=sha(out_aq), out_packed_equals_no_flash=bool(torch.equal(out_aq, out_nf)),
         out_flash_sha=sha(out_fl), out_flash_head0=as_np(out_fl[:, :, 0, :]),
+        out_bf16_sha=sha(out_bf), out_bf16_equals_no_flash=bool(torch.equal(out_bf, out_nf)),
     )
     print(name, "t", d.t, "rows", d.block_num * 128)
 

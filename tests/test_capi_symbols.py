@@ -25,7 +25,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
-    for must in ("pto_li_decode", "pto_li_scores", "pto_li_topk", "pto_sfa_quant", "pto_sfa_packed",
+    for must in ("pto_li_decode", "pto_li_scores", "pto_li_topk", "pto_sfa_quant", "pto_sfa_bf16", "pto_sfa_packed",
                  "pto_decode_fused", "pto_li_decode_static", "pto_workspace_status"):
         assert must in names
 

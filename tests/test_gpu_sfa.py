@@ -14,8 +14,11 @@ MAX_ABS, REL_L2 = 2e-2, 5e-3
 SCALE = 576 ** -0.5
 
 
-def _run(d, packed=False, prefill=False, nq=128):
+def _run(d, packed=False, prefill=False, nq=128, bf16_cache=False):
     g = d.to(DEV)
+    if bf16_cache:  # the non-quantised branch: the cache holds the values the int8 rows dequantise to
+        g.key_nope_2d = oracle.dequantised_cache(d.key_nope_2d, d.k_nope_scales).to(DEV)
+        g.k_nope_scales = torch.zeros(1, 4, device=DEV)  # not read
     out = torch.full((d.b, d.s1, nq, 512), 7.0, dtype=torch.bfloat16, device=DEV)
     cfg = pto.SaTileShapeConfig()
     if packed:
@@ -95,3 +98,42 @@ def test_order_of_indices_does_not_matter_beyond_rounding():
     d.topk_indices = d.topk_indices.flip(-1).contiguous()
     b = _run(d)
     _check(a, b)
+
+
+@pytest.mark.parametrize("name", SFA_CASES)
+def test_bf16_cache_matches_reference_fixture(name):
+    """Non-quantised `key_nope_2d` (the golden's is_kn_quant = 0): the reference's output over the bf16
+    cache of dequantised values is the fixture's `out_no_flash` itself."""
+    d, z = load_case(name)
+    assert bool(z["out_bf16_equals_no_flash"])
+    want = mask_empty_rows(from_np_bf16(z["out_no_flash"]).reshape(d.b, d.s1, 128, 512), d)
+    got = _run(d, bf16_cache=True)
+    _check(got, want)
+    for bi in range(d.b):
+        for i in range(d.s1):
+            if d.act_seq[bi] - d.s1 + 1 + i > 0:
+                _check(got[bi, i], want[bi, i])
+            else:
+                assert torch.all(got[bi, i] == 0)
+    # same values in the K tiles, same arithmetic after them: bit-identical to the int8 path
+    assert torch.equal(got, _run(d))
+
+
+def test_bf16_cache_many_tokens_and_split():
+    """Both launch shapes of the bf16 branch: config 0 (2 tokens, split over CTAs) and 80 ragged tokens."""
+    d = gen.make_config(0)
+    assert torch.equal(_run(d, bf16_cache=True), _run(d))
+    g = torch.Generator().manual_seed(18)
+    act = torch.randint(1, 900, (40,), generator=g).tolist()
+    d = gen.make_inputs(act, s1=2, seed=23, with_indexer=False, with_topk=True)
+    want = oracle.sparse_attention(d.query_nope, d.query_rope, oracle.dequantised_cache(d.key_nope_2d, d.k_nope_scales),
+                                   d.key_rope_2d, None, d.topk_indices, d.block_table, d.act_seq, d.s1)
+    got = _run(d, bf16_cache=True, prefill=True)
+    _check(got, want)
+    assert torch.equal(got, _run(d))
+
+
+def test_bf16_cache_head_slice_is_refused():
+    d = gen.make_inputs([300], s1=1, seed=3, with_indexer=False, with_topk=True, attn_heads=16)
+    with pytest.raises(RuntimeError, match="128 heads"):
+        _run(d, nq=16, bf16_cache=True)

@@ -66,7 +66,7 @@ def test_indexer_rejects_bad_arguments(d, field, bad, exc):
 @pytest.mark.parametrize("field,bad,exc", [
     ("query_nope", lambda d: d.query_nope.to(torch.float16), ValueError),
     ("query_rope", lambda d: d.query_rope[:, :32].contiguous(), ValueError),
-    ("key_nope_2d", lambda d: d.key_nope_2d.to(torch.bfloat16), ValueError),  # bf16 cache: not this path
+    ("key_nope_2d", lambda d: d.key_nope_2d.to(torch.float16), ValueError),  # int8 or bfloat16 only
     ("k_nope_scales", lambda d: d.k_nope_scales[:, :2].contiguous(), ValueError),
     ("topk_indices", lambda d: d.topk_indices.to(torch.int64), ValueError),
     ("kv_act_seqs", lambda d: d.act_seq_key.float(), ValueError),

@@ -46,6 +46,25 @@ def test_sfa_oracle_matches_reference_golden(name):
 
 
 @pytest.mark.parametrize("name", SFA_CASES)
+def test_sfa_oracle_bf16_cache_branch(name):
+    """The golden's is_kn_quant = 0 branch over the bf16 cache that holds the dequantised values:
+    the reference returned the very output of the int8 branch (recorded in the fixture), and so does
+    the oracle, bit for bit."""
+    d, z = load_case(name)
+    assert bool(z["out_bf16_equals_no_flash"])
+    kn_bf16 = oracle.dequantised_cache(d.key_nope_2d, d.k_nope_scales)
+    assert kn_bf16.dtype == torch.bfloat16 and kn_bf16.shape == d.key_nope_2d.shape
+    got = oracle.sparse_attention(d.query_nope, d.query_rope, kn_bf16, d.key_rope_2d, None, d.topk_indices,
+                                  d.block_table, d.act_seq, d.s1)
+    ref = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                  d.topk_indices, d.block_table, d.act_seq, d.s1)
+    assert torch.equal(got, ref)
+    want = mask_empty_rows(from_np_bf16(z["out_no_flash"]).reshape(got.shape), d)
+    e = oracle.attention_errors(got, want)
+    assert e["rel_l2"] < 1e-3 and e["max_abs"] < 2e-3, e
+
+
+@pytest.mark.parametrize("name", SFA_CASES)
 def test_sfa_packed_and_online_oracles(name):
     d, z = load_case(name)
     want = from_np_bf16(z["out_no_flash"])
