@@ -280,3 +280,69 @@ def score_stage_bytes(d: DecodeInputs) -> int:
     s_el = d.idx_key_scale.element_size()
     return sum(s * (IDX_DIM + s_el) + d.s1 * (IDX_HEADS * IDX_DIM + IDX_HEADS * 2 * s_el) + 4 * math.ceil(s / BLOCK_SIZE)
                for s in d.act_seq)
+
+
+# ---------------------------------------------------------------------------------------------
+# MLA + indexer prolog (the producer of every tensor above)
+# ---------------------------------------------------------------------------------------------
+HIDDEN = 7168
+Q_LORA = 1536
+NOPE_DIM = 128  # per-head query width before absorption
+
+
+def make_prolog_inputs(act_seq: Sequence[int], s1: int = 1, seed: int = 0, device="cpu") -> dict:
+    """Inputs of the fused prolog operator, named after the reference driver's dictionaries and drawn from
+    its distributions (examples/models/deepseek_v32_exp/deepseekv32_mla_indexer_prolog_quant.py:229-406):
+    activations U(-1,1), bf16 weights U(-0.1,0.1), the query up-projection quantised per output column,
+    cos/sin U(-0.1,0.1), random cache contents, `cache_index` = the paged row of each new token
+    (positions S-s1 .. S-1 of its sequence). Tokens are flattened: t = b*s1 rows."""
+    g = torch.Generator().manual_seed(seed)
+    b = len(act_seq)
+    t = b * s1
+    block_num, _, table = make_block_table(act_seq, g)
+    rows = block_num * BLOCK_SIZE
+    bf = torch.bfloat16
+
+    def uni(shape, lo, hi, dtype=bf):
+        return _uniform(shape, lo, hi, g, "cpu", torch.float32).to(dtype)
+
+    cache_index = torch.empty(t, dtype=torch.int64)
+    for bi, s in enumerate(act_seq):
+        for j in range(s1):
+            pos = s - s1 + j
+            cache_index[bi * s1 + j] = int(table[bi, pos // BLOCK_SIZE]) * BLOCK_SIZE + pos % BLOCK_SIZE
+    w_uqqr_f = _uniform((Q_LORA, ATT_HEADS * (NOPE_DIM + ROPE_DIM)), -0.1, 0.1, g, "cpu")
+    col_max = w_uqqr_f.abs().amax(dim=0, keepdim=True)
+    w_uqqr = torch.round(w_uqqr_f * (127.0 / col_max)).to(torch.int8)
+    p = dict(
+        token_x=uni((t, HIDDEN), -1, 1),
+        w_dq=uni((HIDDEN, Q_LORA), -0.1, 0.1),
+        w_uqqr=w_uqqr,
+        w_qb_scale=(col_max / 127.0).reshape(-1, 1).contiguous(),
+        w_uk=uni((ATT_HEADS, NOPE_DIM, KV_LORA), -0.1, 0.1),
+        w_dkvkr=uni((HIDDEN, KV_LORA + ROPE_DIM), -0.1, 0.1),
+        gamma_cq=uni((Q_LORA,), -1, 1),
+        gamma_ckv=uni((KV_LORA,), -1, 1),
+        cos=uni((t, ROPE_DIM), -0.1, 0.1),
+        sin=uni((t, ROPE_DIM), -0.1, 0.1),
+        cache_index=cache_index,
+        kv_cache=_int8((rows, KV_LORA), g, "cpu"),
+        kr_cache=uni((rows, ROPE_DIM), -1, 1),
+        kv_scale_cache=_uniform((rows, 4), 1e-3, 1e-2, g, "cpu"),
+        w_idx_qb=torch.randint(-128, 128, (Q_LORA, IDX_HEADS * IDX_DIM), generator=g, dtype=torch.int8),
+        w_idx_qb_scale=_uniform((IDX_HEADS * IDX_DIM, 1), -1, 1, g, "cpu"),
+        w_idx_k=uni((HIDDEN, IDX_DIM), -1, 1),
+        w_idx_proj=uni((HIDDEN, IDX_HEADS), -1, 1),
+        ln_gamma=uni((IDX_DIM,), 0.5, 1.5),
+        ln_beta=uni((IDX_DIM,), -0.5, 0.5),
+        hadamard_q=uni((IDX_DIM, IDX_DIM), -1, 1),
+        hadamard_k=uni((IDX_DIM, IDX_DIM), -1, 1),
+        idx_k_cache=_int8((rows, IDX_DIM), g, "cpu"),
+        idx_k_scale_cache=_uniform((rows, 1), 1e-3, 1e-2, g, "cpu").to(torch.float16),
+        block_table=table,
+    )
+    if str(device) != "cpu":
+        p = {k: v.to(device) for k, v in p.items()}
+    p["act_seq"] = list(act_seq)
+    p["s1"] = s1
+    return p

@@ -162,6 +162,63 @@ def make_sfa(sfa_mod, aq_mod, name, act_seq, s1):
     print(name, "t", d.t, "rows", d.block_num * 128)
 
 
+PROLOG_CASES = {
+    # name: (act_seq, s1)
+    "prolog_mtp": ([300, 131], 2),
+    "prolog_single": ([129, 1, 640], 1),
+}
+PROLOG_HEADS = (0, 37, 127)  # heads of q_nope kept in full; the whole tensor is kept as a digest
+
+
+def make_prolog(pro_mod, name, act_seq, s1):
+    """Runs the reference's two torch goldens (`mla_prolog_quant_v32_compute`, then `indexer_prolog` on its
+    q_norm outputs, as gen_test_data does, deepseekv32_mla_indexer_prolog_quant.py:617-712) on inputs of
+    `pypto_b200.inputs.make_prolog_inputs`, reshaped to the [b, s, ...] layouts the goldens take."""
+    seed = 11000 + sum(act_seq) + s1
+    p = gen.make_prolog_inputs(act_seq, s1=s1, seed=seed)
+    b, t = len(act_seq), len(act_seq) * s1
+    rows = p["kv_cache"].shape[0]
+    nb = rows // 128
+    mla_in = dict(dtype=torch.bfloat16, is_quant_a=False, is_quant_b=True, has_smooth=False,
+                  gamma_cq=p["gamma_cq"], gamma_ckv=p["gamma_ckv"], x=p["token_x"].reshape(b, s1, -1),
+                  w_dq=p["w_dq"], w_uqqr=p["w_uqqr"], w_uk=p["w_uk"], w_dkvkr=p["w_dkvkr"],
+                  cos=p["cos"].reshape(b, s1, -1), sin=p["sin"].reshape(b, s1, -1),
+                  kv_cache=p["kv_cache"].reshape(nb, 128, 1, 512), kr_cache=p["kr_cache"].reshape(nb, 128, 1, 64),
+                  kv_quant_scale_cache=p["kv_scale_cache"].reshape(nb, 128, 1, 4),
+                  cache_index=p["cache_index"].reshape(b, s1), w_qb_scale=p["w_qb_scale"].reshape(1, -1))
+    q_nope, q_rope, q_norm, q_norm_scale, kv_out, kr_out, sc_out = pro_mod.mla_prolog_quant_v32_compute(mla_in)
+    ip_in = dict(token_x=mla_in["x"], q_norm=q_norm.reshape(b, s1, -1), q_norm_scale=q_norm_scale.reshape(b, s1, 1),
+                 w_idx_qb=p["w_idx_qb"], w_idx_qb_scale=p["w_idx_qb_scale"].reshape(1, -1), w_idx_k=p["w_idx_k"],
+                 w_idx_proj=p["w_idx_proj"], layer_norm_gamma=p["ln_gamma"], layer_norm_beta=p["ln_beta"],
+                 cos_idx_rope=mla_in["cos"], sin_idx_rope=mla_in["sin"], hadamard_q=p["hadamard_q"],
+                 hadamard_k=p["hadamard_k"], idx_k_cache=p["idx_k_cache"].reshape(nb, 128, 1, 128),
+                 idx_k_scale_cache=p["idx_k_scale_cache"].reshape(nb, 128, 1, 1),
+                 idx_k_cache_index=mla_in["cache_index"], idx_block_table=p["block_table"])
+    ip = pro_mod.indexer_prolog(ip_in, dict(b=b, t=t, idx_n_heads=64, idx_head_dim=128, rope_head_dim=64))
+    idx = p["cache_index"]
+    q_nope = q_nope.reshape(t, 128, 512)
+    tensors = {k: v for k, v in p.items() if isinstance(v, torch.Tensor)}
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed),
+        hashes=np.array([f"{k}={sha(v)}" for k, v in sorted(tensors.items())]),
+        q_nope_sha=sha(q_nope), q_nope_heads=as_np(q_nope[:, list(PROLOG_HEADS), :]),
+        q_rope=as_np(q_rope.reshape(t, 128, 64)),
+        q_norm=q_norm.reshape(t, -1).numpy(), q_norm_scale=q_norm_scale.reshape(t).numpy(),
+        # caches: the rows the operator wrote, plus a digest of the whole updated cache
+        kv_rows=kv_out.reshape(rows, 512)[idx].numpy(), kv_cache_sha=sha(kv_out),
+        kr_rows=as_np(kr_out.reshape(rows, 64)[idx]), kr_cache_sha=sha(kr_out),
+        kv_scale_rows=sc_out.reshape(rows, 4)[idx].numpy(), kv_scale_cache_sha=sha(sc_out),
+        q_int8=ip["q_int8"].reshape(t, 64, 128).numpy(),
+        q_scale=ip["q_scale"].reshape(t, 64).numpy(),
+        idx_k_rows=ip["idx_k_cache_out"].reshape(rows, 128)[idx].numpy(), idx_k_cache_sha=sha(ip["idx_k_cache_out"]),
+        idx_k_scale_rows=ip["idx_k_scale_cache_out"].reshape(rows)[idx].numpy(),
+        idx_k_scale_cache_sha=sha(ip["idx_k_scale_cache_out"]),
+        weights=ip["weights"].reshape(t, 64).numpy(),
+    )
+    print(name, "t", t, "rows", rows)
+
+
 def make_gather_kat():
     """The paged-gather known answer printed in the reference docstring
     (python/pypto/experimental.py:62-87) and the `10*token + h` buffer pattern of
@@ -180,6 +237,9 @@ def main():
     for name, (act, s1) in SFA_CASES.items():
         make_sfa(sfa_mod, aq_mod, name, act, s1)
     make_gather_kat()
+    pro_mod = importlib.import_module("deepseekv32_mla_indexer_prolog_quant")
+    for name, (act, s1) in PROLOG_CASES.items():
+        make_prolog(pro_mod, name, act, s1)
 
 
 if __name__ == "__main__":

@@ -34,6 +34,19 @@ def load_case(name: str, **kw):
     return d, z
 
 
+PROLOG_CASES = ["prolog_mtp", "prolog_single"]
+PROLOG_HEADS = (0, 37, 127)  # heads of q_nope the fixture keeps in full
+
+
+def load_prolog_case(name: str):
+    z = np.load(GOLDEN / f"{name}.npz")
+    p = gen.make_prolog_inputs([int(x) for x in z["act_seq"]], s1=int(z["s1"]), seed=int(z["seed"]))
+    want = dict(h.split("=") for h in z["hashes"])
+    got = {k: sha(v) for k, v in p.items() if isinstance(v, torch.Tensor)}
+    assert got == want, f"regenerated inputs of {name} differ from the ones the fixture was made with"
+    return p, z
+
+
 LI_CASES = ["li_ragged_f32", "li_mtp_f16", "li_short_f16"]
 SFA_CASES = ["sfa_ragged_mtp", "sfa_single"]
 
