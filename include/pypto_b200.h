@@ -175,6 +175,47 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
                    void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * MLA + lightning-indexer prolog: produces every input of the entry points above from the
+ * token's hidden state and writes the token's rows into the paged caches. Replaces
+ * `mla_indexer_prolog_quant_d/_p` (examples/models/deepseek_v32_exp/
+ * mla_indexer_prolog_quant_impl.py:37-139, :142-256; bodies mla_prolog_quant_impl.py:502-707 and
+ * lightning_indexer_prolog_quant_impl.py:325-504; goldens deepseekv32_mla_indexer_prolog_quant.py
+ * :409-541 and :544-614), in the configuration the example runs: bf16 down-projections, int8
+ * up-projection of the normalised query with per-column scales, int8 latent cache.
+ *
+ *   token_x   bf16 [t, hidden]                 cos, sin   bf16 [t, 64]      cache_index int64 [t]
+ *   w_dq      bf16 [hidden, q_lora]            w_uqqr     int8 [q_lora, 128*192], w_qb_scale f32 [128*192]
+ *   w_uk      bf16 [128, 128, 512]             w_dkvkr    bf16 [hidden, 576]
+ *   gamma_cq  bf16 [q_lora]                    gamma_ckv  bf16 [512]
+ *   w_idx_qb  int8 [q_lora, 64*128], w_idx_qb_scale f32 [64*128]
+ *   w_idx_k   bf16 [hidden, 128]               w_idx_proj bf16 [hidden, 64]
+ *   ln_gamma, ln_beta bf16 [128]               hadamard_q, hadamard_k bf16 [128, 128]
+ * updated in place (row cache_index[i] of each, rows outside [0, cache_rows) are skipped and
+ * reported as PTO_ST_BAD_PAGE):
+ *   kv_cache int8 [cache_rows, 512]   kr_cache bf16 [cache_rows, 64]   kv_scale_cache f32 [cache_rows, 4]
+ *   idx_k_cache int8 [cache_rows, 128]   idx_k_scale_cache f16 [cache_rows]
+ * outputs:
+ *   query_nope_out bf16 [t, 128, 512]   query_rope_out bf16 [t, 128, 64]
+ *   q_int8_out int8 [t, 64, 128]        q_scale_out f16 [t, 64]        weights_out f16 [t, 64]
+ *
+ * The seven projections are plain GEMMs issued to cuBLAS (libcublas.so.12, resolved at the first call;
+ * PTO_ERR_UNSUPPORTED if absent); everything between them is this library's kernels. No allocation:
+ * the workspace also holds cuBLAS's own scratch, so the call can be recorded into a CUDA graph.
+ * ------------------------------------------------------------------------------------------ */
+size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora);
+
+int pto_mla_indexer_prolog_quant(
+    const void* token_x, const void* w_dq, const int8_t* w_uqqr, const float* w_qb_scale,
+    const void* w_uk, const void* w_dkvkr, const void* gamma_cq, const void* gamma_ckv,
+    const void* cos, const void* sin, const int64_t* cache_index, int8_t* kv_cache, void* kr_cache,
+    float* kv_scale_cache, const int8_t* w_idx_qb, const float* w_idx_qb_scale, const void* w_idx_k,
+    const void* w_idx_proj, const void* ln_gamma, const void* ln_beta, const void* hadamard_q,
+    const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache, void* query_nope_out,
+    void* query_rope_out, int8_t* q_int8_out, void* q_scale_out, void* weights_out, int t,
+    int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
+    void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Fused decode chain: indexer -> top-k -> sparse attention on one stream, the order of
  * `DeepSeekIndexerAttentionQuant`
  * (framework/src/operator/models/deepseek_v3.2_exp/deepseek_indexer_attention_quant.cpp:170-250).

@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libpypto_b200.so"
-SOURCES = ["capi.cu", "li_score.cu", "topk_select.cu", "sfa_decode.cu", "sfa_cluster.cu"]
+SOURCES = ["capi.cu", "li_score.cu", "topk_select.cu", "sfa_decode.cu", "sfa_cluster.cu", "prolog.cu"]
 HEADERS = [CSRC / "common.cuh", CSRC / "sfa_common.cuh", PKG.parent / "include" / "pypto_b200.h"]
 
 
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    link = [nvcc_path(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB)] + objs
+    link = [nvcc_path(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB)] + objs + ["-ldl"]
     subprocess.run(link, check=True)
     return LIB
 

