@@ -162,10 +162,54 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_prolog_stage(args, dev):
+    """Profiling aid: the fused MLA + indexer prolog for --batch sequences x --s1 tokens, eager and replayed
+    from a CUDA graph, timed with CUDA events. Algorithmic bytes = every weight once + the token's rows."""
+    import pypto_b200 as pto
+
+    p = gen.make_prolog_inputs([args.ctx] * args.batch, s1=args.s1, seed=4321, device=dev)
+    t = args.batch * args.s1
+    out = [torch.zeros(t, 128, 512, dtype=torch.bfloat16, device=dev), torch.zeros(t, 128, 64, dtype=torch.bfloat16, device=dev),
+           p["kv_cache"], p["kr_cache"], p["kv_scale_cache"], torch.zeros(t, 64, 128, dtype=torch.int8, device=dev),
+           torch.zeros(t, 64, 1, dtype=torch.float16, device=dev), p["idx_k_cache"], p["idx_k_scale_cache"],
+           torch.zeros(t, 64, dtype=torch.float16, device=dev)]
+    names = ["token_x", "w_dq", "w_uqqr", "w_qb_scale", "w_uk", "w_dkvkr", "gamma_cq", "gamma_ckv", "cos", "sin",
+             "cache_index", "kv_cache", "kr_cache", "kv_scale_cache", "w_idx_qb", "w_idx_qb_scale", "w_idx_k",
+             "w_idx_proj", "ln_gamma", "ln_beta", "hadamard_q", "hadamard_k", "idx_k_cache", "idx_k_scale_cache"]
+    call_args = [p[n] for n in names] + out + [1e-5, 1e-5, "PA_BSND", None, None, None, None]
+    weights = ["w_dq", "w_uqqr", "w_qb_scale", "w_uk", "w_dkvkr", "w_idx_qb", "w_idx_qb_scale", "w_idx_k", "w_idx_proj",
+               "hadamard_q", "hadamard_k"]
+    by = sum(p[n].numel() * p[n].element_size() for n in weights)
+    by += t * (7168 * 2 + 128 * 576 * 2 + 64 * 128 + 64 * 4 + 656 + 130)
+    captured = pto.CapturedCall(pto.mla_indexer_prolog_quant_d, *call_args)
+    res = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # the weights (100 MB) would stay in the 126 MB L2
+    for tag, fn in (("eager", lambda: pto.mla_indexer_prolog_quant_d(*call_args)), ("graph", captured.replay)):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        res[tag + "_ms"] = statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+    peak, src = load_peaks()
+    print(json.dumps({"stage": "prolog", "tokens": t, **res, "algorithmic_bytes": by,
+                      "achieved_gbs": by / res["graph_ms"] / 1e6, "peak_gbs": peak, "peak_source": src,
+                      "frac": by / res["graph_ms"] / 1e6 / peak, "gpu_launches_per_call": 11,
+                      "l2": "256 MB written between timed calls",
+                      "status": pto.workspace_status(dev)[0]}), flush=True)
+
+
 def run_stage(args, dev):
     """Profiling aid: one stage alone on a uniform synthetic case, timed with CUDA events."""
     import pypto_b200 as pto
 
+    if args.stage == "prolog":
+        return run_prolog_stage(args, dev)
     d = gen.make_inputs([args.ctx] * args.batch, s1=args.s1, seed=4321, device=dev,
                         scale_dtype=getattr(torch, args.scale_dtype), with_topk=True)
     t = d.t
@@ -217,7 +261,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
-    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused"],
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

@@ -204,6 +204,14 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
  * ------------------------------------------------------------------------------------------ */
 size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora);
 
+/* Optional one-time weight preparation (the counterpart of the reference's cast of these weights to its
+ * NZ format, deepseekv32_mla_indexer_prolog_quant.py:696-698, :721-725): the four projections of the token
+ * share their left operand, so their weights are laid side by side, packed bf16
+ * [hidden, q_lora + 576 + 128 + 64] = w_dq | w_dkvkr | w_idx_k | w_idx_proj, and become one product. */
+int pto_prolog_pack_weights(const void* w_dq, const void* w_dkvkr, const void* w_idx_k,
+                            const void* w_idx_proj, int hidden, int q_lora, void* packed,
+                            pto_stream_t stream);
+
 int pto_mla_indexer_prolog_quant(
     const void* token_x, const void* w_dq, const int8_t* w_uqqr, const float* w_qb_scale,
     const void* w_uk, const void* w_dkvkr, const void* gamma_cq, const void* gamma_ckv,
@@ -211,8 +219,9 @@ int pto_mla_indexer_prolog_quant(
     float* kv_scale_cache, const int8_t* w_idx_qb, const float* w_idx_qb_scale, const void* w_idx_k,
     const void* w_idx_proj, const void* ln_gamma, const void* ln_beta, const void* hadamard_q,
     const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache, void* query_nope_out,
-    void* query_rope_out, int8_t* q_int8_out, void* q_scale_out, void* weights_out, int t,
-    int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
+    void* query_rope_out, int8_t* q_int8_out, void* q_scale_out, void* weights_out,
+    const void* w_x_packed /* from pto_prolog_pack_weights, or NULL: four separate products */,
+    int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
     void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

@@ -376,8 +376,14 @@ int gemm_rowmajor(cublasHandle_t h, int t, int n, int k, const void* a, int lda,
 constexpr size_t kBlasWorkspace = 32u << 20;
 
 struct PrologWs {
-  size_t status, blas, qa, kv, ki, wp, q_norm, q_norm_scale, qb_i32, q_b, qi_i32, total;
+  size_t status, blas, xproj, q_norm, q_norm_scale, qb_i32, q_b, qi_i32, total;
 };
+constexpr int kXProjExtra = 576 + 128 + 64;  // columns after the q_lora ones: latent+rope key | indexer key | weights
+
+// The int8 products run with at least 64 rows: below that the library falls back to a kernel for narrow
+// outputs that is several times slower (measured: 104 + 55 us at 8 tokens against 17 + 11 us at 64). The
+// padding rows are workspace contents; their results are never read.
+inline int prolog_int8_rows(int t) { return t < 64 ? 64 : t; }
 
 PrologWs prolog_ws(int t, int q_lora) {
   PrologWs w{};
@@ -388,17 +394,15 @@ PrologWs prolog_ws(int t, int q_lora) {
     return at;
   };
   const size_t tt = static_cast<size_t>(t);
+  const size_t tp = static_cast<size_t>(prolog_int8_rows(t));
   w.status = take(kStatusBytes);
   w.blas = take(kBlasWorkspace);
-  w.qa = take(tt * q_lora * 4);
-  w.kv = take(tt * 576 * 4);
-  w.ki = take(tt * 128 * 4);
-  w.wp = take(tt * 64 * 4);
-  w.q_norm = take(tt * q_lora);
+  w.xproj = take(tt * (q_lora + kXProjExtra) * 4);  // fp32 [t, q_lora | 576 | 128 | 64]
+  w.q_norm = take(tp * q_lora);
   w.q_norm_scale = take(tt * 4);
-  w.qb_i32 = take(tt * 128 * 192 * 4);
+  w.qb_i32 = take(tp * 128 * 192 * 4);
   w.q_b = take(tt * 128 * 192 * 2);
-  w.qi_i32 = take(tt * 64 * 128 * 4);
+  w.qi_i32 = take(tp * 64 * 128 * 4);
   w.total = off;
   return w;
 }
@@ -578,6 +582,22 @@ size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora) {
   return prolog_ws(t, q_lora).total;
 }
 
+int pto_prolog_pack_weights(const void* w_dq, const void* w_dkvkr, const void* w_idx_k, const void* w_idx_proj, int hidden,
+                            int q_lora, void* packed, pto_stream_t stream) {
+  PTO_REQUIRE(w_dq && w_dkvkr && w_idx_k && w_idx_proj && packed, "null tensor pointer");
+  PTO_REQUIRE(hidden >= 1 && q_lora >= 1, "hidden / q_lora");
+  const size_t ld = static_cast<size_t>(q_lora + kXProjExtra) * 2;  // bytes per packed row (bf16)
+  uint8_t* dst = reinterpret_cast<uint8_t*>(packed);
+  const void* src[4] = {w_dq, w_dkvkr, w_idx_k, w_idx_proj};
+  const size_t width[4] = {static_cast<size_t>(q_lora) * 2, 576 * 2, 128 * 2, 64 * 2};
+  size_t off = 0;
+  for (int i = 0; i < 4; ++i) {
+    PTO_CUDA(cudaMemcpy2DAsync(dst + off, ld, src[i], width[i], width[i], hidden, cudaMemcpyDeviceToDevice, stream));
+    off += width[i];
+  }
+  return PTO_OK;
+}
+
 int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const int8_t* w_uqqr, const float* w_qb_scale,
                                  const void* w_uk, const void* w_dkvkr, const void* gamma_cq, const void* gamma_ckv,
                                  const void* cos, const void* sin, const int64_t* cache_index, int8_t* kv_cache,
@@ -586,9 +606,9 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
                                  const void* ln_gamma, const void* ln_beta, const void* hadamard_q,
                                  const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache,
                                  void* query_nope_out, void* query_rope_out, int8_t* q_int8_out, void* q_scale_out,
-                                 void* weights_out, int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq,
-                                 float eps_ckv, float ln_eps, void* workspace, size_t workspace_bytes,
-                                 pto_stream_t stream) {
+                                 void* weights_out, const void* w_x_packed, int t, int hidden, int q_lora,
+                                 int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps, void* workspace,
+                                 size_t workspace_bytes, pto_stream_t stream) {
   PTO_REQUIRE(token_x && w_dq && w_uqqr && w_qb_scale && w_uk && w_dkvkr && gamma_cq && gamma_ckv && cos && sin &&
                   cache_index && kv_cache && kr_cache && kv_scale_cache && w_idx_qb && w_idx_qb_scale && w_idx_k &&
                   w_idx_proj && ln_gamma && ln_beta && hadamard_q && hadamard_k && idx_k_cache && idx_k_scale_cache &&
@@ -612,10 +632,11 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   if (rc != PTO_OK) return rc;
   uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
   int32_t* status = reinterpret_cast<int32_t*>(base + w.status);
-  float* qa = reinterpret_cast<float*>(base + w.qa);
-  float* kv = reinterpret_cast<float*>(base + w.kv);
-  float* ki = reinterpret_cast<float*>(base + w.ki);
-  float* wp = reinterpret_cast<float*>(base + w.wp);
+  const int ld = q_lora + kXProjExtra;
+  float* qa = reinterpret_cast<float*>(base + w.xproj);
+  float* kv = qa + q_lora;
+  float* ki = kv + 576;
+  float* wp = ki + 128;
   int8_t* q_norm = reinterpret_cast<int8_t*>(base + w.q_norm);
   float* q_norm_scale = reinterpret_cast<float*>(base + w.q_norm_scale);
   int32_t* qb_i32 = reinterpret_cast<int32_t*>(base + w.qb_i32);
@@ -629,23 +650,31 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   PTO_BLAS(blas().set_stream(h, stream));
   PTO_BLAS(blas().set_workspace(h, base + w.blas, kBlasWorkspace));  // no allocation inside a captured call
 
-  // projections of the token: fp32 results, rounded where the golden rounds by the kernels that read them
-  rc = gemm_rowmajor(h, t, q_lora, hidden, token_x, hidden, w_dq, q_lora, qa, q_lora, CUDA_R_16BF, CUDA_R_32F);
-  if (rc != PTO_OK) return rc;
-  rc = gemm_rowmajor(h, t, 576, hidden, token_x, hidden, w_dkvkr, 576, kv, 576, CUDA_R_16BF, CUDA_R_32F);
-  if (rc != PTO_OK) return rc;
-  rc = gemm_rowmajor(h, t, 128, hidden, token_x, hidden, w_idx_k, 128, ki, 128, CUDA_R_16BF, CUDA_R_32F);
-  if (rc != PTO_OK) return rc;
-  rc = gemm_rowmajor(h, t, 64, hidden, token_x, hidden, w_idx_proj, 64, wp, 64, CUDA_R_16BF, CUDA_R_32F);
-  if (rc != PTO_OK) return rc;
-  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
-  PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
+  // projections of the token: fp32 results [t, q_lora | 576 | 128 | 64], rounded where the golden rounds by the
+  // kernels that read them. One product when the caller has packed the four weights side by side, else four.
+  if (w_x_packed != nullptr) {
+    PTO_REQUIRE(aligned16(w_x_packed), "w_x_packed must be 16-byte aligned");
+    rc = gemm_rowmajor(h, t, ld, hidden, token_x, hidden, w_x_packed, ld, qa, ld, CUDA_R_16BF, CUDA_R_32F);
+    if (rc != PTO_OK) return rc;
+  } else {
+    rc = gemm_rowmajor(h, t, q_lora, hidden, token_x, hidden, w_dq, q_lora, qa, ld, CUDA_R_16BF, CUDA_R_32F);
+    if (rc != PTO_OK) return rc;
+    rc = gemm_rowmajor(h, t, 576, hidden, token_x, hidden, w_dkvkr, 576, kv, ld, CUDA_R_16BF, CUDA_R_32F);
+    if (rc != PTO_OK) return rc;
+    rc = gemm_rowmajor(h, t, 128, hidden, token_x, hidden, w_idx_k, 128, ki, ld, CUDA_R_16BF, CUDA_R_32F);
+    if (rc != PTO_OK) return rc;
+    rc = gemm_rowmajor(h, t, 64, hidden, token_x, hidden, w_idx_proj, 64, wp, ld, CUDA_R_16BF, CUDA_R_32F);
+    if (rc != PTO_OK) return rc;
+  }
+  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
+  PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, ld, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
                                  t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
                                  weights_out, status, stream));
   // int8 up-projections of the normalised query
-  rc = gemm_rowmajor(h, t, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
+  const int tp = prolog_int8_rows(t);
+  rc = gemm_rowmajor(h, tp, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
   if (rc != PTO_OK) return rc;
-  rc = gemm_rowmajor(h, t, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
+  rc = gemm_rowmajor(h, tp, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
   if (rc != PTO_OK) return rc;
   PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream));
   PTO_CUDA(pto::launch_prolog_idxq(qi_i32, q_norm_scale, w_idx_qb_scale, cos, sin, hadamard_q, t, q_int8_out, q_scale_out,

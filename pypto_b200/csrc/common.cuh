@@ -307,13 +307,13 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
 cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster
 
 // Prolog stages between the projections (prolog.cu). Fixed widths: 128 heads x (128 + 64), latent 512,
-// rope 64, indexer 64 x 128.
-cudaError_t launch_prolog_qnorm_quant(const float* qa, const void* gamma_cq, int t, int q_lora, float eps,
+// rope 64, indexer 64 x 128. `ld`: row stride (elements) of the fp32 projection results.
+cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
                                       int8_t* q_norm, float* q_norm_scale, cudaStream_t stream);
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
                                           const void* cos, const void* sin, int t, void* q_b, void* q_rope,
                                           cudaStream_t stream);
-cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, const void* gamma_ckv, const void* cos,
+cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, const void* gamma_ckv, const void* cos,
                              const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,

@@ -64,12 +64,12 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale_q) {
 // ---- query down-projection: bf16 rounding, RMSNorm, per-token int8 ------------------------------------
 // grid = tokens, dynamic shared memory = q_lora floats
 __global__ void __launch_bounds__(256)
-prolog_qnorm_quant_kernel(const float* __restrict__ qa, const __nv_bfloat16* __restrict__ gamma, int q_lora,
+prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, const __nv_bfloat16* __restrict__ gamma, int q_lora,
                           float eps, int8_t* __restrict__ q_norm, float* __restrict__ q_norm_scale) {
   extern __shared__ float row[];
   __shared__ float red[32];
   const int ti = blockIdx.x;
-  const float* src = qa + static_cast<int64_t>(ti) * q_lora;
+  const float* src = qa + static_cast<int64_t>(ti) * ld;
   const float inv_n = 1.0f / static_cast<float>(q_lora);
   float ss = 0.f;
   for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
@@ -122,7 +122,7 @@ prolog_qb_dequant_rope_kernel(const int32_t* __restrict__ qb_i32, const float* _
 // ---- per token: latent KV row, rope key, indexer key, indexer weights; scatter into the caches ---------
 // grid = tokens, block = 128 (thread i owns latent dims 4i..4i+3: warp w = 128-wide quantisation tile w)
 __global__ void __launch_bounds__(128)
-prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, const float* __restrict__ wp,
+prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, const float* __restrict__ wp, int ld,
                  const __nv_bfloat16* __restrict__ gamma_ckv, const __nv_bfloat16* __restrict__ cos,
                  const __nv_bfloat16* __restrict__ sin, const __nv_bfloat16* __restrict__ ln_gamma,
                  const __nv_bfloat16* __restrict__ ln_beta, const __nv_bfloat16* __restrict__ hadamard_k,
@@ -133,13 +133,20 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   __shared__ float red[32];
   __shared__ float pe[kRope];
   __shared__ float kvec[kIdxDim];
+  __shared__ __align__(16) __nv_bfloat16 had[kIdxDim * kIdxDim];  // 32 KB, fetched while the norms are computed
   const int ti = blockIdx.x, i = threadIdx.x, lane = i & 31, warp = i >> 5;
+  {
+    const uint4* hsrc = reinterpret_cast<const uint4*>(hadamard_k);
+    uint4* hdst = reinterpret_cast<uint4*>(had);
+#pragma unroll 4
+    for (int u = i; u < kIdxDim * kIdxDim / 8; u += 128) hdst[u] = __ldg(hsrc + u);
+  }
   const int64_t row = cache_index[ti];
   const bool row_ok = row >= 0 && row < cache_rows;
   if (!row_ok && i == 0) set_status(status, PTO_ST_BAD_PAGE, static_cast<int>(row), 60);
 
   // latent part: bf16 rounding, RMSNorm, int8 per 128-wide tile
-  const float* src = kv + static_cast<int64_t>(ti) * (kLora + kRope);
+  const float* src = kv + static_cast<int64_t>(ti) * ld;
   float v[4];
   float ss = 0.f;
 #pragma unroll
@@ -179,7 +186,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   }
 
   // indexer key: LayerNorm in fp32 -> bf16, rope on the first 64 dims (halves, no de-interleave), Hadamard, int8
-  const float x = ki[static_cast<int64_t>(ti) * kIdxDim + i];
+  const float x = ki[static_cast<int64_t>(ti) * ld + i];
   const float mean = block_sum(x, red) * (1.0f / kIdxDim);
   const float dx = x - mean;
   const float var = block_sum(__fmul_rn(dx, dx), red) * (1.0f / kIdxDim);
@@ -197,7 +204,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   __syncthreads();
   float acc = 0.f;
 #pragma unroll 8
-  for (int r = 0; r < kIdxDim; ++r) acc = fmaf(kvec[r], ld_bf16(hadamard_k + r * kIdxDim + i), acc);
+  for (int r = 0; r < kIdxDim; ++r) acc = fmaf(kvec[r], __bfloat162float(had[r * kIdxDim + i]), acc);
   const float hk = bf16_round(acc);
   const float kmax = block_max(fabsf(hk), red);
   const float ksq = __fdiv_rn(127.0f, kmax);
@@ -208,15 +215,16 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
 
   // indexer weights: bf16 rounding, then heads^-1/2 and dim^-1/2 in fp32, fp16 out
   if (i < kIdxHeads) {
-    const float w = bf16_round(wp[static_cast<int64_t>(ti) * kIdxHeads + i]);
+    const float w = bf16_round(wp[static_cast<int64_t>(ti) * ld + i]);
     weights[static_cast<int64_t>(ti) * kIdxHeads + i] =
         __float2half_rn(__fmul_rn(__fmul_rn(w, 0.125f), 0.08838834764831845f));
   }
 }
 
 // ---- indexer query: int32 -> bf16, rope, Hadamard, per-head int8 ------------------------------------------
-// grid = (16 head groups, tokens), block = 128: four heads per block share each Hadamard row they read
-constexpr int kHeadsPerBlock = 4;
+// grid = (8 head groups, tokens), block = 128: eight heads per block share the Hadamard matrix, staged in
+// shared memory while the products are dequantised
+constexpr int kHeadsPerBlock = 8;
 __global__ void __launch_bounds__(128)
 prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__ q_norm_scale,
                    const float* __restrict__ w_scale, const __nv_bfloat16* __restrict__ cos,
@@ -224,7 +232,14 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
                    int8_t* __restrict__ q_int8, __half* __restrict__ q_scale) {
   __shared__ float red[32];
   __shared__ float qv[kHeadsPerBlock][kIdxDim];
+  __shared__ __align__(16) __nv_bfloat16 had[kIdxDim * kIdxDim];
   const int hg = blockIdx.x, ti = blockIdx.y, i = threadIdx.x;
+  {
+    const uint4* hsrc = reinterpret_cast<const uint4*>(hadamard_q);
+    uint4* hdst = reinterpret_cast<uint4*>(had);
+#pragma unroll 4
+    for (int u = i; u < kIdxDim * kIdxDim / 8; u += 128) hdst[u] = __ldg(hsrc + u);
+  }
   const float rs = q_norm_scale[ti];
   const float cs = i < kRope ? ld_bf16(cos + ti * kRope + i) : 0.f;
   const float sn = i < kRope ? ld_bf16(sin + ti * kRope + i) : 0.f;
@@ -249,10 +264,12 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
 #pragma unroll
   for (int hh = 0; hh < kHeadsPerBlock; ++hh) qv[hh][i] = q[hh];
   __syncthreads();
-  float acc[kHeadsPerBlock] = {0.f, 0.f, 0.f, 0.f};
+  float acc[kHeadsPerBlock];
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) acc[hh] = 0.f;
 #pragma unroll 4
   for (int r = 0; r < kIdxDim; ++r) {
-    const float hv = ld_bf16(hadamard_q + r * kIdxDim + i);
+    const float hv = __bfloat162float(had[r * kIdxDim + i]);
 #pragma unroll
     for (int hh = 0; hh < kHeadsPerBlock; ++hh) acc[hh] = fmaf(qv[hh][r], hv, acc[hh]);
   }
@@ -269,10 +286,10 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
 
 }  // namespace
 
-cudaError_t launch_prolog_qnorm_quant(const float* qa, const void* gamma_cq, int t, int q_lora, float eps,
+cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
                                       int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
   prolog_qnorm_quant_kernel<<<t, 256, static_cast<size_t>(q_lora) * sizeof(float), stream>>>(
-      qa, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
+      qa, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
   return cudaGetLastError();
 }
 
@@ -286,13 +303,13 @@ cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_
   return cudaGetLastError();
 }
 
-cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, const void* gamma_ckv, const void* cos,
+cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, const void* gamma_ckv, const void* cos,
                              const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
                              void* idx_k_scale_cache, void* weights, int32_t* status, cudaStream_t stream) {
   prolog_kv_kernel<<<t, 128, 0, stream>>>(
-      kv, ki, wp, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
+      kv, ki, wp, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(ln_gamma),
       reinterpret_cast<const __nv_bfloat16*>(ln_beta), reinterpret_cast<const __nv_bfloat16*>(hadamard_k), cache_index,
       cache_rows, eps_ckv, ln_eps, kv_cache, reinterpret_cast<__nv_bfloat16*>(kr_cache), kv_scale_cache, idx_k_cache,

@@ -310,6 +310,29 @@ def _cache_out(cache_in, cache_out, name):
     return o
 
 
+_PACKED_X_WEIGHTS = {}
+
+
+def _packed_x_weights(lib, dev, w_dq, w_dkvkr, w_idx_k, w_idx_proj, h, q_lora):
+    """The four weights that multiply the token, packed side by side once per set of weight tensors (keyed by
+    address and in-place version, so a weight that is overwritten is packed again; an entry keeps its weight
+    tensors alive, so an address cannot come back with other contents while the entry exists)."""
+    ws = (w_dq, w_dkvkr, w_idx_k, w_idx_proj)
+    key = tuple((w.data_ptr(), w._version) for w in ws) + (dev.index,)
+    hit = _PACKED_X_WEIGHTS.get(key)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # no allocation inside a capture: the warm-up call before it has filled the cache
+        hit = torch.empty((h, q_lora + 768), dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.pto_prolog_pack_weights(*[w.data_ptr() for w in ws], h, q_lora, hit.data_ptr(),
+                                               torch.cuda.current_stream(dev).cuda_stream))
+        if len(_PACKED_X_WEIGHTS) >= 8:
+            _PACKED_X_WEIGHTS.pop(next(iter(_PACKED_X_WEIGHTS)))
+        _PACKED_X_WEIGHTS[key] = (hit, ws)
+        return hit
+    return hit[0]
+
+
 def _mla_indexer_prolog_quant(token_x, mla_w_dq, mla_w_uq_qr, mla_dequant_scale, mla_w_uk, mla_w_dkv_kr, mla_gamma_cq,
                               mla_gamma_ckv, cos, sin, cache_index, mla_kv_cache, mla_kr_cache, mla_k_scale_cache,
                               ip_w_qb_in, ip_w_qb_scale_in, ip_wk_in, ip_w_proj_in, ip_ln_gamma_k_in, ip_ln_beta_k_in,
@@ -374,7 +397,9 @@ def _mla_indexer_prolog_quant(token_x, mla_w_dq, mla_w_uq_qr, mla_dequant_scale,
     nbytes = lib.pto_prolog_workspace_bytes(t, h, q_lora)
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
-        _lib.check(lib.pto_mla_indexer_prolog_quant(*[v.data_ptr() for v in tensors], t, h, q_lora, rows,
+        packed = _packed_x_weights(lib, dev, w_dq, w_dkvkr, w_idx_k, w_idx_proj, h, q_lora)
+        _lib.check(lib.pto_mla_indexer_prolog_quant(*[v.data_ptr() for v in tensors],
+                                                    packed.data_ptr() if packed is not None else None, t, h, q_lora, rows,
                                                     float(mla_epsilon_cq), float(mla_epsilon_ckv), ln_eps,
                                                     ws.data_ptr(), ws.numel(),
                                                     torch.cuda.current_stream(dev).cuda_stream))

@@ -66,6 +66,13 @@ def check_scale(got, want, name, rtol_ref):
     ref_compare(got, want, name, 2.5e-5, rtol_ref, 0.05)
 
 
+def check_weights(got, want):
+    """bf16(x @ w) scaled into fp16: equal to the golden's up to the fp16 rounding, or one bf16 step off when the
+    fp32 sum lies at a bf16 rounding boundary (seen: an exact sum of 32.37503 between 32.25 and 32.5)."""
+    ref_compare(got, want, "weights (one bf16 step)", 2.5e-5, 2.0 ** -6, 0)
+    ref_compare(got, want, "weights", 2.5e-5, 2.0 ** -9, 0.02)
+
+
 def check_q_scale(got, want):
     check_scale(got, want, "q_scale", 0.006)
 
@@ -84,7 +91,7 @@ def check_against(o, want, idx):
     # (the reference's absolute bound on the key scales is met through the untouched rows of the whole cache,
     # which the callers compare bit for bit; the written rows follow the rule for scales)
     check_scale(o["idx_k_scale_cache"].reshape(-1)[idx], want["idx_k_scale_cache"].reshape(-1)[idx], "k_scale rows", 0.005)
-    ref_compare(o["weights"], want["weights"], "weights", 2.5e-5, 2.0 ** -7, 0)
+    check_weights(o["weights"], want["weights"])
     # beyond the reference's bound: in the rows whose scale equals the golden's, an int8 value differs only when
     # a rounding boundary was crossed upstream, and then by one step (the Hadamard output is bf16: near the row
     # maximum one bf16 step is already half an int8 step, so a few per cent of the values do move)
@@ -110,7 +117,7 @@ def test_matches_reference_fixture(name):
     check_q_scale(o["q_scale"].reshape(t, 64), torch.from_numpy(z["q_scale"]))
     ref_compare(o["idx_k_cache"][idx], torch.from_numpy(z["idx_k_rows"]), "idx k rows", 1, 0, 0)
     check_scale(o["idx_k_scale_cache"].reshape(-1)[idx], torch.from_numpy(z["idx_k_scale_rows"]), "k_scale rows", 0.005)
-    ref_compare(o["weights"], torch.from_numpy(z["weights"]), "weights", 2.5e-5, 2.0 ** -7, 0)
+    check_weights(o["weights"], torch.from_numpy(z["weights"]))
     # rows the operator did not write are untouched
     keep = torch.ones(p["kv_cache"].shape[0], dtype=torch.bool)
     keep[idx] = False
