@@ -315,6 +315,10 @@ struct Blas {
                                  const void*, void*, cudaDataType, int, long long, int, cublasComputeType_t,
                                  cublasGemmAlgo_t) = nullptr;
   cublasHandle_t handle[64] = {nullptr};
+  // second stream and fork/join events per device: the per-token kernel and the indexer-query kernel run
+  // beside the chain of products they do not depend on
+  cudaStream_t side[64] = {nullptr};
+  cudaEvent_t ev[64][3] = {{nullptr}};
   std::mutex mu;
   bool loaded = false;
 };
@@ -324,7 +328,7 @@ Blas& blas() {
   return b;
 }
 
-int blas_handle(cublasHandle_t* out) {
+int blas_handle(cublasHandle_t* out, int* device = nullptr) {
   Blas& b = blas();
   if (!b.loaded) {
     void* lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
@@ -346,7 +350,12 @@ int blas_handle(cublasHandle_t* out) {
     cublasStatus_t st = b.create(&b.handle[dev]);
     if (st != CUBLAS_STATUS_SUCCESS) return fail(PTO_ERR_CUDA, "cublasCreate failed with %d", static_cast<int>(st));
   }
+  if (b.side[dev] == nullptr) {
+    PTO_CUDA(cudaStreamCreateWithFlags(&b.side[dev], cudaStreamNonBlocking));
+    for (int i = 0; i < 3; ++i) PTO_CUDA(cudaEventCreateWithFlags(&b.ev[dev][i], cudaEventDisableTiming));
+  }
   *out = b.handle[dev];
+  if (device != nullptr) *device = dev;
   return PTO_OK;
 }
 
@@ -645,8 +654,11 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
 
   std::lock_guard<std::mutex> lock(blas().mu);
   cublasHandle_t h;
-  rc = blas_handle(&h);
+  int dev = 0;
+  rc = blas_handle(&h, &dev);
   if (rc != PTO_OK) return rc;
+  cudaStream_t side = blas().side[dev];
+  cudaEvent_t* ev = blas().ev[dev];
   PTO_BLAS(blas().set_stream(h, stream));
   PTO_BLAS(blas().set_workspace(h, base + w.blas, kBlasWorkspace));  // no allocation inside a captured call
 
@@ -666,19 +678,26 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
     rc = gemm_rowmajor(h, t, 64, hidden, token_x, hidden, w_idx_proj, 64, wp, ld, CUDA_R_16BF, CUDA_R_32F);
     if (rc != PTO_OK) return rc;
   }
-  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
+  // fork: the per-token kernel (caches, indexer key, weights) needs only the projections
+  PTO_CUDA(cudaEventRecord(ev[0], stream));
+  PTO_CUDA(cudaStreamWaitEvent(side, ev[0], 0));
   PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, ld, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
                                  t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
-                                 weights_out, status, stream));
+                                 weights_out, status, side));
+  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
   // int8 up-projections of the normalised query
   const int tp = prolog_int8_rows(t);
   rc = gemm_rowmajor(h, tp, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
   if (rc != PTO_OK) return rc;
   rc = gemm_rowmajor(h, tp, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
   if (rc != PTO_OK) return rc;
-  PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream));
+  // the indexer-query kernel joins the side stream; the attention query finishes on the caller's
+  PTO_CUDA(cudaEventRecord(ev[1], stream));
+  PTO_CUDA(cudaStreamWaitEvent(side, ev[1], 0));
   PTO_CUDA(pto::launch_prolog_idxq(qi_i32, q_norm_scale, w_idx_qb_scale, cos, sin, hadamard_q, t, q_int8_out, q_scale_out,
-                                   stream));
+                                   side));
+  PTO_CUDA(cudaEventRecord(ev[2], side));
+  PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream));
   // absorbed nope part: per head [t, 128] (row stride 128*192, head stride 192) @ w_uk[head] [128, 512] -> bf16
   {
     const float one = 1.f, zero = 0.f;
@@ -686,6 +705,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
                                  CUDA_R_16BF, 128 * 192, 192LL, &zero, query_nope_out, CUDA_R_16BF, 128 * 512, 512LL, 128,
                                  CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
   }
+  PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));  // join: everything is ordered before what the caller enqueues next
   return PTO_OK;
 }
 
