@@ -204,12 +204,65 @@ def run_prolog_stage(args, dev):
                       "status": pto.workspace_status(dev)[0]}), flush=True)
 
 
+def run_layer_stage(args, dev):
+    """Profiling aid: what one decoder layer runs of this path per step - the prolog on the new tokens' hidden
+    states, then indexer -> top-2048 -> sparse attention on the prolog's outputs and the caches it has just
+    updated - recorded into one CUDA graph and replayed. Caches hold random rows; --ctx keys per sequence."""
+    import pypto_b200 as pto
+
+    act = [args.ctx] * args.batch
+    p = gen.make_prolog_inputs(act, s1=args.s1, seed=4321, device=dev)
+    t, rows = args.batch * args.s1, p["kv_cache"].shape[0]
+    q_nope = torch.zeros(t, 128, 512, dtype=torch.bfloat16, device=dev)
+    q_rope = torch.zeros(t, 128, 64, dtype=torch.bfloat16, device=dev)
+    q_i8 = torch.zeros(t, 64, 128, dtype=torch.int8, device=dev)
+    q_sc = torch.zeros(t, 64, 1, dtype=torch.float16, device=dev)
+    w = torch.zeros(t, 64, dtype=torch.float16, device=dev)
+    names = ["token_x", "w_dq", "w_uqqr", "w_qb_scale", "w_uk", "w_dkvkr", "gamma_cq", "gamma_ckv", "cos", "sin",
+             "cache_index", "kv_cache", "kr_cache", "kv_scale_cache", "w_idx_qb", "w_idx_qb_scale", "w_idx_k",
+             "w_idx_proj", "ln_gamma", "ln_beta", "hadamard_q", "hadamard_k", "idx_k_cache", "idx_k_scale_cache"]
+    pro_args = [p[n] for n in names] + [q_nope, q_rope, p["kv_cache"], p["kr_cache"], p["kv_scale_cache"], q_i8, q_sc,
+                                        p["idx_k_cache"], p["idx_k_scale_cache"], w, 1e-5, 1e-5, "PA_BSND", None, None,
+                                        None, None]
+    act_t = torch.tensor(act, dtype=torch.int32, device=dev)
+    topk = torch.zeros(t, 1, 2048, dtype=torch.int32, device=dev)
+    out = torch.zeros(args.batch, args.s1, 128, 512, dtype=torch.bfloat16, device=dev)
+    # the indexer reads its key scales in the dtype of the query scales: fp16 here, as the prolog writes them
+    dec_args = [q_i8, q_sc.reshape(t, 64), p["idx_k_cache"].reshape(rows // 128, 128, 1, 128),
+                p["idx_k_scale_cache"].reshape(rows // 128, 128, 1), w, q_nope.reshape(t * 128, 512),
+                q_rope.reshape(t * 128, 64), p["kv_cache"], p["kr_cache"], p["kv_scale_cache"], act_t, p["block_table"],
+                topk, out]
+
+    def layer(_out):
+        pto.mla_indexer_prolog_quant_d(*pro_args)
+        pto.decode_indexer_attention_quant(*dec_args)
+
+    captured = pto.CapturedCall(layer, out)
+    for _ in range(args.warmup):
+        captured.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        captured.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / max(args.steps, 1)
+    print(json.dumps({"stage": "layer", "batch": args.batch, "ctx": args.ctx, "s1": args.s1, "ms": ms,
+                      "tokens_per_s": t / ms * 1e3, "gpu_launches_per_step": 12,
+                      "l2": "caches larger than L2; the 100 MB of weights may stay in L2 between replays",
+                      "status": pto.workspace_status(dev)[0], "finite": bool(torch.isfinite(out.float()).all())}),
+          flush=True)
+
+
 def run_stage(args, dev):
     """Profiling aid: one stage alone on a uniform synthetic case, timed with CUDA events."""
     import pypto_b200 as pto
 
     if args.stage == "prolog":
         return run_prolog_stage(args, dev)
+    if args.stage == "layer":
+        return run_layer_stage(args, dev)
     d = gen.make_inputs([args.ctx] * args.batch, s1=args.s1, seed=4321, device=dev,
                         scale_dtype=getattr(torch, args.scale_dtype), with_topk=True)
     t = d.t
@@ -261,7 +314,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
-    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog"],
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

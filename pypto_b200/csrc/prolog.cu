@@ -93,28 +93,39 @@ prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, const __nv_bfloa
 }
 
 // ---- query up-projection: int32 -> bf16, rope of the 64-wide tail ----------------------------------------
-// grid = (heads, tokens), block = 192: one value per thread
-__global__ void __launch_bounds__(kQHead)
+// grid = (16 head groups, tokens), block = 256: eight heads (1536 values) per block
+constexpr int kQbHeadsPerBlock = 8;
+__global__ void __launch_bounds__(256)
 prolog_qb_dequant_rope_kernel(const int32_t* __restrict__ qb_i32, const float* __restrict__ q_norm_scale,
                               const float* __restrict__ w_scale, const __nv_bfloat16* __restrict__ cos,
                               const __nv_bfloat16* __restrict__ sin, __nv_bfloat16* __restrict__ q_b,
                               __nv_bfloat16* __restrict__ q_rope) {
-  __shared__ float pe[kRope];
-  const int h = blockIdx.x, ti = blockIdx.y, c = threadIdx.x;
-  const int64_t col = static_cast<int64_t>(h) * kQHead + c;
-  const int64_t off = static_cast<int64_t>(ti) * kHeads * kQHead + col;
-  const float v = bf16_round(__fmul_rn(__fmul_rn(static_cast<float>(qb_i32[off]), q_norm_scale[ti]), w_scale[col]));
-  q_b[off] = __float2bfloat16_rn(v);
-  if (c >= kNope) pe[c - kNope] = v;
+  __shared__ float pe[kQbHeadsPerBlock][kRope];
+  const int hg = blockIdx.x, ti = blockIdx.y;
+  const float rs = q_norm_scale[ti];
+  const int64_t col0 = static_cast<int64_t>(hg) * kQbHeadsPerBlock * kQHead;
+  const int64_t row0 = static_cast<int64_t>(ti) * kHeads * kQHead;
+#pragma unroll
+  for (int u = 0; u < kQbHeadsPerBlock * kQHead / 256; ++u) {
+    const int e = u * 256 + threadIdx.x;  // element of the block's 8 x 192 slice
+    const int64_t col = col0 + e;
+    const float v = bf16_round(__fmul_rn(__fmul_rn(static_cast<float>(qb_i32[row0 + col]), rs), w_scale[col]));
+    q_b[row0 + col] = __float2bfloat16_rn(v);
+    const int hh = e / kQHead, c = e % kQHead;
+    if (c >= kNope) pe[hh][c - kNope] = v;
+  }
   __syncthreads();
-  if (c < kRope) {
+#pragma unroll
+  for (int u = 0; u < kQbHeadsPerBlock * kRope / 256; ++u) {
+    const int e = u * 256 + threadIdx.x;
+    const int hh = e / kRope, c = e % kRope;
     // de-interleaved layout: first half = even dims, second half = odd dims; rotate_half = (-second, first)
     const int j = c & 31;
-    const float even = pe[2 * j], odd = pe[2 * j + 1];
+    const float even = pe[hh][2 * j], odd = pe[hh][2 * j + 1];
     const float cs = ld_bf16(cos + ti * kRope + c), sn = ld_bf16(sin + ti * kRope + c);
     const float x = c < 32 ? even : odd;
     const float rot = c < 32 ? -odd : even;
-    q_rope[(static_cast<int64_t>(ti) * kHeads + h) * kRope + c] =
+    q_rope[(static_cast<int64_t>(ti) * kHeads + hg * kQbHeadsPerBlock + hh) * kRope + c] =
         __float2bfloat16_rn(__fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn)));
   }
 }
@@ -296,7 +307,7 @@ cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
                                           const void* cos, const void* sin, int t, void* q_b, void* q_rope,
                                           cudaStream_t stream) {
-  prolog_qb_dequant_rope_kernel<<<dim3(kHeads, t), kQHead, 0, stream>>>(
+  prolog_qb_dequant_rope_kernel<<<dim3(kHeads / kQbHeadsPerBlock, t), 256, 0, stream>>>(
       qb_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_b),
       reinterpret_cast<__nv_bfloat16*>(q_rope));
