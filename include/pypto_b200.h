@@ -204,6 +204,13 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
  * ------------------------------------------------------------------------------------------ */
 size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora);
 
+/* The packed cache format as the native one: converts the three split arrays (int8 [n_rows, 512], bf16
+ * [n_rows, 64], f32 [n_rows, 4]) into the 656-byte rows `pto_sfa_packed` reads (packing of
+ * deepseekv32_sparse_attention_antiquant.py:258-268); afterwards the prolog keeps the packed cache current
+ * through its `packed_kv_cache` argument. */
+int pto_kv_pack_rows(const int8_t* key_nope_2d, const void* key_rope_2d, const float* k_nope_scales,
+                     int64_t n_rows, int8_t* nope_cache, pto_stream_t stream);
+
 /* Optional one-time weight preparation (the counterpart of the reference's cast of these weights to its
  * NZ format, deepseekv32_mla_indexer_prolog_quant.py:696-698, :721-725): the four projections of the token
  * share their left operand, so their weights are laid side by side, packed bf16
@@ -221,6 +228,7 @@ int pto_mla_indexer_prolog_quant(
     const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache, void* query_nope_out,
     void* query_rope_out, int8_t* q_int8_out, void* q_scale_out, void* weights_out,
     const void* w_x_packed /* from pto_prolog_pack_weights, or NULL: four separate products */,
+    int8_t* packed_kv_cache /* int8 [cache_rows, 656] or NULL: the token's row is also written there */,
     int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
     void* workspace, size_t workspace_bytes, pto_stream_t stream);
 

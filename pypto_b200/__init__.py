@@ -8,7 +8,7 @@ _OPS = (
     "lightning_indexer_decode", "lightning_indexer_scores", "lightning_indexer_topk",
     "sparse_flash_attention_quant_d", "sparse_flash_attention_quant_p",
     "sparse_attention_antiquant_d", "sparse_attention_antiquant_p",
-    "mla_indexer_prolog_quant_d", "mla_indexer_prolog_quant_p",
+    "mla_indexer_prolog_quant_d", "mla_indexer_prolog_quant_p", "pack_kv_cache",
     "decode_indexer_attention_quant", "workspace_status", "reset_workspace_status",
 )
 

@@ -591,6 +591,19 @@ size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora) {
   return prolog_ws(t, q_lora).total;
 }
 
+int pto_kv_pack_rows(const int8_t* key_nope_2d, const void* key_rope_2d, const float* k_nope_scales, int64_t n_rows,
+                     int8_t* nope_cache, pto_stream_t stream) {
+  PTO_REQUIRE(key_nope_2d && key_rope_2d && k_nope_scales && nope_cache, "null tensor pointer");
+  PTO_REQUIRE(n_rows >= 1, "n_rows");
+  PTO_REQUIRE(aligned16(key_nope_2d) && aligned16(key_rope_2d) && aligned16(k_nope_scales) && aligned16(nope_cache),
+              "cache tensors must be 16-byte aligned");
+  DeviceInfo di;
+  const int rc = get_device_info(&di);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_kv_pack_rows(key_nope_2d, key_rope_2d, k_nope_scales, n_rows, nope_cache, di.num_sms, stream));
+  return PTO_OK;
+}
+
 int pto_prolog_pack_weights(const void* w_dq, const void* w_dkvkr, const void* w_idx_k, const void* w_idx_proj, int hidden,
                             int q_lora, void* packed, pto_stream_t stream) {
   PTO_REQUIRE(w_dq && w_dkvkr && w_idx_k && w_idx_proj && packed, "null tensor pointer");
@@ -615,7 +628,8 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
                                  const void* ln_gamma, const void* ln_beta, const void* hadamard_q,
                                  const void* hadamard_k, int8_t* idx_k_cache, void* idx_k_scale_cache,
                                  void* query_nope_out, void* query_rope_out, int8_t* q_int8_out, void* q_scale_out,
-                                 void* weights_out, const void* w_x_packed, int t, int hidden, int q_lora,
+                                 void* weights_out, const void* w_x_packed, int8_t* packed_kv_cache, int t, int hidden,
+                                 int q_lora,
                                  int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps, void* workspace,
                                  size_t workspace_bytes, pto_stream_t stream) {
   PTO_REQUIRE(token_x && w_dq && w_uqqr && w_qb_scale && w_uk && w_dkvkr && gamma_cq && gamma_ckv && cos && sin &&
@@ -628,6 +642,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   PTO_REQUIRE(q_lora >= 16 && q_lora % 16 == 0 && q_lora <= 12288, "q_lora %d must be a multiple of 16, at most 12288",
               q_lora);
   PTO_REQUIRE(cache_rows >= 1, "cache_rows");
+  PTO_REQUIRE(packed_kv_cache == nullptr || aligned16(packed_kv_cache), "packed_kv_cache must be 16-byte aligned");
   PTO_REQUIRE(eps_cq >= 0.f && eps_ckv >= 0.f && ln_eps >= 0.f, "negative epsilon");
   PTO_REQUIRE(aligned16(token_x) && aligned16(w_dq) && aligned16(w_uqqr) && aligned16(w_uk) && aligned16(w_dkvkr) &&
                   aligned16(w_idx_qb) && aligned16(w_idx_k) && aligned16(w_idx_proj) && aligned16(kv_cache) &&
@@ -683,7 +698,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   PTO_CUDA(cudaStreamWaitEvent(side, ev[0], 0));
   PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, ld, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
                                  t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
-                                 weights_out, status, side));
+                                 weights_out, packed_kv_cache, status, side));
   PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
   // int8 up-projections of the normalised query
   const int tp = prolog_int8_rows(t);

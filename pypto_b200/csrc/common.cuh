@@ -317,7 +317,10 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
                              const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
-                             void* idx_k_scale_cache, void* weights, int32_t* status, cudaStream_t stream);
+                             void* idx_k_scale_cache, void* weights, int8_t* packed_cache, int32_t* status,
+                             cudaStream_t stream);
+cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* sc, int64_t rows, int8_t* packed,
+                                int num_sms, cudaStream_t stream);
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,
                                const void* sin, const void* hadamard_q, int t, int8_t* q_int8, void* q_scale,
                                cudaStream_t stream);

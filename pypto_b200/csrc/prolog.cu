@@ -20,6 +20,7 @@ constexpr int kLora = 512;      // latent KV width
 constexpr int kIdxHeads = 64;   // indexer heads
 constexpr int kIdxDim = 128;    // indexer head width
 constexpr int kQHead = kNope + kRope;
+constexpr int kPackedRow = kLora + 2 * kRope + 16;  // 656 bytes: int8 latent | bf16 rope | 4 fp32 scales
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float ld_bf16(const __nv_bfloat16* p) { return __bfloat162float(*p); }
@@ -140,7 +141,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
                  const int64_t* __restrict__ cache_index, int64_t cache_rows, float eps_ckv, float ln_eps,
                  int8_t* __restrict__ kv_cache, __nv_bfloat16* __restrict__ kr_cache, float* __restrict__ kv_scale_cache,
                  int8_t* __restrict__ idx_k_cache, __half* __restrict__ idx_k_scale_cache, __half* __restrict__ weights,
-                 int32_t* status) {
+                 int8_t* __restrict__ packed_cache, int32_t* status) {
   __shared__ float red[32];
   __shared__ float pe[kRope];
   __shared__ float kvec[kIdxDim];
@@ -181,7 +182,12 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
     q.z = quant_one(v[2], scale_q);
     q.w = quant_one(v[3], scale_q);
     *reinterpret_cast<char4*>(kv_cache + row * kLora + 4 * i) = q;
-    if (lane == 0) kv_scale_cache[row * 4 + warp] = __fdiv_rn(1.0f, scale_q);
+    const float dq = __fdiv_rn(1.0f, scale_q);
+    if (lane == 0) kv_scale_cache[row * 4 + warp] = dq;
+    if (packed_cache != nullptr) {  // the same row in the packed layout: 512 int8 | 64 bf16 | 4 f32
+      *reinterpret_cast<char4*>(packed_cache + row * kPackedRow + 4 * i) = q;
+      if (lane == 0) *reinterpret_cast<float*>(packed_cache + row * kPackedRow + kLora + 2 * kRope + 4 * warp) = dq;
+    }
   }
 
   // rope key: the 64 values after the latent part, de-interleaved rope
@@ -193,7 +199,9 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
     const float cs = ld_bf16(cos + ti * kRope + i), sn = ld_bf16(sin + ti * kRope + i);
     const float x = i < 32 ? even : odd;
     const float rot = i < 32 ? -odd : even;
-    kr_cache[row * kRope + i] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn)));
+    const __nv_bfloat16 kr = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn)));
+    kr_cache[row * kRope + i] = kr;
+    if (packed_cache != nullptr) *reinterpret_cast<__nv_bfloat16*>(packed_cache + row * kPackedRow + kLora + 2 * i) = kr;
   }
 
   // indexer key: LayerNorm in fp32 -> bf16, rope on the first 64 dims (halves, no de-interleave), Hadamard, int8
@@ -295,7 +303,29 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
   }
 }
 
+// ---- split caches -> packed 656-byte rows: one warp per row, 41 16-byte pieces ----------------------------
+__global__ void __launch_bounds__(256)
+kv_pack_rows_kernel(const int8_t* __restrict__ kv, const __nv_bfloat16* __restrict__ kr, const float* __restrict__ sc,
+                    int64_t rows, int8_t* __restrict__ packed) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    uint4* dst = reinterpret_cast<uint4*>(packed + r * kPackedRow);
+    dst[lane] = __ldg(reinterpret_cast<const uint4*>(kv + r * kLora) + lane);
+    if (lane < 8) dst[32 + lane] = __ldg(reinterpret_cast<const uint4*>(kr + r * kRope) + lane);
+    if (lane == 8) dst[40] = __ldg(reinterpret_cast<const uint4*>(sc + r * 4));
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* sc, int64_t rows, int8_t* packed,
+                                int num_sms, cudaStream_t stream) {
+  const int64_t want = (rows + 7) / 8;
+  const int grid = static_cast<int>(want < static_cast<int64_t>(num_sms) * 8 ? (want < 1 ? 1 : want) : num_sms * 8);
+  kv_pack_rows_kernel<<<grid, 256, 0, stream>>>(kv, reinterpret_cast<const __nv_bfloat16*>(kr), sc, rows, packed);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
                                       int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
@@ -318,13 +348,14 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
                              const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
-                             void* idx_k_scale_cache, void* weights, int32_t* status, cudaStream_t stream) {
+                             void* idx_k_scale_cache, void* weights, int8_t* packed_cache, int32_t* status,
+                             cudaStream_t stream) {
   prolog_kv_kernel<<<t, 128, 0, stream>>>(
       kv, ki, wp, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(ln_gamma),
       reinterpret_cast<const __nv_bfloat16*>(ln_beta), reinterpret_cast<const __nv_bfloat16*>(hadamard_k), cache_index,
       cache_rows, eps_ckv, ln_eps, kv_cache, reinterpret_cast<__nv_bfloat16*>(kr_cache), kv_scale_cache, idx_k_cache,
-      reinterpret_cast<__half*>(idx_k_scale_cache), reinterpret_cast<__half*>(weights), status);
+      reinterpret_cast<__half*>(idx_k_scale_cache), reinterpret_cast<__half*>(weights), packed_cache, status);
   return cudaGetLastError();
 }
 

@@ -340,7 +340,7 @@ def _mla_indexer_prolog_quant(token_x, mla_w_dq, mla_w_uq_qr, mla_dequant_scale,
                               mla_query_rope_out, mla_kv_cache_out, mla_kr_cache_out, mla_k_scale_cache_out,
                               ip_q_int8_out, ip_q_scale_out, ip_k_int8_out, ip_k_scale_out, ip_weights_out,
                               mla_epsilon_cq, mla_epsilon_ckv, mla_cache_mode="PA_BSND", mla_tile_config=None,
-                              ip_attrs=None, ip_configs=None, rope_cfg=None):
+                              ip_attrs=None, ip_configs=None, rope_cfg=None, *, packed_kv_cache=None):
     bf, i8, f32, f16 = torch.bfloat16, torch.int8, torch.float32, torch.float16
     x = unwrap(token_x, "token_x")
     _need(x.dtype == bf and x.dim() == 2, "token_x: bfloat16 [t, h]")
@@ -392,14 +392,19 @@ def _mla_indexer_prolog_quant(token_x, mla_w_dq, mla_w_uq_qr, mla_dequant_scale,
     tensors = [x, w_dq, w_uqqr, w_qb_scale, w_uk, w_dkvkr, g_cq, g_ckv, cos_t, sin_t, ci, kv, kr, ks, w_idx_qb,
                w_idx_qb_scale, w_idx_k, w_idx_proj, ln_g, ln_b, had_q, had_k, ik, iks, q_nope, q_rope, q_i8, q_sc,
                w_out]
-    dev = _same_device(tensors)
+    pk = None
+    if packed_kv_cache is not None:
+        pk = unwrap(packed_kv_cache, "packed_kv_cache")
+        _need(pk.dtype == i8 and pk.numel() == rows * 656, "packed_kv_cache: int8 [block_num*block_size, 656]")
+    dev = _same_device(tensors + ([pk] if pk is not None else []))
     lib = _lib.load()
     nbytes = lib.pto_prolog_workspace_bytes(t, h, q_lora)
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         packed = _packed_x_weights(lib, dev, w_dq, w_dkvkr, w_idx_k, w_idx_proj, h, q_lora)
         _lib.check(lib.pto_mla_indexer_prolog_quant(*[v.data_ptr() for v in tensors],
-                                                    packed.data_ptr() if packed is not None else None, t, h, q_lora, rows,
+                                                    packed.data_ptr() if packed is not None else None,
+                                                    pk.data_ptr() if pk is not None else None, t, h, q_lora, rows,
                                                     float(mla_epsilon_cq), float(mla_epsilon_ckv), ln_eps,
                                                     ws.data_ptr(), ws.numel(),
                                                     torch.cuda.current_stream(dev).cuda_stream))
@@ -410,7 +415,9 @@ def mla_indexer_prolog_quant_d(*args, **kwargs):
     """Decode entry of the fused MLA + indexer prolog; positional signature of the reference
     (mla_indexer_prolog_quant_impl.py:142-256): 24 inputs, 10 outputs (the five caches are updated in
     place), then mla_epsilon_cq, mla_epsilon_ckv, mla_cache_mode, mla_tile_config, ip_attrs, ip_configs,
-    rope_cfg. The tiling objects are accepted and not read; `ip_attrs.eps` is the LayerNorm epsilon."""
+    rope_cfg. The tiling objects are accepted and not read; `ip_attrs.eps` is the LayerNorm epsilon.
+    Not in the reference: keyword `packed_kv_cache` (int8 [rows, 656]) also receives the token's row in the
+    packed layout `sparse_attention_antiquant_d/_p` read."""
     return _mla_indexer_prolog_quant(*args, **kwargs)
 
 
@@ -418,6 +425,22 @@ def mla_indexer_prolog_quant_p(*args, **kwargs):
     """Prefill entry: the same arithmetic and kernels (the reference differs in scheduling options only,
     mla_indexer_prolog_quant_impl.py:37-139)."""
     return _mla_indexer_prolog_quant(*args, **kwargs)
+
+
+def pack_kv_cache(key_nope_2d, key_rope_2d, k_nope_scales, nope_cache):
+    """Split latent cache -> packed 656-byte rows (int8 latent | bf16 rope | 4 fp32 scales), on the device."""
+    kn, kr, sc, out = (unwrap(x, n) for x, n in ((key_nope_2d, "key_nope_2d"), (key_rope_2d, "key_rope_2d"),
+                                                 (k_nope_scales, "k_nope_scales"), (nope_cache, "nope_cache")))
+    _need(kn.dtype == torch.int8 and kn.numel() % 512 == 0, "key_nope_2d: int8 [rows, 512]")
+    rows = kn.numel() // 512
+    _need(kr.dtype == torch.bfloat16 and kr.numel() == rows * 64, "key_rope_2d: bfloat16 [rows, 64]")
+    _need(sc.dtype == torch.float32 and sc.numel() == rows * 4, "k_nope_scales: float32 [rows, 4]")
+    _need(out.dtype == torch.int8 and out.numel() == rows * 656, "nope_cache: int8 [rows, 656]")
+    dev = _same_device([kn, kr, sc, out])
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_kv_pack_rows(kn.data_ptr(), kr.data_ptr(), sc.data_ptr(), rows, out.data_ptr(),
+                                                torch.cuda.current_stream(dev).cuda_stream))
+    return None
 
 
 def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, query_nope,

@@ -167,3 +167,46 @@ def test_bad_cache_index_is_reported_not_written():
         run_prolog(p)  # the status word is non-zero
     assert pto.workspace_status()[0] & 1
     pto.reset_workspace_status()
+
+
+def test_packed_cache_is_kept_current_by_the_prolog():
+    """The 656-byte row format as the native cache: converted once on the device, then written by the prolog
+    next to the split arrays; the packed-row attention operator reads it and agrees with the split-array one."""
+    act = [700, 2300, 129]
+    p = gen.make_prolog_inputs(act, s1=1, seed=31)
+    g = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+    rows = g["kv_cache"].shape[0]
+    packed = torch.zeros(rows, 656, dtype=torch.int8, device=DEV)
+    pto.pack_kv_cache(g["kv_cache"], g["kr_cache"], g["kv_scale_cache"], packed)
+    assert torch.equal(packed.cpu(), gen.pack_kv_rows(p["kv_cache"], p["kr_cache"], p["kv_scale_cache"]))
+    t = len(act)
+    q_nope = torch.zeros(t, 128, 512, dtype=torch.bfloat16, device=DEV)
+    q_rope = torch.zeros(t, 128, 64, dtype=torch.bfloat16, device=DEV)
+    q_i8 = torch.zeros(t, 64, 128, dtype=torch.int8, device=DEV)
+    q_sc = torch.zeros(t, 64, 1, dtype=torch.float16, device=DEV)
+    w = torch.zeros(t, 64, dtype=torch.float16, device=DEV)
+    pto.mla_indexer_prolog_quant_d(
+        g["token_x"], g["w_dq"], g["w_uqqr"], g["w_qb_scale"], g["w_uk"], g["w_dkvkr"], g["gamma_cq"], g["gamma_ckv"],
+        g["cos"], g["sin"], g["cache_index"], g["kv_cache"], g["kr_cache"], g["kv_scale_cache"], g["w_idx_qb"],
+        g["w_idx_qb_scale"], g["w_idx_k"], g["w_idx_proj"], g["ln_gamma"], g["ln_beta"], g["hadamard_q"], g["hadamard_k"],
+        g["idx_k_cache"], g["idx_k_scale_cache"], q_nope, q_rope, g["kv_cache"], g["kr_cache"], g["kv_scale_cache"],
+        q_i8, q_sc, g["idx_k_cache"], g["idx_k_scale_cache"], w, 1e-5, 1e-5, "PA_BSND", None, None, None, None,
+        packed_kv_cache=packed)
+    torch.cuda.synchronize()
+    assert pto.workspace_status()[0] == 0
+    assert not torch.equal(g["kv_cache"].cpu(), p["kv_cache"])  # the new rows were written
+    assert torch.equal(packed.cpu(), gen.pack_kv_rows(g["kv_cache"].cpu(), g["kr_cache"].cpu(), g["kv_scale_cache"].cpu()))
+    # attention over the packed rows = attention over the split arrays
+    gsel = torch.Generator().manual_seed(5)
+    topk = gen.random_topk_indices(act, 1, gsel).to(DEV)
+    act_t = torch.tensor(act, dtype=torch.int32, device=DEV)
+    bt = g["block_table"]
+    o1 = torch.zeros(t, 1, 128, 512, dtype=torch.bfloat16, device=DEV)
+    o2 = torch.zeros_like(o1)
+    pto.sparse_attention_antiquant_d(q_nope.reshape(-1, 512), q_rope.reshape(-1, 64), packed, topk, bt, act_t, o1, 128, 1,
+                                     576 ** -0.5, 2048, 128, bt.shape[1])
+    pto.sparse_flash_attention_quant_d(q_nope.reshape(-1, 512), q_rope.reshape(-1, 64), g["kv_cache"], g["kr_cache"],
+                                       g["kv_scale_cache"], topk, bt, act_t, o2, 128, 1, 576 ** -0.5, 2048, 128,
+                                       bt.shape[1])
+    torch.cuda.synchronize()
+    assert torch.equal(o1, o2) and float(o1.float().abs().max()) > 0
