@@ -220,7 +220,7 @@ enum { kSfaSplitInt8 = 0, kSfaPackedInt8 = 1, kSfaSplitBf16 = 2 };
 int run_sfa(const void* qn, const void* qr, const void* kn, const void* kr, const float* sc, int layout,
             const int32_t* topk_idx, const int32_t* bt, const int32_t* act, void* out, int b, int s1, int nq, int n_kv,
             float softmax_scale, int topk, int block_size, int64_t n_rows, int max_blocks, int nq_total, int head_begin,
-            uint8_t* part_base, size_t part_bytes, int32_t* status, cudaStream_t stream) {
+            uint8_t* part_base, size_t part_bytes, int32_t* status, cudaStream_t stream, int behind_topk = 0) {
   PTO_REQUIRE(qn && qr && kn && topk_idx && bt && act && out, "null tensor pointer");
   const bool packed = layout == kSfaPackedInt8, bf16 = layout == kSfaSplitBf16;
   PTO_REQUIRE(packed || (kr && (sc || bf16)), "null tensor pointer");
@@ -269,6 +269,7 @@ int run_sfa(const void* qn, const void* qr, const void* kn, const void* kr, cons
   p.n_split = ns;
   p.packed = packed ? 1 : 0;
   p.kn_bf16 = bf16 ? 1 : 0;
+  p.pdl = behind_topk;
   p.n_rows = n_rows;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
@@ -754,7 +755,7 @@ int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const
   if (rc != PTO_OK) return rc;
   return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, 0, topk_res, block_table, act_seq,
                  attention_out, b, s1, nq, 1, softmax_scale, selected_count, 128, static_cast<int64_t>(block_num) * 128,
-                 max_blocks, nq, 0, part, sfa_part_bytes(b * s1, nq), status, stream);
+                 max_blocks, nq, 0, part, sfa_part_bytes(b * s1, nq), status, stream, /*behind_topk=*/1);
 }
 
 }  // extern "C"

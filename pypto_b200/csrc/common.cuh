@@ -73,6 +73,15 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream still runs; `pdl_wait` blocks until that predecessor has completed and
+// its writes are visible (a no-op in a kernel launched the ordinary way). `pdl_trigger` lets the successor
+// start early. Rule kept throughout: a kernel triggers only after its own wait, and the first kernel of a
+// chain is launched the ordinary way, so a successor that is running implies that everything before the
+// chain has completed.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Bounded wait: gives up after ~`kWaitBudgetCycles` SM clocks and returns false. Every spin in the
 // library goes through this, so a protocol error turns into a status word, not a hang.
 constexpr long long kWaitBudgetCycles = 2000000000LL;  // about one second at 2 GHz
@@ -294,6 +303,7 @@ struct SfaParams {
   float* part_o;                // [t, n_split, nq, 512]
   float* part_ml;               // [t, n_split, nq, 2]
   int b, s1, nq, nq_total, head_begin, topk_k, block_size, max_blocks, n_split, packed, kn_bf16;
+  int pdl;  // launched behind the top-k kernel with programmatic serialization: setup overlaps the selection
   int64_t n_rows;
   float scale_log2;  // softmax_scale * log2(e)
   int32_t* status;

@@ -103,6 +103,9 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  // this kernel is launched the ordinary way (everything before it has completed); the top-k kernel behind it
+  // may be scheduled as soon as SMs drain and waits there for this grid to complete
+  if (tid == 0) pdl_trigger();
   const int s1 = p.s1;
   const int n_cols = kHeads * s1;                                // accumulator columns per page
   const uint32_t n_slots = min(kLiSlots, kTmemCols / n_cols);   // 8, 4, 2, 2 for s1 = 1..4

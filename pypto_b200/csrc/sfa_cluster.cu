@@ -587,6 +587,7 @@ __device__ __forceinline__ void cl_role_producer(const SfaParams& p, const ClCtx
   const int rsw = (row >> 1) & 3;
   bool ok = true;
   RowRegs ra;
+  pdl_wait();          // the selected indices come from the kernel before this one, which may still be running
   long long row_n;     // row of tile j+1
   int idx_a, entry_a;  // tile j+2
   int idx_b;           // tile j+3
@@ -860,13 +861,17 @@ cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream) {
   cfg.blockDim = dim3(kClThreads, 1, 1);
   cfg.dynamicSmemBytes = kClSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // behind the top-k kernel of the fused chain: tensor-memory allocation, barrier set-up and the copy of Q run
+  // while the selection finishes; only the producers read its output, and they wait first
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 

@@ -249,6 +249,9 @@ __global__ void __launch_bounds__(kTopkThreads, 1)
 li_topk_kernel(TopkParams p) {
   extern __shared__ __align__(16) uint8_t topk_smem_raw[];
   TopkSmem* sm = reinterpret_cast<TopkSmem*>(topk_smem_raw);
+  // launched with programmatic serialization: the score kernel before it may still be running
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const unsigned int csize = cluster_size();
@@ -490,13 +493,16 @@ cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream
   cfg.blockDim = dim3(kTopkThreads, 1, 1);
   cfg.dynamicSmemBytes = sizeof(TopkSmem);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // may be scheduled while the kernel before it drains; it waits (first instruction) before it reads anything
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, li_topk_kernel, p);
 }
 

@@ -106,3 +106,31 @@ def test_tiling_dataclasses_are_accepted_and_inert():
     s = pto.SaTileShapeConfig(g_tile=128, s_kv_tile=2048, c1_tile_shape=[128] * 6, v1_tile_shape=[8, 2048],
                               c2_tile_shape=[128] * 6, v2_tile_shape=[64, 128])
     assert s.s_kv_tile == 2048
+
+
+def test_prolog_rejects_bad_arguments_before_any_launch():
+    p = gen.make_prolog_inputs([200], s1=1, seed=1)
+    t = 1
+    outs = [torch.zeros(t, 128, 512, dtype=torch.bfloat16), torch.zeros(t, 128, 64, dtype=torch.bfloat16),
+            p["kv_cache"], p["kr_cache"], p["kv_scale_cache"], torch.zeros(t, 64, 128, dtype=torch.int8),
+            torch.zeros(t, 64, 1, dtype=torch.float16), p["idx_k_cache"], p["idx_k_scale_cache"],
+            torch.zeros(t, 64, dtype=torch.float16)]
+    names = ["token_x", "w_dq", "w_uqqr", "w_qb_scale", "w_uk", "w_dkvkr", "gamma_cq", "gamma_ckv", "cos", "sin",
+             "cache_index", "kv_cache", "kr_cache", "kv_scale_cache", "w_idx_qb", "w_idx_qb_scale", "w_idx_k",
+             "w_idx_proj", "ln_gamma", "ln_beta", "hadamard_q", "hadamard_k", "idx_k_cache", "idx_k_scale_cache"]
+    tail = [1e-5, 1e-5, "PA_BSND", None, None, None, None]
+
+    def call(**over):
+        ins = [over.get(n, p[n]) for n in names]
+        return pto.mla_indexer_prolog_quant_d(*ins, *outs, *tail)
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        call()  # CPU tensors: there is no CPU path
+    with pytest.raises(ValueError, match="token_x"):
+        call(token_x=p["token_x"].float())
+    with pytest.raises(ValueError, match="mla_w_uq_qr"):
+        call(w_uqqr=p["w_uqqr"][:, :100].contiguous())
+    with pytest.raises(ValueError, match="cache_index"):
+        call(cache_index=p["cache_index"].to(torch.int32))
+    with pytest.raises(ValueError, match="PA_BSND"):
+        pto.mla_indexer_prolog_quant_d(*[p[n] for n in names], *outs, 1e-5, 1e-5, "BSND", None, None, None, None)
