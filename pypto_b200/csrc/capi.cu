@@ -109,6 +109,23 @@ int make_rows128_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t
   return PTO_OK;
 }
 
+// 2-D map over a byte matrix [outer, inner] (row pitch `pitch` bytes) with an [box_outer, box_inner] box and
+// 128-byte swizzle; box_inner must be 128.
+int make_bytes_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_outer) {
+  EncodeTiledFn enc;
+  int rc = get_encode_fn(&enc);
+  if (rc != PTO_OK) return rc;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {128, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PTO_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+  return PTO_OK;
+}
+
 size_t li_scores_bytes(int t, int max_blocks, int block_size) {
   return align_up(static_cast<size_t>(t) * max_blocks * block_size * sizeof(float), 256);
 }
@@ -701,12 +718,25 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
                                  t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
                                  weights_out, packed_kv_cache, status, side));
   PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
-  // int8 up-projections of the normalised query
+  // int8 up-projections of the normalised query: one tcgen05 weight-streaming launch for both when the token
+  // rows fit its resident activation buffer (decode), else two library products
   const int tp = prolog_int8_rows(t);
-  rc = gemm_rowmajor(h, tp, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
-  if (rc != PTO_OK) return rc;
-  rc = gemm_rowmajor(h, tp, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
-  if (rc != PTO_OK) return rc;
+  if (pto::prolog_i8_gemm_supported(t, q_lora)) {
+    alignas(64) CUtensorMap map_w0, map_w1, map_x;
+    rc = make_bytes_map(&map_w0, w_uqqr, 128 * 192, q_lora, 128 * 192, 128);
+    if (rc != PTO_OK) return rc;
+    rc = make_bytes_map(&map_w1, w_idx_qb, 64 * 128, q_lora, 64 * 128, 128);
+    if (rc != PTO_OK) return rc;
+    rc = make_bytes_map(&map_x, q_norm, q_lora, tp, q_lora, static_cast<uint32_t>((t + 15) / 16 * 16));
+    if (rc != PTO_OK) return rc;
+    PTO_CUDA(pto::launch_prolog_i8_gemm(&map_w0, &map_w1, &map_x, qb_i32, 128 * 192, qi_i32, 64 * 128, q_lora, t,
+                                        di.num_sms, status, stream));
+  } else {
+    rc = gemm_rowmajor(h, tp, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
+    if (rc != PTO_OK) return rc;
+    rc = gemm_rowmajor(h, tp, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
+    if (rc != PTO_OK) return rc;
+  }
   // the indexer-query kernel joins the side stream; the attention query finishes on the caller's
   PTO_CUDA(cudaEventRecord(ev[1], stream));
   PTO_CUDA(cudaStreamWaitEvent(side, ev[1], 0));

@@ -329,6 +329,10 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
                              void* idx_k_scale_cache, void* weights, int8_t* packed_cache, int32_t* status,
                              cudaStream_t stream);
+// both int8 up-projections of the prolog in one tcgen05 launch (prolog_gemm.cu); t <= 64 token rows
+bool prolog_i8_gemm_supported(int t, int k);
+cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, const void* tmap_x, int32_t* out0, int n0,
+                                  int32_t* out1, int n1, int k, int t, int num_sms, int32_t* status, cudaStream_t stream);
 cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* sc, int64_t rows, int8_t* packed,
                                 int num_sms, cudaStream_t stream);
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,
