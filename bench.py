@@ -279,6 +279,7 @@ def run_stage(args, dev):
                    ).reshape(-1, 512).to(torch.bfloat16)
     fns = {
         "li_score": lambda: pto.lightning_indexer_scores(*li, sc),
+        "li_score_chain": lambda: pto.lightning_indexer_scores(*li, sc, fp16_chain=True),  # needs --scale-dtype float16
         "li_decode": lambda: pto.lightning_indexer_decode(*li, idx, None, None, 2048),
         "topk": lambda: pto.lightning_indexer_topk(sc, d.act_seq_key, idx, s1=d.s1),
         "sfa": lambda: pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d,
@@ -317,7 +318,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
-    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer"],
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer", "li_score_chain"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

@@ -48,6 +48,10 @@ typedef struct CUstream_st* pto_stream_t; /* cudaStream_t */
 /* flags of the indexer entry points */
 #define PTO_LI_SCORE_SIMT 0x1 /* score stage on CUDA cores (dp4a) instead of tcgen05; validation aid */
 #define PTO_LI_UNSORTED 0x2   /* leave the selected indices unordered (default: value-descending) */
+#define PTO_LI_FP16_CHAIN 0x4 /* the older formulation of the score, LightningIndexerTopkImpl
+                               * (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:150-196):
+                               * fp16(dot * 2^-11), x q_scale, x k_scale, relu, x weight all in fp16, head sum in
+                               * fp32; scales and weights must be fp16 */
 
 /* device status area at the start of every workspace */
 #define PTO_STATUS_WORDS 8

@@ -59,6 +59,41 @@ def li_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weig
     return (rows_out, fm_out) if return_first_mm else rows_out
 
 
+def li_scores_fp16_chain(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq, block_table, s1):
+    """The older quantised formulation, `LightningIndexerTopkImpl`
+    (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:150-196; golden
+    `indexer_topk_compute(is_quant=True)`, framework/tests/st/operator/src/test_deepseek_v3.2_exp/
+    gen_lightning_indexer.py:243-257): everything between the int32 dot and the head sum stays in fp16,
+
+      h     = fp16( fp32(d) * 2^-11 )          (no relu yet)
+      a     = fp16( fp16(h * q_scale_h) * k_scale_key )
+      m     = fp16( relu(a) * weight_h )
+      score = sum_h fp32(m)
+
+    with fp16 scales and weights. Same return value as `li_scores`."""
+    t, n_heads, dim = idx_query.shape
+    block_num, block_size = idx_key_cache.shape[0], idx_key_cache.shape[1]
+    assert idx_query_scale.dtype == torch.float16 and idx_key_scale.dtype == torch.float16
+    assert idx_weight.dtype == torch.float16
+    keys2d = idx_key_cache.reshape(block_num * block_size, dim)
+    kscale1d = idx_key_scale.reshape(block_num * block_size)
+    b = len(act_seq)
+    rows_out = []
+    for bi in range(b):
+        seq = int(act_seq[bi])
+        k, rows = _gather_pages(keys2d, block_table[bi], seq, block_size)
+        kf = k.to(torch.float32)
+        ks = kscale1d[rows]  # fp16 [S]
+        for i in range(s1):
+            ti = bi * s1 + i
+            d = idx_query[ti].to(torch.float32) @ kf.T  # [64, S], exact integers
+            h = (d * (1.0 / 2048)).to(torch.float16)
+            a = (h * idx_query_scale[ti].reshape(-1, 1)) * ks.reshape(1, -1)  # two fp16 products, left to right
+            m = torch.relu(a) * idx_weight[ti].reshape(-1, 1)
+            rows_out.append(m.to(torch.float32).sum(dim=0))
+    return rows_out
+
+
 def li_topk(score_rows, act_seq, s1, selected_count=2048):
     """Exact top-k per row over the causal prefix; value-descending; -1 padding."""
     t = len(score_rows)
@@ -77,7 +112,8 @@ def li_topk(score_rows, act_seq, s1, selected_count=2048):
 
 
 def lightning_indexer(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq, block_table,
-                      s1, selected_count=2048):
-    rows = li_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq, block_table, s1)
+                      s1, selected_count=2048, fp16_chain=False):
+    fn = li_scores_fp16_chain if fp16_chain else li_scores
+    rows = fn(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq, block_table, s1)
     idx, vals = li_topk(rows, act_seq, s1, selected_count)
     return idx, vals, rows

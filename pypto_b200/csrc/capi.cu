@@ -185,6 +185,9 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
   p.status = status;
   const bool simt = (flags & PTO_LI_SCORE_SIMT) != 0;
   PTO_REQUIRE(simt || first_mm == nullptr, "first_mm is only produced with PTO_LI_SCORE_SIMT");
+  p.fp16_chain = (flags & PTO_LI_FP16_CHAIN) != 0 ? 1 : 0;
+  PTO_REQUIRE(!p.fp16_chain || scale_dtype == PTO_DT_F16, "PTO_LI_FP16_CHAIN needs fp16 scales and weights");
+  PTO_REQUIRE(!p.fp16_chain || first_mm == nullptr, "first_mm is not produced with PTO_LI_FP16_CHAIN");
   DeviceInfo di;
   CUtensorMap tmap_k, tmap_q;
   const int group = s1 < pto::li_max_s1() ? s1 : pto::li_max_s1();

@@ -276,6 +276,7 @@ struct LiParams {
   void* first_mm;           // optional f16 [t*64, row_stride] (SIMT path)
   int64_t row_stride;
   int b, s1, block_num, max_blocks;
+  int fp16_chain;  // PTO_LI_FP16_CHAIN: the older formulation of the score
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
   int32_t* status;

@@ -75,6 +75,26 @@ __device__ __forceinline__ float2 relu_scale_round(int d0, int d1) {
   return __half22float2(h);
 }
 
+// The older formulation for 32 heads of one key: table entries come in pairs, (q_scale_2p, q_scale_2p+1) and
+// (weight_2p, weight_2p+1) as half2 bit patterns; d * 2^-11 is exact by the same magic number as above.
+__device__ __forceinline__ float chain_sum_32(const uint32_t (&v)[32], const float* table, __half2 ks2) {
+  const uint32_t* tb = reinterpret_cast<const uint32_t*>(table);
+  float acc = 0.f;
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    const float f0 = __int_as_float(0x45C00000 + static_cast<int>(v[c])) - 6144.0f;
+    const float f1 = __int_as_float(0x45C00000 + static_cast<int>(v[c + 1])) - 6144.0f;
+    const uint32_t qs_bits = tb[c], w_bits = tb[c + 1];
+    const __half2 qs2 = *reinterpret_cast<const __half2*>(&qs_bits);
+    const __half2 w2 = *reinterpret_cast<const __half2*>(&w_bits);
+    __half2 a = __hmul2(__hmul2(__floats2half2_rn(f0, f1), qs2), ks2);
+    a = __hmax2(a, __float2half2_rn(0.0f));
+    const float2 m = __half22float2(__hmul2(a, w2));
+    acc = __fadd_rn(__fadd_rn(acc, m.x), m.y);
+  }
+  return acc;
+}
+
 __device__ __forceinline__ float weighted_sum_32(const uint32_t (&v)[32], const float* ws) {
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -90,6 +110,7 @@ __device__ __forceinline__ float weighted_sum_32(const uint32_t (&v)[32], const 
   return (a0 + a1) + (a2 + a3);
 }
 
+template <bool kChain>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q, LiParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -189,7 +210,16 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
       }
       const int e = tid - 32 * kLiEpilogueWarp0;
-      if (e >= 0 && e < s1 * kHeads) ctl->ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
+      if (e >= 0 && e < s1 * kHeads) {
+        if (kChain) {
+          // pairs of heads: even slot = the two query scales, odd slot = the two weights (fp16 bit patterns)
+          const __half* src = reinterpret_cast<const __half*>((e & 1) ? p.weight : p.q_scale) + tok0 * kHeads + (e & ~1);
+          const __half2 two = __halves2half2(src[0], src[1]);
+          reinterpret_cast<uint32_t*>(ctl->ws)[e] = *reinterpret_cast<const uint32_t*>(&two);
+        } else {
+          ctl->ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
+        }
+      }
     }
     __syncthreads();
 
@@ -296,7 +326,12 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[slot]));
               }
-              res[i] = (weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32)) * ks;
+              if (kChain) {
+                const __half2 ks2 = __half2half2(reinterpret_cast<const __half*>(sc_smem)[row]);
+                res[i] = __fadd_rn(chain_sum_32(v0, ctl->ws + i * kHeads, ks2), chain_sum_32(v1, ctl->ws + i * kHeads + 32, ks2));
+              } else {
+                res[i] = (weighted_sum_32(v0, ctl->ws + i * kHeads) + weighted_sum_32(v1, ctl->ws + i * kHeads + 32)) * ks;
+              }
             }
           }
           if (pos < seq_len) {
@@ -335,6 +370,7 @@ __global__ void __launch_bounds__(128)
 li_score_simt_kernel(LiParams p) {
   __shared__ __align__(16) int8_t qs[kMaxS1 * kQBytesPerToken];
   __shared__ float ws[kMaxS1 * kHeads];
+  __shared__ __half qsc[kMaxS1 * kHeads], wgt[kMaxS1 * kHeads];  // older formulation: scales and weights apart
   const int bi = blockIdx.y;
   const int page = blockIdx.x;
   const int seq_len = p.act_seq[bi];
@@ -347,7 +383,12 @@ li_score_simt_kernel(LiParams p) {
     int4* dst = reinterpret_cast<int4*>(qs);
     for (int i = tid; i < s1 * kQBytesPerToken / 16; i += blockDim.x) dst[i] = src[i];
     for (int e = tid; e < s1 * kHeads; e += blockDim.x) {
-      ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
+      if (p.fp16_chain) {
+        qsc[e] = reinterpret_cast<const __half*>(p.q_scale)[tok0 * kHeads + e];
+        wgt[e] = reinterpret_cast<const __half*>(p.weight)[tok0 * kHeads + e];
+      } else {
+        ws[e] = load_ws(p.q_scale, p.weight, p.scale_dtype, tok0 * kHeads + e);
+      }
     }
   }
   __syncthreads();
@@ -376,6 +417,13 @@ li_score_simt_kernel(LiParams p) {
         d = __dp4a(kreg[c].z, qv.z, d);
         d = __dp4a(kreg[c].w, qv.w, d);
       }
+      if (p.fp16_chain) {
+        const __half ksh = reinterpret_cast<const __half*>(p.k_scale)[static_cast<int64_t>(phys) * kPageKeys + tid];
+        __half a = __hmul(__hmul(__float2half_rn(static_cast<float>(d) * (1.0f / 2048.0f)), qsc[i * kHeads + h]), ksh);
+        a = __hmax(a, __float2half_rn(0.0f));
+        acc = __fadd_rn(acc, __half2float(__hmul(a, wgt[i * kHeads + h])));
+        continue;
+      }
       const float f = fmaxf(static_cast<float>(d), 0.f) * (1.0f / 2048.0f);
       const __half hh = __float2half_rn(f);
       if (p.first_mm != nullptr) {
@@ -383,7 +431,7 @@ li_score_simt_kernel(LiParams p) {
       }
       acc = fmaf(ws[i * kHeads + h], __half2float(hh), acc);
     }
-    p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = acc * ks;
+    p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = p.fp16_chain ? acc : acc * ks;
   }
 }
 
@@ -391,17 +439,14 @@ li_score_simt_kernel(LiParams p) {
 
 cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void* tmap_q, int num_sms,
                                cudaStream_t stream) {
-  static bool configured = false;  // attribute is per function, idempotent
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(li_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kLiSmemBytes));
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  auto kernel = p.fp16_chain ? li_score_tc_kernel<true> : li_score_tc_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kLiSmemBytes));
+  if (e != cudaSuccess) return e;
   long long max_items = static_cast<long long>(p.b) * p.max_blocks;
   int grid = static_cast<int>(max_items < num_sms ? max_items : num_sms);
   if (grid < 1) grid = 1;
-  li_score_tc_kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
+  kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_q), p);
   return cudaGetLastError();
 }

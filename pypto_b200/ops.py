@@ -110,8 +110,10 @@ def _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weigh
 
 def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
                              block_table, topk_res, unroll_list=None, configs=None, selected_count=2048, *,
-                             sort=True, _simt_scores=False):
-    """Top-`selected_count` key positions per query token (value-descending, -1 padded)."""
+                             sort=True, _simt_scores=False, fp16_chain=False):
+    """Top-`selected_count` key positions per query token (value-descending, -1 padded).
+    `fp16_chain=True` (not in the reference's Python signature) scores with the older formulation of
+    LightningIndexerTopkImpl, lightning_indexer.cpp:150-196 (fp16 scales and weights only)."""
     dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
                                                     idx_weight, act_seq_key, block_table)
     out = unwrap(topk_res, "topk_res")
@@ -122,6 +124,7 @@ def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_
     lib = _lib.load()
     nbytes = lib.pto_li_workspace_bytes(m["t"], m["max_blocks"], m["block_size"])
     flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_SCORE_SIMT if _simt_scores else 0)
+    flags |= _lib.PTO_LI_FP16_CHAIN if fp16_chain else 0
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         _lib.check(lib.pto_li_decode(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
@@ -133,7 +136,7 @@ def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_
 
 
 def lightning_indexer_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
-                             block_table, scores, first_mm=None, *, simt=False):
+                             block_table, scores, first_mm=None, *, simt=False, fp16_chain=False):
     """Score stage alone: fp32 [t, max_blocks*block_size] (the reference ST's `mm_out` hook);
     positions at or beyond a sequence's length are left untouched. `first_mm` (fp16
     [t*64, max_blocks*block_size]) is available with simt=True only."""
@@ -159,7 +162,9 @@ def lightning_indexer_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_
         _lib.check(lib.pto_li_scores(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
                                      m["scale_dtype"], act.data_ptr(), bt.data_ptr(), sc.data_ptr(), fm_ptr, m["b"],
                                      m["s1"], m["n_heads"], m["head_dim"], m["block_size"], m["block_num"],
-                                     m["max_blocks"], _lib.PTO_LI_SCORE_SIMT if simt else 0, ws.data_ptr(), ws.numel(),
+                                     m["max_blocks"],
+                                     (_lib.PTO_LI_SCORE_SIMT if simt else 0) | (_lib.PTO_LI_FP16_CHAIN if fp16_chain else 0),
+                                     ws.data_ptr(), ws.numel(),
                                      torch.cuda.current_stream(dev).cuda_stream))
     return None
 
@@ -446,7 +451,7 @@ def pack_kv_cache(key_nope_2d, key_rope_2d, k_nope_scales, nope_cache):
 def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, query_nope,
                                    query_rope, key_nope_2d, key_rope_2d, k_nope_scales, act_seq, block_table,
                                    topk_res, attention_out, nq=128, softmax_scale=576 ** -0.5, selected_count=2048, *,
-                                   sort=False):
+                                   sort=False, fp16_chain=False):
     """Fused chain: indexer score -> top-k -> sparse attention with the kernel's own indices.
     Both caches share `block_table` / `act_seq`. Writes `topk_res` and `attention_out`."""
     dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
@@ -466,7 +471,7 @@ def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, id
     dev = _same_device([q, qs, kc, ks, w, act, bt, qn, qr, kn, kr, sc, out_idx, out])
     lib = _lib.load()
     nbytes = lib.pto_decode_workspace_bytes(t, m["max_blocks"], 128, int(nq))
-    flags = 0 if sort else _lib.PTO_LI_UNSORTED
+    flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_FP16_CHAIN if fp16_chain else 0)
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         _lib.check(lib.pto_decode_fused(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),

@@ -118,6 +118,13 @@ def make_li(li_mod, st_mod, name, act_seq, s1, dt):
     topk = li_mod.lightning_indexer_compute(dict(data), params).reshape(d.t, 1, 2048)
     first_mm, mm_out, topk_value, topk2 = st_mod.lightning_indexer_compute(dict(data), params)
     assert torch.equal(topk.reshape(-1), topk2.reshape(-1).to(torch.int32)), "example and ST goldens disagree"
+    extra = {}
+    if dtype == torch.float16:
+        # the older formulation (fp16 chain between the dot and the head sum) on the same inputs: the ST golden
+        # of LightningIndexerTopkImpl, quantised branch
+        _, chain_topk, chain_rows = st_mod.indexer_topk_compute(dict(data), dict(params, n2=1), True)
+        extra = dict(chain_topk_res=chain_topk.reshape(d.t, 1, 2048).numpy().astype(np.int32),
+                     chain_rows=chain_rows.numpy().astype(np.float32))
     np.savez_compressed(
         HERE / f"{name}.npz",
         act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed), scale_dtype=dt,
@@ -126,6 +133,7 @@ def make_li(li_mod, st_mod, name, act_seq, s1, dt):
         mm_out=mm_out.numpy().astype(np.float32),
         first_mm_sha=sha(first_mm),
         first_mm_head0=first_mm.reshape(d.t, 64, -1)[:, 0, :].numpy(),
+        **extra,
     )
     print(name, "t", d.t, "blocks", d.block_num)
 

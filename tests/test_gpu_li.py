@@ -165,3 +165,43 @@ def test_rejected_page_sets_status_without_fault():
     assert st[0] & 0x1 and st[1] == d.block_num + 5
     pto.reset_workspace_status()
     assert pto.workspace_status()[0] == 0
+
+
+@pytest.mark.parametrize("name", [n for n in LI_CASES if n.endswith("f16")])
+@pytest.mark.parametrize("simt", [True, False], ids=["simt", "tcgen05"])
+def test_fp16_chain_formulation_matches_st_golden(name, simt):
+    """The older formulation (LightningIndexerTopkImpl, flag PTO_LI_FP16_CHAIN): scores against the ST golden's
+    quantised branch (every fp16 step reproduces exactly; the fp32 head sum is taken in another order), selected
+    sets exact on untied scores."""
+    d, z = load_case(name)
+    g = d.to(DEV)
+    stride = d.max_blocks * 128
+    sc = torch.full((d.t, stride), float("nan"), dtype=torch.float32, device=DEV)
+    pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                 g.act_seq_key, g.block_table, sc, None, simt=simt, fp16_chain=True)
+    torch.cuda.synchronize()
+    sc = sc.cpu()
+    want_rows = torch.from_numpy(z["chain_rows"])
+    rows = oracle.li_scores_fp16_chain(d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale, d.idx_weight,
+                                       d.act_seq, d.block_table, d.s1)
+    for bi in range(d.b):
+        for i in range(d.s1):
+            ti = bi * d.s1 + i
+            eff = d.act_seq[bi] - (d.s1 - 1 - i)
+            torch.testing.assert_close(sc[ti, :d.act_seq[bi]], rows[ti], rtol=3e-6, atol=1e-9)
+            if eff > 0:
+                torch.testing.assert_close(sc[ti, :eff], want_rows[ti, :eff], rtol=3e-6, atol=1e-9)
+    got = _decode(d, _simt_scores=simt, fp16_chain=True)
+    want = torch.from_numpy(z["chain_topk_res"])
+    for ti in range(d.t):
+        untied, _ = oracle.topk_set_diff(got[ti], want[ti], want_rows[ti])
+        assert untied == 0, f"row {ti}: {untied} untied differences"
+
+
+def test_fp16_chain_needs_fp16_scales():
+    d = gen.make_inputs([300], s1=1, seed=5, scale_dtype=torch.float32, with_attention=False)
+    g = d.to(DEV)
+    sc = torch.zeros((d.t, d.max_blocks * 128), dtype=torch.float32, device=DEV)
+    with pytest.raises(RuntimeError, match="fp16"):
+        pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                     g.act_seq_key, g.block_table, sc, None, fp16_chain=True)
