@@ -129,3 +129,38 @@ def test_empty_and_tiny_sequences():
                                    want_idx.reshape(d.t, 2048), d.block_table, d.act_seq, d.s1)
     e = oracle.attention_errors(out, want)
     assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, e
+
+
+@pytest.mark.parametrize("b,s1", [(3, 2), (64, 1), (70, 1)])
+def test_back_to_back_fused_calls_equal_the_stages_run_one_by_one(b, s1):
+    """Inside the fused call the top-k and attention kernels are launched with programmatic serialization (they
+    may start while their predecessor drains). Six calls without any synchronisation in between, a fill kernel
+    before each, must give the index sets of the stand-alone indexer and, for those indices, bit for bit the
+    output of the stand-alone attention operator."""
+    g0 = torch.Generator().manual_seed(b * 10 + s1)
+    choices = [1, 100, 2047, 2049, 5000, 9000, 20000, 40000]
+    act = [choices[int(torch.randint(0, len(choices), (1,), generator=g0))] for _ in range(b)]
+    d = gen.make_inputs(act, s1=s1, seed=900 + b, device=DEV)
+    li = (d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale, d.idx_weight)
+    reps = 6
+    idxs = [torch.full((d.t, 1, 2048), -7, dtype=torch.int32, device=DEV) for _ in range(reps)]
+    outs = [torch.full((d.b, d.s1, 128, 512), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(reps)]
+    junk = torch.empty(32 << 20, dtype=torch.uint8, device=DEV)
+    for r in range(reps):
+        junk.fill_(r)
+        pto.decode_indexer_attention_quant(*li, d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d,
+                                           d.k_nope_scales, d.act_seq_key, d.block_table, idxs[r], outs[r])
+    torch.cuda.synchronize()
+    assert pto.workspace_status()[0] == 0
+    idx_ref = torch.zeros_like(idxs[0])
+    pto.lightning_indexer_decode(*li, d.act_seq_key, d.block_table, idx_ref, None, None, 2048)
+    torch.cuda.synchronize()
+    want_sets = idx_ref.sort(dim=-1).values
+    for r in range(reps):
+        assert torch.equal(idxs[r].sort(dim=-1).values, want_sets)
+        out2 = torch.zeros_like(outs[r])
+        pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                           idxs[r].reshape(d.t, 2048), d.block_table, d.act_seq_key, out2, 128, 1,
+                                           576 ** -0.5, 2048, 128, d.max_blocks)
+        torch.cuda.synchronize()
+        assert torch.equal(out2, outs[r])
