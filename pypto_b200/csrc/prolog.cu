@@ -249,8 +249,9 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
                    const float* __restrict__ w_scale, const __nv_bfloat16* __restrict__ cos,
                    const __nv_bfloat16* __restrict__ sin, const __nv_bfloat16* __restrict__ hadamard_q,
                    int8_t* __restrict__ q_int8, __half* __restrict__ q_scale) {
-  __shared__ float red[32];
+  __shared__ float red8[4][kHeadsPerBlock];
   __shared__ float qv[kHeadsPerBlock][kIdxDim];
+  __shared__ __align__(16) float qt[kIdxDim][kHeadsPerBlock];  // the roped rows, dim-major: 8 heads of a dim in 32 B
   __shared__ __align__(16) __nv_bfloat16 had[kIdxDim * kIdxDim];
   const int hg = blockIdx.x, ti = blockIdx.y, i = threadIdx.x;
   {
@@ -279,26 +280,41 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
       q[hh] = bf16_round(__fadd_rn(__fmul_rn(q[hh], cs), __fmul_rn(rot, sn)));
     }
   }
-  __syncthreads();
 #pragma unroll
-  for (int hh = 0; hh < kHeadsPerBlock; ++hh) qv[hh][i] = q[hh];
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) qt[i][hh] = q[hh];
   __syncthreads();
   float acc[kHeadsPerBlock];
 #pragma unroll
   for (int hh = 0; hh < kHeadsPerBlock; ++hh) acc[hh] = 0.f;
 #pragma unroll 4
-  for (int r = 0; r < kIdxDim; ++r) {
+  for (int r = 0; r < kIdxDim; ++r) {  // per dim: one Hadamard element and two broadcast 16-byte reads of the 8 heads
     const float hv = __bfloat162float(had[r * kIdxDim + i]);
-#pragma unroll
-    for (int hh = 0; hh < kHeadsPerBlock; ++hh) acc[hh] = fmaf(qv[hh][r], hv, acc[hh]);
+    const float4 a = *reinterpret_cast<const float4*>(&qt[r][0]);
+    const float4 b = *reinterpret_cast<const float4*>(&qt[r][4]);
+    acc[0] = fmaf(a.x, hv, acc[0]);
+    acc[1] = fmaf(a.y, hv, acc[1]);
+    acc[2] = fmaf(a.z, hv, acc[2]);
+    acc[3] = fmaf(a.w, hv, acc[3]);
+    acc[4] = fmaf(b.x, hv, acc[4]);
+    acc[5] = fmaf(b.y, hv, acc[5]);
+    acc[6] = fmaf(b.z, hv, acc[6]);
+    acc[7] = fmaf(b.w, hv, acc[7]);
   }
+  // the eight row maxima with one hand-over through shared memory
+  float hq[kHeadsPerBlock];
 #pragma unroll
   for (int hh = 0; hh < kHeadsPerBlock; ++hh) {
-    const float hq = bf16_round(acc[hh]);
-    const float amax = block_max(fabsf(hq), red);
+    hq[hh] = bf16_round(acc[hh]);
+    const float m = warp_max(fabsf(hq[hh]));
+    if ((i & 31) == 0) red8[i >> 5][hh] = m;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < kHeadsPerBlock; ++hh) {
+    const float amax = fmaxf(fmaxf(red8[0][hh], red8[1][hh]), fmaxf(red8[2][hh], red8[3][hh]));
     const float sq = __fdiv_rn(127.0f, amax);
     const int64_t head = static_cast<int64_t>(ti) * kIdxHeads + hg * kHeadsPerBlock + hh;
-    q_int8[head * kIdxDim + i] = quant_one(hq, sq);
+    q_int8[head * kIdxDim + i] = quant_one(hq[hh], sq);
     if (i == 0) q_scale[head] = __float2half_rn(__fdiv_rn(1.0f, sq));
   }
 }
