@@ -666,7 +666,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   PTO_REQUIRE(packed_kv_cache == nullptr || aligned16(packed_kv_cache), "packed_kv_cache must be 16-byte aligned");
   PTO_REQUIRE(eps_cq >= 0.f && eps_ckv >= 0.f && ln_eps >= 0.f, "negative epsilon");
   PTO_REQUIRE(aligned16(token_x) && aligned16(w_dq) && aligned16(w_uqqr) && aligned16(w_uk) && aligned16(w_dkvkr) &&
-                  aligned16(w_idx_qb) && aligned16(w_idx_k) && aligned16(w_idx_proj) && aligned16(kv_cache) &&
+                  aligned16(w_idx_qb) && aligned16(w_idx_k) && aligned16(w_idx_proj) && aligned16(kv_cache) && aligned16(gamma_cq) &&
                   aligned16(query_nope_out),
               "prolog tensors must be 16-byte aligned");
   DeviceInfo di;

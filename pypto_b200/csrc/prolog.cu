@@ -63,32 +63,53 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale_q) {
 }
 
 // ---- query down-projection: bf16 rounding, RMSNorm, per-token int8 ------------------------------------
-// grid = tokens, dynamic shared memory = q_lora floats
-__global__ void __launch_bounds__(256)
+// grid = tokens, 512 threads, dynamic shared memory = q_lora floats (16-byte aligned rows: ld and q_lora multiples of 4)
+__global__ void __launch_bounds__(512)
 prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, const __nv_bfloat16* __restrict__ gamma, int q_lora,
                           float eps, int8_t* __restrict__ q_norm, float* __restrict__ q_norm_scale) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
   const int ti = blockIdx.x;
-  const float* src = qa + static_cast<int64_t>(ti) * ld;
+  const float4* src = reinterpret_cast<const float4*>(qa + static_cast<int64_t>(ti) * ld);
+  float4* row4 = reinterpret_cast<float4*>(row);
+  const int groups = q_lora >> 2;  // four values per step: at q_lora = 1536 every thread makes one trip to memory
   const float inv_n = 1.0f / static_cast<float>(q_lora);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
-    const float v = bf16_round(src[i]);
-    row[i] = v;
-    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v, v), inv_n));
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float4 v = __ldg(src + g);
+    v.x = bf16_round(v.x);
+    v.y = bf16_round(v.y);
+    v.z = bf16_round(v.z);
+    v.w = bf16_round(v.w);
+    row4[g] = v;
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v.x, v.x), inv_n));
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v.y, v.y), inv_n));
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v.z, v.z), inv_n));
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v.w, v.w), inv_n));
   }
   const float rms = sqrtf(block_sum(ss, red) + eps);
   float amax = 0.f;
-  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
-    const float y = bf16_round(__fmul_rn(__fdiv_rn(row[i], rms), ld_bf16(gamma + i)));
-    row[i] = y;
-    amax = fmaxf(amax, fabsf(y));
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float4 v = row4[g];
+    const uint2 gm = __ldg(reinterpret_cast<const uint2*>(gamma) + g);  // four bf16
+    v.x = bf16_round(__fmul_rn(__fdiv_rn(v.x, rms), __uint_as_float(gm.x << 16)));
+    v.y = bf16_round(__fmul_rn(__fdiv_rn(v.y, rms), __uint_as_float(gm.x & 0xffff0000u)));
+    v.z = bf16_round(__fmul_rn(__fdiv_rn(v.z, rms), __uint_as_float(gm.y << 16)));
+    v.w = bf16_round(__fmul_rn(__fdiv_rn(v.w, rms), __uint_as_float(gm.y & 0xffff0000u)));
+    row4[g] = v;
+    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
   }
   amax = block_max(amax, red);
   const float scale_q = __fdiv_rn(127.0f, amax);
-  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) {
-    q_norm[static_cast<int64_t>(ti) * q_lora + i] = quant_one(row[i], scale_q);
+  char4* dst = reinterpret_cast<char4*>(q_norm + static_cast<int64_t>(ti) * q_lora);
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    const float4 v = row4[g];
+    char4 q;
+    q.x = quant_one(v.x, scale_q);
+    q.y = quant_one(v.y, scale_q);
+    q.z = quant_one(v.z, scale_q);
+    q.w = quant_one(v.w, scale_q);
+    dst[g] = q;
   }
   if (threadIdx.x == 0) q_norm_scale[ti] = __fdiv_rn(1.0f, scale_q);
 }
@@ -345,7 +366,7 @@ cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* s
 
 cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
                                       int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
-  prolog_qnorm_quant_kernel<<<t, 256, static_cast<size_t>(q_lora) * sizeof(float), stream>>>(
+  prolog_qnorm_quant_kernel<<<t, 512, static_cast<size_t>(q_lora) * sizeof(float), stream>>>(
       qa, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
   return cudaGetLastError();
 }
