@@ -506,7 +506,9 @@ def main():
         score_bytes = gen.score_stage_bytes(d)
         achieved = score_bytes / (score_ms * 1e-3) / 1e9
         step_gbs = bytes_step["total"] / (ms_per_step * 1e-3) / 1e9
-        n_split_launch = 0 if t * 2 >= 148 else 1
+        # the attention kernel splits a token's rows over several clusters (and adds a combine launch) only when
+        # t * 2 head blocks fill less than half of the 148 SMs
+        n_split_launch = 1 if 148 // max(t * 2, 1) >= 2 else 0
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
