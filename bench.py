@@ -435,21 +435,36 @@ def main():
     # copies of neighbouring steps overlap the compute, every byte is still moved every step.
     host_names = ["idx_query", "idx_query_scale", "idx_weight", "query_nope", "query_rope", "act_seq_key",
                   "block_table"]
-    host = {n: getattr(d, n).cpu().pin_memory() for n in host_names}
-    dev_in = [{n: torch.empty_like(getattr(d, n)) for n in host_names} for _ in range(2)]
+    # one pinned staging arena on the host and one arena per buffer set on the device, the operator's tensors
+    # being views into them: a step's inputs cross the bus as ONE copy (seven separate copies of 0.1-8 MB were
+    # measured at 266 us against 188 us for the same bytes in one)
+    layout, total = {}, 0
+    for n in host_names:
+        v = getattr(d, n)
+        layout[n] = (total, v.numel() * v.element_size(), v.dtype, tuple(v.shape))
+        total += (v.numel() * v.element_size() + 255) // 256 * 256
+
+    def views(arena):
+        return {n: arena[off:off + nb].view(dt).reshape(shape) for n, (off, nb, dt, shape) in layout.items()}
+
+    host_arena = torch.empty(total, dtype=torch.uint8).pin_memory()
+    host = views(host_arena)
+    for n in host_names:
+        host[n].copy_(getattr(d, n).cpu())
+    dev_arena = [torch.empty(total, dtype=torch.uint8, device=dev) for _ in range(2)]
+    dev_in = [views(a) for a in dev_arena]
     dev_idx = [torch.zeros_like(idx) for _ in range(2)]
     dev_out = [torch.zeros_like(out) for _ in range(2)]
     out_host = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
-    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    h2d = total
     d2h = out_host[0].numel() * out_host[0].element_size()
     s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     in_ready = [torch.cuda.Event() for _ in range(2)]
     comp_done = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
 
-    for n in host_names:  # (valid contents for the warm-up call inside the capture helper)
-        for i in range(2):
-            dev_in[i][n].copy_(host[n], non_blocking=True)
+    for i in range(2):  # (valid contents for the warm-up call inside the capture helper)
+        dev_arena[i].copy_(host_arena, non_blocking=True)
     torch.cuda.synchronize()
     e2e_steps = [pto.CapturedCall(pto.decode_indexer_attention_quant, x["idx_query"], x["idx_query_scale"],
                                   d.idx_key_cache, d.idx_key_scale, x["idx_weight"], x["query_nope"], x["query_rope"],
@@ -462,8 +477,7 @@ def main():
             with torch.cuda.stream(s_in):
                 if k >= 2:
                     s_in.wait_event(comp_done[i])  # step k-2 no longer reads this input set
-                for n in host_names:
-                    dev_in[i][n].copy_(host[n], non_blocking=True)
+                dev_arena[i].copy_(host_arena, non_blocking=True)
                 in_ready[i].record(s_in)
             with torch.cuda.stream(s_comp):
                 s_comp.wait_event(in_ready[i])
@@ -529,8 +543,8 @@ def main():
             "roofline_step": {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
                               "frac": step_gbs / peak, "algorithmic_bytes_per_step": bytes_step},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "per-step inputs (queries, scales, weights, lengths, block table) from pinned host "
-                            "memory, output copied back, steps double-buffered over H2D/compute/D2H streams; "
+                    "note": "per-step inputs (queries, scales, weights, lengths, block table) from one pinned host "
+                            "arena in one copy, output copied back, steps double-buffered over H2D/compute/D2H streams; "
                             "KV caches are resident device state"},
             "gpu_launches": (3 + n_split_launch) * args.steps,
             "eager": {"ms_per_step": eager_ms, "value": t * 1e3 / eager_ms,
