@@ -530,9 +530,11 @@ def main():
             "config": {"workload": f"config{args.config}: fused indexer -> top-2048 -> sparse MLA decode",
                        "step": "the public fused operator, recorded once into a CUDA graph and replayed",
                        "per_gpu_batch": d.b, "s1": d.s1, "global_batch": d.b * world,
-                       "context": f"U[4096,65536], mean {sum(d.act_seq) / d.b:.0f}", "scale_dtype": args.scale_dtype,
+                       "context": f"{min(d.act_seq)}..{max(d.act_seq)} keys per sequence, mean {sum(d.act_seq) / d.b:.0f}",
+                       "scale_dtype": args.scale_dtype,
                        "partition": f"batch x{world}, no collective on the data path",
-                       "l2": "inputs (1.7 GB of cache per rank) larger than L2, no flush needed"},
+                       "l2": f"inputs ({d.block_num * 128 * (132 + 656) / 1e9:.1f} GB of cache per rank) larger than L2, "
+                             "no flush needed"},
             "roofline": {"bound": "hbm", "kernel": "li_score_tc_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          # dram read+write of one launch: ncu measured 143.93 MB for 138.58 MB algorithmic on
