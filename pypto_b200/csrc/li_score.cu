@@ -31,7 +31,7 @@ constexpr int kStageBytes = kPageBytes + 1024;  // key page + the page's 128 key
 constexpr int kHeads = 64;
 constexpr int kQBytesPerToken = kHeads * 128;
 constexpr int kLiMmaWarps = 2;         // warps 1..2: issuer for pages n with n % 2 == warp - 1
-constexpr int kLiEpilogueGroups = 4;   // groups of four warps; group g takes pages n with n % 4 == g
+constexpr int kLiEpilogueGroups = 4;   // groups of four warps; a slot is always served by the same group (below)
 constexpr int kLiEpilogueWarp0 = 1 + kLiMmaWarps;
 constexpr int kLiThreads = 32 * (kLiEpilogueWarp0 + 4 * kLiEpilogueGroups);
 constexpr int kMaxS1 = 4;
@@ -295,8 +295,12 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         const int row = quarter * 32 + lane;
         for (int j = 0; j < npages; ++j) {
           const uint32_t n = n_item + j;
-          if (static_cast<int>(n % kLiEpilogueGroups) != grp) continue;
           const uint32_t slot = n % n_slots;
+          // A slot belongs to one group, so that the group sees every use of the slot and consecutive waits on its
+          // barriers alternate in parity. (Taking pages n % 4 == grp is the same thing for 8 and 4 slots, but with
+          // the two slots of s1 = 3, 4 a group met only every second use of a slot: two waits in a row on the same
+          // parity, of which the second returned at once, before the page's products were there.)
+          if (static_cast<int>(slot % kLiEpilogueGroups) != grp) continue;
           const uint32_t ph = (n / n_slots) & 1u;
           if (!mbar_wait(smem_u32(&ctl->accfull[slot]), ph)) {
             ctl->abort = 1;

@@ -205,3 +205,16 @@ def test_fp16_chain_needs_fp16_scales():
     with pytest.raises(RuntimeError, match="fp16"):
         pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
                                      g.act_seq_key, g.block_table, sc, None, fp16_chain=True)
+
+
+@pytest.mark.parametrize("s1", [3, 4])
+def test_three_and_four_query_tokens_with_many_pages_per_cta(s1):
+    """s1 = 3, 4 leave room for two accumulator slots only; with more than four pages per CTA every slot is
+    reused many times by the epilogue warps (one sequence of 131072 keys: about seven pages per CTA). The
+    tensor-core scores must equal the CUDA-core kernel's."""
+    d = gen.make_inputs([131072], s1=s1, seed=60 + s1, with_attention=False)
+    a, _ = _scores(d, simt=True)
+    b, _ = _scores(d, simt=False)
+    assert pto.workspace_status()[0] == 0
+    for i in range(s1):
+        torch.testing.assert_close(b[i, :131072], a[i, :131072], rtol=3e-6, atol=1e-9)
