@@ -548,7 +548,7 @@ def main():
                     "note": "per-step inputs (queries, scales, weights, lengths, block table) from one pinned host "
                             "arena in one copy, output copied back, steps double-buffered over H2D/compute/D2H streams; "
                             "KV caches are resident device state"},
-            "gpu_launches": (3 + n_split_launch) * args.steps,
+            "gpu_launches": ((d.s1 + 3) // 4 + 2 + n_split_launch) * args.steps,  # score launches take four tokens each
             "eager": {"ms_per_step": eager_ms, "value": t * 1e3 / eager_ms,
                       "note": "this rank, the same operator called from the host every step instead of replayed"},
             "clocks": clocks,
