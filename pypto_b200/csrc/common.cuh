@@ -279,6 +279,7 @@ struct LiParams {
   int fp16_chain;  // PTO_LI_FP16_CHAIN: the older formulation of the score
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
+  int groups;      // token groups of s1 tokens taken by one launch (grid y; tensor-core kernel), >= 1
   int32_t* status;
 };
 

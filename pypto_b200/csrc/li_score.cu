@@ -200,7 +200,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int page0 = cur - ctl->prefix[bi];
     const int npages = seg_end - cur;
     const int seq_len = p.act_seq[bi];
-    const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset;
+    // (grid y: further groups of s1 tokens of the same sequences, prefill chunks)
+    const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + static_cast<int>(blockIdx.y) * p.s1;
 
     __syncthreads();  // previous segment fully drained: Q tile and ws may be overwritten
     const bool aborted = ctl->abort != 0;
@@ -447,9 +448,14 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kLiSmemBytes));
   if (e != cudaSuccess) return e;
+  // a launch that takes several token groups gives each group its share of the SMs: every CTA then walks more
+  // pages and the fixed cost of a launch (about 8 us) is paid once for all of them
+  const int groups = p.groups < 1 ? 1 : p.groups;
   long long max_items = static_cast<long long>(p.b) * p.max_blocks;
-  int grid = static_cast<int>(max_items < num_sms ? max_items : num_sms);
-  if (grid < 1) grid = 1;
+  const int per_group = num_sms / groups < 1 ? 1 : num_sms / groups;
+  int gx = static_cast<int>(max_items < per_group ? max_items : per_group);
+  if (gx < 1) gx = 1;
+  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(groups), 1);
   kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_q), p);
   return cudaGetLastError();

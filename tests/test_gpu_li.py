@@ -218,3 +218,15 @@ def test_three_and_four_query_tokens_with_many_pages_per_cta(s1):
     assert pto.workspace_status()[0] == 0
     for i in range(s1):
         torch.testing.assert_close(b[i, :131072], a[i, :131072], rtol=3e-6, atol=1e-9)
+
+
+def test_prefill_chunk_groups_share_a_launch():
+    """22 query tokens per sequence: five full groups of four go into one launch (grid y), the last two tokens
+    into a second one. Scores equal the CUDA-core kernel's for every token."""
+    d = gen.make_inputs([9000, 300], s1=22, seed=77, with_attention=False)
+    a, _ = _scores(d, simt=True)
+    b, _ = _scores(d, simt=False)
+    assert pto.workspace_status()[0] == 0
+    for bi, s in enumerate(d.act_seq):
+        for i in range(22):
+            torch.testing.assert_close(b[bi * 22 + i, :s], a[bi * 22 + i, :s], rtol=3e-6, atol=1e-9)
