@@ -198,7 +198,7 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
     if (rc != PTO_OK) return rc;
   }
   // more than four query tokens per sequence (prefill chunks): groups of four tokens; the tensor-core kernel
-  // takes up to eight full groups per launch (grid y), a last partial group gets a launch of its own
+  // takes up to sixteen full groups per launch (grid y), a last partial group gets a launch of its own
   p.s1_total = s1;
   int off = 0;
   while (off < s1) {
@@ -209,7 +209,7 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
       PTO_CUDA(pto::launch_li_score_simt(p, stream));
     } else {
       const int full = (s1 - off) / group;
-      if (p.s1 == group && full > 1) p.groups = full < 8 ? full : 8;
+      if (p.s1 == group && full > 1) p.groups = full < 16 ? full : 16;
       int rc = make_rows128_map(&tmap_q, q, static_cast<uint64_t>(b) * s1 * 64, static_cast<uint32_t>(64 * p.s1));
       if (rc != PTO_OK) return rc;
       PTO_CUDA(pto::launch_li_score_tc(p, &tmap_k, &tmap_q, di.num_sms, stream));
