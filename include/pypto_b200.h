@@ -16,8 +16,14 @@
  *     256-byte aligned. Its first PTO_STATUS_WORDS int32 words are a device status area that the
  *     kernels set on a rejected page-table entry or an expired bounded wait; read it with
  *     `pto_workspace_status` (which synchronises the stream).
- *   - the library allocates no device memory and is re-entrant; calls on different streams need
- *     different workspaces.
+ *   - the library allocates no device memory; the indexer, attention and fused entry points keep no
+ *     state between calls and are re-entrant (calls on different streams need different
+ *     workspaces). The prolog entry point is the exception: per device it creates, at its first
+ *     call, a second stream and three events (and, as long as a projection is still issued to the
+ *     GEMM library, that library's handle), and its calls on one device are serialised by a
+ *     per-device mutex while they enqueue. A prolog call must not be enqueued on a device while
+ *     another stream of that device is capturing a prolog call: both would use the same side
+ *     stream.
  *   - t = b * s1 query tokens; the tokens of sequence `bi` are rows bi*s1 .. bi*s1+s1-1.
  */
 #ifndef PYPTO_B200_H_
@@ -61,6 +67,10 @@ typedef struct CUstream_st* pto_stream_t; /* cudaStream_t */
 int pto_abi_version(void);
 const char* pto_strerror(int code);
 const char* pto_last_error(void);
+/* Kernels of this library enqueued so far by this process (library GEMMs of the prolog are not counted): a
+ * diagnostic that a call reached the CUDA path. A launch recorded during stream capture counts once, at
+ * capture time. No counterpart in the reference. */
+long long pto_launch_count(void);
 
 /* Copies the status words of `workspace` to `host_out[PTO_STATUS_WORDS]` and synchronises `stream`. */
 int pto_workspace_status(const void* workspace, int32_t* host_out, pto_stream_t stream);
@@ -110,23 +120,29 @@ int pto_li_scores(const int8_t* idx_query, const void* idx_query_scale, const in
  * `pto_li_decode`, minus the workspace: the fp32 score rows and the status words live in a
  * file-scope `static __device__` array of PTO_LI_STATIC_SCRATCH_BYTES that every GPU loading the
  * library holds until the process exits.
- *   - limit: 256 + t * max_blocks * block_size * 4 bytes must fit in the array, otherwise
- *     PTO_ERR_WORKSPACE is returned and nothing is launched (t = 16 tokens at 131072 keys, or 64
- *     tokens at 32768 keys, fit);
+ *   - limit: t * max_blocks * block_size * 4 bytes of score rows may not exceed 8 MiB (the array is
+ *     8 MiB + 256 bytes of status words), otherwise PTO_ERR_WORKSPACE is returned and nothing is
+ *     launched (t = 16 tokens at 131072 keys, or 64 tokens at 32768 keys, just fit);
  *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress, with
  *     that device current) and caches it; make that first call outside of any stream capture;
  *   - all calls share the one array and it keeps the previous call's contents; the status words
  *     are cleared at the start of each call, every score that is read is written first. Two calls
  *     that overlap on the GPU (different streams) race on it: serialise them;
  *   - `status_out` (host, PTO_STATUS_WORDS ints, may be NULL) receives the status words after the
- *     call; passing it synchronises the stream. */
-#define PTO_LI_STATIC_SCRATCH_BYTES (8u << 20)
+ *     call; passing it synchronises the stream, so it is refused (PTO_ERR_INVALID) while `stream`
+ *     is being captured. With NULL, read the words later with `pto_li_static_status`, before the
+ *     next call clears them. After PTO_ST_WAIT_EXPIRED the indices are undefined. */
+#define PTO_LI_STATIC_SCRATCH_BYTES ((8u << 20) + 256u)
 int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
                          const void* idx_key_scale, const void* idx_weight, int scale_dtype,
                          const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res,
                          int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
                          int max_blocks, int selected_count, int flags, int32_t* status_out,
                          pto_stream_t stream);
+
+/* Status words left by the last `pto_li_decode_static` call on the current device (synchronises
+ * `stream`; no counterpart in the reference). */
+int pto_li_static_status(int32_t* host_out, pto_stream_t stream);
 
 /* Top-k stage alone over f32 score rows with row stride `row_stride` elements
  * (TopKSort/Merge/Extract semantics, lightning_indexer_quant_impl.py:196-312: exact, -1 padded). */
@@ -145,8 +161,9 @@ int pto_li_topk(const float* scores, int64_t row_stride, const int32_t* act_seq_
  *   block_table    int32 [b, max_blocks]  kv_act_seqs  int32 [b]
  *   attention_out  bf16 [b, s1, nq, 512]  out (rows of tokens that see no key are zeroed)
  *
- * `q_row_stride_tokens` heads per token in the query/out arrays (= nq unless a head slice
- * [head_begin, head_begin+nq) of a wider tensor is processed; pass nq_total there).
+ * Head slices: the query and output arrays hold `nq_total` heads per token; the call processes
+ * heads [head_begin, head_begin + nq) of every token and touches no other output row. Pass
+ * nq_total = nq and head_begin = 0 for whole tokens.
  * ------------------------------------------------------------------------------------------ */
 size_t pto_sfa_workspace_bytes(int t, int nq);
 

@@ -13,7 +13,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libpypto_b200.so"
 PTO_DT_F16, PTO_DT_F32 = 0, 1
 PTO_LI_SCORE_SIMT, PTO_LI_UNSORTED, PTO_LI_FP16_CHAIN = 0x1, 0x2, 0x4
 PTO_STATUS_WORDS = 8
-PTO_LI_STATIC_SCRATCH_BYTES = 8 << 20
+PTO_LI_STATIC_SCRATCH_BYTES = (8 << 20) + 256
 PTO_ST_BAD_PAGE, PTO_ST_WAIT_EXPIRED = 0x1, 0x2
 
 _vp, _i, _sz, _i64, _f = C.c_void_p, C.c_int, C.c_size_t, C.c_int64, C.c_float
@@ -23,11 +23,13 @@ SIGNATURES = {
     "pto_abi_version": (_i, []),
     "pto_strerror": (C.c_char_p, [_i]),
     "pto_last_error": (C.c_char_p, []),
+    "pto_launch_count": (C.c_longlong, []),
     "pto_workspace_status": (_i, [_vp, _vp, _vp]),
     "pto_workspace_reset": (_i, [_vp, _vp]),
     "pto_li_workspace_bytes": (_sz, [_i, _i, _i]),
     "pto_li_decode": (_i, [_vp] * 5 + [_i] + [_vp] * 3 + [_i] * 9 + [_vp, _sz, _vp]),
     "pto_li_decode_static": (_i, [_vp] * 5 + [_i] + [_vp] * 3 + [_i] * 9 + [_vp, _vp]),
+    "pto_li_static_status": (_i, [_vp, _vp]),
     "pto_li_scores": (_i, [_vp] * 5 + [_i] + [_vp] * 4 + [_i] * 8 + [_vp, _sz, _vp]),
     "pto_li_topk": (_i, [_vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pto_sfa_workspace_bytes": (_sz, [_i, _i]),

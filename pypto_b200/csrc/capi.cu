@@ -7,12 +7,15 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
 #include "common.cuh"
 
 namespace pto {
+static std::atomic<long long> g_launch_count{0};
+void count_launch(int n) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
 int li_max_s1();
 int li_max_sequences();
 int topk_max_k();
@@ -346,7 +349,8 @@ struct Blas {
   // beside the chain of products they do not depend on
   cudaStream_t side[64] = {nullptr};
   cudaEvent_t ev[64][3] = {{nullptr}};
-  std::mutex mu;
+  std::mutex mu;          // guards the library resolution and the per-device set-up
+  std::mutex dev_mu[64];  // a device's calls enqueue one after the other (they share its side stream and events)
   bool loaded = false;
 };
 
@@ -357,6 +361,7 @@ Blas& blas() {
 
 int blas_handle(cublasHandle_t* out, int* device = nullptr) {
   Blas& b = blas();
+  std::lock_guard<std::mutex> lock(b.mu);
   if (!b.loaded) {
     void* lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
     if (lib == nullptr) return fail(PTO_ERR_UNSUPPORTED, "libcublas.so.12 not found: %s", dlerror());
@@ -470,6 +475,8 @@ const char* pto_strerror(int code) {
 
 const char* pto_last_error(void) { return g_err; }
 
+long long pto_launch_count(void) { return pto::g_launch_count.load(std::memory_order_relaxed); }
+
 int pto_workspace_status(const void* workspace, int32_t* host_out, pto_stream_t stream) {
   if (workspace == nullptr || host_out == nullptr) return fail(PTO_ERR_INVALID, "null pointer");
   PTO_CUDA(cudaMemcpyAsync(host_out, workspace, PTO_STATUS_WORDS * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
@@ -543,6 +550,12 @@ int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, c
                            act_seq_key, block_table, b, s1, n_heads, head_dim, block_size, block_num, max_blocks);
   if (rc != PTO_OK) return rc;
   PTO_REQUIRE(topk_res != nullptr, "topk_res is null");
+  if (status_out != nullptr) {  // reading the words back synchronises the stream, which a capture forbids
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    PTO_CUDA(cudaStreamIsCapturing(stream, &cap));
+    PTO_REQUIRE(cap == cudaStreamCaptureStatusNone,
+                "status_out must be NULL while the stream is being captured (read the words with pto_li_static_status)");
+  }
   const size_t need = pto_li_workspace_bytes(b * s1, max_blocks, block_size);
   if (need == 0 || need > PTO_LI_STATIC_SCRATCH_BYTES) {
     return fail(PTO_ERR_WORKSPACE,
@@ -566,6 +579,16 @@ int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, c
     PTO_CUDA(cudaMemcpyAsync(status_out, scratch, PTO_STATUS_WORDS * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
     PTO_CUDA(cudaStreamSynchronize(stream));
   }
+  return PTO_OK;
+}
+
+int pto_li_static_status(int32_t* host_out, pto_stream_t stream) {
+  PTO_REQUIRE(host_out != nullptr, "null pointer");
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(cudaMemcpyAsync(host_out, scratch, PTO_STATUS_WORDS * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  PTO_CUDA(cudaStreamSynchronize(stream));
   return PTO_OK;
 }
 
@@ -694,11 +717,11 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   void* q_b = base + w.q_b;
   int32_t* qi_i32 = reinterpret_cast<int32_t*>(base + w.qi_i32);
 
-  std::lock_guard<std::mutex> lock(blas().mu);
   cublasHandle_t h;
   int dev = 0;
   rc = blas_handle(&h, &dev);
   if (rc != PTO_OK) return rc;
+  std::lock_guard<std::mutex> lock(blas().dev_mu[dev]);
   cudaStream_t side = blas().side[dev];
   cudaEvent_t* ev = blas().ev[dev];
   PTO_BLAS(blas().set_stream(h, stream));

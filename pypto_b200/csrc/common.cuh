@@ -263,6 +263,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // ---------------------------------------------------------------------------------------------
 // kernel launchers (defined in the .cu files, called from capi.cu)
 // ---------------------------------------------------------------------------------------------
+// Every launcher counts the kernels it enqueues (read back through pto_launch_count): a caller can check
+// that its call reached this library's kernels, and how many of them.
+void count_launch(int n = 1);
+
 struct LiParams {
   const int8_t* q;          // [t*64, 128]
   const void* q_scale;      // [t, 64]

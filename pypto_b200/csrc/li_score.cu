@@ -398,11 +398,18 @@ li_score_simt_kernel(LiParams p) {
   }
   __syncthreads();
   const int phys = p.block_table[static_cast<int64_t>(bi) * p.max_blocks + page];
+  const int pos = page * kPageKeys + tid;
   if (phys < 0 || phys >= p.block_num) {
+    // a rejected page scores 0 for every token, as in the tensor-core kernel (where the page reads as zeros):
+    // the top-k stage never ranks what an earlier call left in the buffer
     if (tid == 0) set_status(p.status, PTO_ST_BAD_PAGE, phys, 5);
+    if (pos < seq_len) {
+      for (int i = 0; i < s1; ++i) {
+        p.scores[(static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + i) * p.row_stride + pos] = 0.f;
+      }
+    }
     return;
   }
-  const int pos = page * kPageKeys + tid;
   if (pos >= seq_len) return;
   int4 kreg[8];
   const int4* krow = reinterpret_cast<const int4*>(p.k_cache + (static_cast<int64_t>(phys) * kPageKeys + tid) * 128);
@@ -456,6 +463,7 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
   int gx = static_cast<int>(max_items < per_group ? max_items : per_group);
   if (gx < 1) gx = 1;
   const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(groups), 1);
+  count_launch();
   kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_q), p);
   return cudaGetLastError();
@@ -463,6 +471,7 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream) {
   dim3 grid(p.max_blocks, p.b);
+  count_launch();
   li_score_simt_kernel<<<grid, 128, 0, stream>>>(p);
   return cudaGetLastError();
 }

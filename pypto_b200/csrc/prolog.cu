@@ -360,13 +360,21 @@ cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* s
                                 int num_sms, cudaStream_t stream) {
   const int64_t want = (rows + 7) / 8;
   const int grid = static_cast<int>(want < static_cast<int64_t>(num_sms) * 8 ? (want < 1 ? 1 : want) : num_sms * 8);
+  count_launch();
   kv_pack_rows_kernel<<<grid, 256, 0, stream>>>(kv, reinterpret_cast<const __nv_bfloat16*>(kr), sc, rows, packed);
   return cudaGetLastError();
 }
 
 cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
                                       int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
-  prolog_qnorm_quant_kernel<<<t, 512, static_cast<size_t>(q_lora) * sizeof(float), stream>>>(
+  const size_t dyn = static_cast<size_t>(q_lora) * sizeof(float);
+  if (dyn > 40 * 1024) {  // beyond what fits the default 48 KB next to the kernel's static shared memory
+    cudaError_t e = cudaFuncSetAttribute(prolog_qnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dyn));
+    if (e != cudaSuccess) return e;
+  }
+  count_launch();
+  prolog_qnorm_quant_kernel<<<t, 512, dyn, stream>>>(
       qa, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
   return cudaGetLastError();
 }
@@ -374,6 +382,7 @@ cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
                                           const void* cos, const void* sin, int t, void* q_b, void* q_rope,
                                           cudaStream_t stream) {
+  count_launch();
   prolog_qb_dequant_rope_kernel<<<dim3(kHeads / kQbHeadsPerBlock, t), 256, 0, stream>>>(
       qb_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_b),
@@ -387,6 +396,7 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
                              void* idx_k_scale_cache, void* weights, int8_t* packed_cache, int32_t* status,
                              cudaStream_t stream) {
+  count_launch();
   prolog_kv_kernel<<<t, 128, 0, stream>>>(
       kv, ki, wp, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(ln_gamma),
@@ -399,6 +409,7 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,
                                const void* sin, const void* hadamard_q, int t, int8_t* q_int8, void* q_scale,
                                cudaStream_t stream) {
+  count_launch();
   prolog_idxq_kernel<<<dim3(kIdxHeads / kHeadsPerBlock, t), 128, 0, stream>>>(
       qi_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(hadamard_q), q_int8,

@@ -220,6 +220,7 @@ cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, cons
   p.status = status;
   const int n_tiles = p.tiles[0] + p.tiles[1];
   const int grid = n_tiles < num_sms ? n_tiles : num_sms;
+  count_launch();
   prolog_i8_gemm_kernel<<<grid, kGThreads, kGSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_w0),
                                                                   *reinterpret_cast<const CUtensorMap*>(tmap_w1),
                                                                   *reinterpret_cast<const CUtensorMap*>(tmap_x), p);

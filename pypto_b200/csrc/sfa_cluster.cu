@@ -872,6 +872,7 @@ cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 2 : 1;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 

@@ -453,11 +453,13 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
     // all 128 heads of a token: tcgen05 cluster kernel (M = 128); narrower head slices use mma.sync below
     e = launch_sfa_cluster(p, stream);
   } else {
+    count_launch();
     sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) return e;
   if (p.n_split > 1) {
+    count_launch();
     sfa_combine_kernel<<<t * p.nq, 128, 0, stream>>>(p);
     e = cudaGetLastError();
   }

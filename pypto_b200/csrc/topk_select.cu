@@ -503,6 +503,7 @@ cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, li_topk_kernel, p);
 }
 

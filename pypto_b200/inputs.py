@@ -210,31 +210,39 @@ def make_config(config_id: int, device="cpu", rank: int = 0, world: int = 1,
                        with_indexer=c["indexer"], with_attention=c["attention"], with_topk=c["topk"])
 
 
-def take_sequences(d: DecodeInputs, seq_ids: Sequence[int], device=None) -> DecodeInputs:
-    """Compact copy holding only the listed sequences: their cache pages are renumbered
-    0..n-1 in block-table order, query rows are sliced. Used to cut a bounded CPU sample out of a
-    large configuration and to hand each rank its batch shard."""
+def take_sequences(d: DecodeInputs, seq_ids: Sequence[int], device=None, permute_seed: Optional[int] = None) -> DecodeInputs:
+    """Compact copy holding only the listed sequences: their cache pages are renumbered 0..n-1 (in
+    block-table order, or in a random order drawn from `permute_seed`, which keeps the block table a
+    permutation), query rows are sliced. Used to cut a bounded CPU sample out of a large configuration and
+    to hand each rank its batch shard."""
     device = torch.device(device) if device is not None else d.block_table.device
+    src = d.block_table.device
     seq_ids = list(seq_ids)
     act = [d.act_seq[i] for i in seq_ids]
     per = [math.ceil(s / BLOCK_SIZE) for s in act]
     max_blocks = max(max(per), 1)
     block_num = max(sum(per), 1)
     out = DecodeInputs(len(seq_ids), d.s1, act, block_num, max_blocks)
+    if permute_seed is None:
+        new_ids = torch.arange(block_num, dtype=torch.long)
+    else:
+        new_ids = torch.randperm(block_num, generator=torch.Generator().manual_seed(permute_seed))
     table = torch.full((len(seq_ids), max_blocks), -1, dtype=torch.int32)
     old_pages = []
     off = 0
     for j, (i, n) in enumerate(zip(seq_ids, per)):
         old_pages.append(d.block_table[i, :n].to("cpu", torch.long))
-        table[j, :n] = torch.arange(off, off + n, dtype=torch.int32)
+        table[j, :n] = new_ids[off:off + n].to(torch.int32)
         off += n
     pages = torch.cat(old_pages) if old_pages else torch.zeros(0, dtype=torch.long)
     if pages.numel() == 0:
         pages = torch.zeros(1, dtype=torch.long)
-    pages_dev = pages.to(d.block_table.device)
-    rows_dev = (pages_dev[:, None] * BLOCK_SIZE + torch.arange(BLOCK_SIZE, device=pages_dev.device)[None, :]).reshape(-1)
-    tok = torch.tensor([i * d.s1 + k for i in seq_ids for k in range(d.s1)], dtype=torch.long,
-                       device=d.block_table.device)
+    # page new_ids[k] of the copy holds old page pages[k]: gather with the inverse map
+    inv = torch.empty(block_num, dtype=torch.long)
+    inv[new_ids[:pages.numel()]] = torch.arange(pages.numel())
+    pages_dev = pages[inv].to(src)
+    rows_dev = (pages_dev[:, None] * BLOCK_SIZE + torch.arange(BLOCK_SIZE, device=src)[None, :]).reshape(-1)
+    tok = torch.tensor([i * d.s1 + k for i in seq_ids for k in range(d.s1)], dtype=torch.long, device=src)
     out.block_table = table.to(device)
     out.act_seq_key = torch.tensor(act, dtype=torch.int32, device=device)
     if d.idx_query is not None:

@@ -47,6 +47,12 @@ def workspace_status(device=None):
     return list(out)
 
 
+def launch_count() -> int:
+    """Kernels of the CUDA library enqueued so far by this process (a launch recorded during stream capture
+    counts once, at capture time)."""
+    return int(_lib.load().pto_launch_count())
+
+
 def reset_workspace_status(device=None):
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     ws = _workspace(device, 256)
@@ -188,7 +194,10 @@ def lightning_indexer_topk(scores, act_seq_key, topk_res, s1=1, selected_count=2
     return None
 
 
-def _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv, topk):
+def _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv, topk,
+                nq_total=None, head_begin=0):
+    nq_slice, nq = int(nq), int(nq if nq_total is None else nq_total)  # rows per token in the query / output arrays
+    _need(0 <= int(head_begin) and int(head_begin) + nq_slice <= nq, "head slice [head_begin, head_begin + nq) outside nq_total")
     qn = unwrap(query_nope, "query_nope")
     qr = unwrap(query_rope, "query_rope")
     ti = unwrap(topk_indices, "topk_indices")
@@ -210,9 +219,9 @@ def _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs, 
 
 def _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
                                   block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
-                                  max_blocknum_perbatch, tile_config=None):
+                                  max_blocknum_perbatch, tile_config=None, head_begin=0, nq_total=None):
     qn, qr, ti, bt, act, out, t, b = _sfa_common(query_nope, query_rope, topk_indices, block_table, kv_act_seqs,
-                                                 attention_out, nq, n_kv, topk)
+                                                 attention_out, nq, n_kv, topk, nq_total, head_begin)
     kn = unwrap(key_nope_2d, "key_nope_2d")
     kr = unwrap(key_rope_2d, "key_rope_2d")
     _need(kn.dtype in (torch.int8, torch.bfloat16) and kn.dim() == 2 and kn.shape[1] == 512,
@@ -224,7 +233,7 @@ def _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_
     lib = _lib.load()
     nbytes = lib.pto_sfa_workspace_bytes(t, int(nq))
     tail = (b, t // b, int(nq), int(n_kv), float(softmax_scale), int(topk), int(block_size), n_rows, bt.shape[1],
-            int(nq), 0)
+            int(nq if nq_total is None else nq_total), int(head_begin))
     if kn.dtype == torch.bfloat16:
         # the reference takes the latent rows as they are when the cache is not int8
         # (sparse_flash_attention_quant_impl.py:149-153, :199-202); the scales are not read
@@ -248,22 +257,27 @@ def _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_
 
 def sparse_flash_attention_quant_d(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
                                    block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
-                                   max_blocknum_perbatch, tile_config=None):
+                                   max_blocknum_perbatch, tile_config=None, *, head_begin=0, nq_total=None):
     """Decode entry: attention_out[b, s1, nq, 512] over the selected int8 latent + bf16 rope rows
-    (or bf16 latent rows: a bfloat16 `key_nope_2d` selects the non-quantised branch, nq = 128 only)."""
+    (or bf16 latent rows: a bfloat16 `key_nope_2d` selects the non-quantised branch, nq = 128 only).
+    Not in the reference's signature: `nq_total`, `head_begin` process heads [head_begin, head_begin + nq) of
+    query / output arrays that hold nq_total heads per token (a device's share of a head-sharded prefill chunk
+    without slicing copies); the other heads' output rows are not touched."""
     return _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales,
                                          topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv,
-                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config)
+                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config,
+                                         head_begin, nq_total)
 
 
 def sparse_flash_attention_quant_p(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, topk_indices,
                                    block_table, kv_act_seqs, attention_out, nq, n_kv, softmax_scale, topk, block_size,
-                                   max_blocknum_perbatch, tile_config=None):
+                                   max_blocknum_perbatch, tile_config=None, *, head_begin=0, nq_total=None):
     """Prefill entry: same arithmetic and kernel as the decode entry (the reference differs only
     in compiler options between the two)."""
     return _sparse_flash_attention_quant(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales,
                                          topk_indices, block_table, kv_act_seqs, attention_out, nq, n_kv,
-                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config)
+                                         softmax_scale, topk, block_size, max_blocknum_perbatch, tile_config,
+                                         head_begin, nq_total)
 
 
 def _sparse_attention_antiquant(query_nope, query_rope, nope_cache, topk_indices, block_table, kv_act_seqs,

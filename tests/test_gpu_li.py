@@ -153,18 +153,26 @@ def test_config1_shape_against_oracle():
         assert untied == 0
 
 
-def test_rejected_page_sets_status_without_fault():
+@pytest.mark.parametrize("simt", [False, True], ids=["tcgen05", "simt"])
+def test_rejected_page_sets_status_without_fault(simt):
     d = gen.make_inputs([700, 300], s1=1, seed=4, with_attention=False)
     d.block_table[0, 2] = d.block_num + 5  # outside the cache: the page is skipped and reads as zeros
     pto.reset_workspace_status()
     g = d.to(DEV)
     out = torch.zeros((d.t, 1, 2048), dtype=torch.int32, device=DEV)
     pto.lightning_indexer_decode(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
-                                 g.act_seq_key, g.block_table, out, None, None, 2048)
+                                 g.act_seq_key, g.block_table, out, None, None, 2048, _simt_scores=simt)
     st = pto.workspace_status()
     assert st[0] & 0x1 and st[1] == d.block_num + 5
     pto.reset_workspace_status()
     assert pto.workspace_status()[0] == 0
+    # both score kernels give the rejected page's 128 positions the score 0, whatever the buffer held before
+    sc = torch.full((d.t, d.max_blocks * 128), float("nan"), dtype=torch.float32, device=DEV)
+    pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
+                                 g.act_seq_key, g.block_table, sc, simt=simt)
+    torch.cuda.synchronize()
+    assert torch.all(sc[0, 256:384] == 0) and not torch.isnan(sc[0, :700]).any()
+    pto.reset_workspace_status()
 
 
 @pytest.mark.parametrize("name", [n for n in LI_CASES if n.endswith("f16")])

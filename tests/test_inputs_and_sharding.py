@@ -66,3 +66,25 @@ def test_byte_model():
     assert abs(by["indexer"] - 8.67e6) < 0.05e6
     assert abs(by["attention"] - 1.63e6) < 0.02e6
     assert gen.score_stage_bytes(d) == 65536 * 132 + 8192 + 64 * 8 + 4 * 512
+
+
+def test_take_sequences_with_a_permuted_page_order_holds_the_same_data():
+    """`permute_seed` renumbers the copied pages in a random order (the block table stays a permutation, as
+    the benchmark configurations ask); what the table points at is unchanged."""
+    d = gen.make_inputs([300, 700, 129, 1000], s1=1, seed=12)
+    a = gen.take_sequences(d, [3, 1])
+    b = gen.take_sequences(d, [3, 1], permute_seed=99)
+    assert a.act_seq == b.act_seq == [1000, 700]
+    assert not torch.equal(a.block_table, b.block_table)
+    used = b.block_table[b.block_table >= 0]
+    assert sorted(used.tolist()) == list(range(b.block_num))
+    for j in range(2):
+        n = (a.act_seq[j] + 127) // 128
+        pa, pb = a.block_table[j, :n].long(), b.block_table[j, :n].long()
+        assert torch.equal(a.idx_key_cache[pa], b.idx_key_cache[pb])
+        assert torch.equal(a.idx_key_scale[pa], b.idx_key_scale[pb])
+        ra = (pa[:, None] * 128 + torch.arange(128)[None, :]).reshape(-1)
+        rb = (pb[:, None] * 128 + torch.arange(128)[None, :]).reshape(-1)
+        assert torch.equal(a.key_nope_2d[ra], b.key_nope_2d[rb])
+        assert torch.equal(a.k_nope_scales[ra], b.k_nope_scales[rb])
+    assert torch.equal(a.idx_query, b.idx_query)

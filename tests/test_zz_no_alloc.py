@@ -51,8 +51,8 @@ def _static_entry(lib, d):
 
 def test_static_scratch_entry_matches_workspace_entry_twice():
     lib = _lib.load()
-    # first call: long rows that fill most of the array; second call: a different, shorter, ragged
-    # batch with two query tokens per sequence, so stale scores of the first call lie beyond its rows
+    # first call: rows of up to 30000 scores (about 0.5 MB of the array); second call: a different, shorter,
+    # ragged batch with two query tokens per sequence, so stale scores of the first call lie beyond its rows
     first = gen.make_inputs([30000, 17000, 2049, 9000], s1=1, seed=101, with_attention=False).to(DEV)
     second = gen.make_inputs([5000, 130, 2500], s1=2, seed=202, scale_dtype=torch.float16, with_attention=False).to(DEV)
     for d in (first, second):
@@ -75,3 +75,31 @@ def test_static_scratch_entry_rejects_oversized_problem():
                                   128, d.block_num, 1024, 2048, 0, None, stream)
     assert rc == -2
     assert b"static array" in lib.pto_last_error()
+
+
+def test_static_scratch_capacity_edge():
+    """The array holds exactly 8 MiB of score rows: 16 tokens x 1024 blocks x 128 keys x 4 bytes are accepted
+    (and run: the block table is that wide, the sequences themselves are short), one more block is refused on
+    the host with nothing launched. The status words of an accepted call can be read back afterwards."""
+    lib = _lib.load()
+    d = gen.make_inputs([700, 129, 3000, 64] * 4, s1=1, seed=303, with_attention=False, max_blocks=1025).to(DEV)
+    assert d.b * 1024 * 128 * 4 == 8 << 20
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(max_blocks, table, out):
+        return lib.pto_li_decode_static(d.idx_query.data_ptr(), d.idx_query_scale.data_ptr(), d.idx_key_cache.data_ptr(),
+                                        d.idx_key_scale.data_ptr(), d.idx_weight.data_ptr(), _lib.PTO_DT_F32,
+                                        d.act_seq_key.data_ptr(), table.data_ptr(), out.data_ptr(), d.b, 1, 64, 128, 128,
+                                        d.block_num, max_blocks, 2048, 0, None, stream)
+
+    out = torch.full((d.t, 1, 2048), -7, dtype=torch.int32, device=DEV)
+    assert call(1025, d.block_table, out) == -2 and b"static array" in lib.pto_last_error()
+    torch.cuda.synchronize()
+    assert torch.all(out == -7)  # refused before any launch
+    narrow = d.block_table[:, :1024].contiguous()
+    _lib.check(call(1024, narrow, out))
+    status = (C.c_int32 * _lib.PTO_STATUS_WORDS)()
+    _lib.check(lib.pto_li_static_status(status, stream))
+    assert status[0] == 0
+    d.max_blocks, d.block_table = 1024, narrow
+    assert torch.equal(out.cpu(), _reference_entry(lib, d))
