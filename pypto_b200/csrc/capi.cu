@@ -134,6 +134,7 @@ size_t li_scores_bytes(int t, int max_blocks, int block_size) {
 }
 
 int sfa_split(int t, int nq) {
+  if (nq == 128) return pto::sfa_pair_split(t, 148);  // one cluster of two CTAs per (token, split)
   const int n_hb = (nq + 63) / 64;
   const long long ctas = static_cast<long long>(t) * n_hb;
   if (ctas >= 148) return 1;

@@ -320,7 +320,9 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
 cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
-cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster
+cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster (bf16 latent cache)
+cudaError_t launch_sfa_pair(const SfaParams& p, cudaStream_t stream);     // nq == 128, int8 cache: 2-SM MMAs, heads split over the pair
+int sfa_pair_split(int t, int num_sms);
 
 // Prolog stages between the projections (prolog.cu). Fixed widths: 128 heads x (128 + 64), latent 512,
 // rope 64, indexer 64 x 128. `ld`: row stride (elements) of the fp32 projection results.

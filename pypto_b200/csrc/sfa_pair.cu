@@ -1,0 +1,946 @@
+// Sparse MLA attention for all 128 heads of a token on a PAIR of SMs that share every matrix product
+// (tcgen05.mma.cta_group::2): the two CTAs of a cluster split the token's HEADS, 64 each.
+//
+// Arithmetic as in sfa_decode.cu (reference:
+// examples/models/deepseek_v32_exp/sparse_flash_attention_quant_impl.py:45-207; golden
+// deepseekv32_sparse_flash_attention_quant.py:169-254).
+//
+// Why a pair: the fp32 output of 128 heads x 512 values is 256 KB, all of one SM's tensor memory. With the
+// heads split, CTA c keeps O for its 64 heads (256 columns) and two score buffers (2 x 64 columns), and the
+// whole 576-wide contraction is local to the pair's MMA: no score ever crosses between the CTAs, and nothing
+// else does either except four "ready" notices per tile. A 2-SM MMA reads half of its B operand from
+// each CTA's shared memory:
+//   q.K^T  (M = 128 heads, N = 128 keys of a tile, K = 576): A = this CTA's 64 query rows, B = the tile's keys,
+//          of which CTA c gathers and dequantises keys [64c, 64c+64) in full width (9 chunks of 64 dims).
+//   P.V    (M = 128 heads, N = 256 of the 512 values per MMA, K = 128 keys): A = this CTA's P, B = V, of which
+//          CTA c supplies the value columns [256c, 256c+256) of ALL 128 keys. Shared memory between the SMs
+//          moves about 7 bytes per clock (measured: a 32 KB bulk copy to the peer takes 4-5 k cycles), far too
+//          slow to ship the other CTA's keys over, so a second group of producers gathers that half of all
+//          128 rows again (an L2 hit: the other CTA has just fetched the row) and dequantises it.
+// Tensor memory of a 2-SM MMA with 64 rows per CTA: lanes 0-63 hold the first half of the N columns, lanes
+// 64-127 the second half (row = lane % 64). So of a score tile lane l holds (head l % 64, keys 64 (l / 64) ..+63),
+// and of O lane l holds (head l % 64, values 256 (l / 64) ..+255).
+//   warp 0          CTA 0: issues every MMA (event loop over "keys ready", "scores read", "P written", "V ready")
+//   warp 1          CTA 1: forwards those four events of its own to CTA 0 (tcgen05.commit arrivals on CTA 0's barriers)
+//   warps 4..11     softmax: four threads per head (two TMEM lanes x two column halves), P goes to shared memory
+//   warps 12..19    K producers: 16-byte gathers of the CTA's 64 rows, int8 -> bf16 in registers, swizzled stores
+//   warps 20..27    V producers: this CTA's half of the value columns of all 128 rows
+// Roles are uniform within each group of four warps so that registers can be moved between them (setmaxnreg):
+// 72 per thread at launch (seven warps share one scheduler's file of 512 x 32), then 24 / 104 / 72 / 64:
+// nothing spills (a spilled register costs a trip to L2: beside 227 KB of shared memory there is no L1 to speak of).
+// All waits are bounded.
+#include "common.cuh"
+#include "sfa_common.cuh"
+
+namespace pto {
+
+namespace {
+
+// Developer aid: -DPTO_PAIR_TIMELINE records clock64() at 16 points of the first 24 tiles of cluster 0.
+#ifdef PTO_PAIR_TIMELINE
+__device__ long long g_pair_tl[2 * 24 * 16];
+#define TLP(slot, j) do { if (blockIdx.x < 2 && (j) >= 0 && (j) < 24) g_pair_tl[((blockIdx.x & 1) * 24 + (j)) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TLP(slot, j) do { } while (0)
+#endif
+
+constexpr int kPT = 128;                 // selected rows per tile (64 per CTA)
+constexpr int kPRows = 64;               // rows a CTA gathers in full width per tile; also heads per CTA
+constexpr int kChunk = kPRows * 128;     // 64 rows x 64 bf16 (128-byte rows, 128-byte swizzle): 8 KB
+constexpr int kQChunks = 9;              // 8 latent chunks + 1 rope chunk
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kSmemQ + kQChunks * kChunk;        // 73,728
+constexpr int kSmemV = kSmemK + kQChunks * kChunk;        // 147,456: two regions (keys 0-63, keys 64-127) of 4 chunks
+constexpr int kSmemP = kSmemV + 8 * kChunk;               // 212,992: two chunks (keys 0-63, keys 64-127)
+constexpr int kSmemCtl = kSmemP + 2 * kChunk;             // 229,376
+constexpr int kVHalfBytes = 4 * kChunk;                   // 32 KB: 64 keys x 256 values
+constexpr int kPairSoftmaxWarp0 = 4, kPairSoftmaxWarps = 8;
+constexpr int kPairKWarp0 = 12, kPairKWarps = 8;
+constexpr int kPairVWarp0 = 20, kPairVWarps = 8;
+constexpr int kPairThreads = 32 * 28;
+constexpr uint32_t kPairTmemCols = 512;
+constexpr uint32_t kPairColO = 0, kPairColS = 256;        // S buffer b at kPairColS + 64 b
+constexpr float kPairRescale = 8.0f;
+
+struct PairCtl {
+  uint64_t kfull;      // K producers filled this CTA's K chunks of tile j               (8 warps)
+  uint64_t vfull;      // V producers filled this CTA's V regions of tile j              (8 warps)
+  uint64_t sfull[2];   // q.K^T of a tile complete                                      (tcgen05.commit, both CTAs)
+  uint64_t pvdone;     // P.V of a tile complete                                        (tcgen05.commit, both CTAs)
+  uint64_t pfull;      // this CTA's P of tile j written                                (8 warps)
+  uint64_t sread[2];   // this CTA's softmax warps have the scores in registers         (8 warps)
+  // in CTA 0 only: the same four events of CTA 1, forwarded (one arrival each)
+  uint64_t kpeer, vpeer, ppeer, speer[2];
+  uint32_t tmem_base;
+  int abort;
+  int go[3][2];        // outcome of a role's latest waits (softmax, K producers, V producers)
+  float mt[2][4][64];  // [tile parity][key half * 2 + column half][head]: partial maxima; partial sums at the end
+};
+static_assert(kSmemCtl + sizeof(PairCtl) <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+constexpr size_t kPairSmemBytes = 232448;
+
+__device__ __forceinline__ uint32_t pair_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void pair_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t pair_map(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+// Notice from CTA 1 to CTA 0: a tcgen05.commit of no outstanding operation arrives at once on the mbarrier at this
+// offset in CTA 0 (mask 1). It travels on the tensor pipe's own path: measured one way 390 cycles, as fast as an
+// asynchronous remote store, but unlike that store it does not queue behind the SM's gathers in the load/store
+// unit (under load the store took 2000-3300 cycles to arrive; a remote mbarrier arrive holds the lane ~1400).
+__device__ __forceinline__ void pair_signal(uint32_t bar_local) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar_local), "h"(static_cast<uint16_t>(1))
+               : "memory");
+}
+
+__device__ __forceinline__ void mma2_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives (count 1) on the mbarrier at this offset in BOTH CTAs once all MMAs issued so far have completed
+__device__ __forceinline__ void tc2_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+
+// Warp-wide bounded wait that sleeps between probes. A probe is a shared-memory access and a handful of
+// instructions; two dozen warps probing back to back take issue slots and shared-memory cycles from the warps
+// that have work.
+template <int kSleepNs>
+__device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity) {
+  bool ok = true;
+  if (!mbar_test_wait(bar, parity)) {
+    const long long t0 = clock64();
+    while (true) {
+      __nanosleep(kSleepNs);
+      if (mbar_test_wait(bar, parity)) break;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Wait of a whole role (kThreads threads = full warps, named barrier kBarId): only the role's first warp probes the
+// mbarrier, the others block at the named barrier without issuing anything. The first warp publishes the outcome
+// in one of two slots (alternating: a thread is never more than one wait behind), every thread of the role reads
+// the same slot after the barrier, so the whole role takes the same branch; the barrier itself depends on no data
+// and every thread of the role reaches it on every path.
+template <int kSleepNs, int kBarId, int kThreads, int kRole>
+__device__ __forceinline__ bool pair_group_wait(PairCtl* ctl, uint32_t& nwait, uint32_t bar, uint32_t parity, bool first_warp) {
+  volatile int* go = &ctl->go[kRole][nwait & 1u];
+  ++nwait;
+  if (first_warp) {
+    const bool ok = pair_wait<kSleepNs>(bar, parity);
+    if ((threadIdx.x & 31) == 0) *go = ok ? 1 : 0;
+  }
+  asm volatile("bar.sync %0, %1;" ::"n"(kBarId), "n"(kThreads) : "memory");
+  return *go != 0;
+}
+
+// 8 int8 (two words) -> 8 bf16 of (value * scale), as `dequant16` but with the subtraction and the multiplication on pairs
+// (fp32x2 instructions): the byte placed in the mantissa of 2^23 gives 2^23 + 128 + x exactly, subtracting 8388736
+// leaves x, one fp32 multiply and one rounding to bf16: bf16(fp32(x) * scale) as the golden computes it.
+__device__ __forceinline__ uint4 pair_dequant8(const uint32_t w0, const uint32_t w1, const float scale) {
+  const float2 off = make_float2(-8388736.0f, -8388736.0f), sc = make_float2(scale, scale);
+  uint4 o;
+  {
+    const uint32_t w = w0 ^ 0x80808080u;
+    float2 a = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)));
+    float2 b = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)));
+    a = __fmul2_rn(__fadd2_rn(a, off), sc);
+    b = __fmul2_rn(__fadd2_rn(b, off), sc);
+    o.x = pack_bf16x2(a.x, a.y);
+    o.y = pack_bf16x2(b.x, b.y);
+  }
+  {
+    const uint32_t w = w1 ^ 0x80808080u;
+    float2 a = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)));
+    float2 b = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)));
+    a = __fmul2_rn(__fadd2_rn(a, off), sc);
+    b = __fmul2_rn(__fadd2_rn(b, off), sc);
+    o.z = pack_bf16x2(a.x, a.y);
+    o.w = pack_bf16x2(b.x, b.y);
+  }
+  return o;
+}
+
+// Paged row of a selected position, in 32 bits (the host side refuses caches of 2^31 rows or more): -1 for a
+// padding index or a rejected one (reported once through the status words).
+__device__ __forceinline__ int pair_row(const SfaParams& p, int idx, int entry) {
+  if (entry == kTableSkip) return -1;
+  const long long r = static_cast<long long>(entry) * p.block_size + idx % p.block_size;
+  if (entry < 0 || r >= p.n_rows) {
+    set_status(p.status, PTO_ST_BAD_PAGE, entry, 21);
+    return -1;
+  }
+  return static_cast<int>(r);
+}
+
+struct PairCtx {
+  PairCtl* ctl;
+  const int32_t* idx_row;  // this token's selected positions
+  int64_t q_row0;          // first query/output row of the token
+  uint32_t base, tmem_base, crank;
+  int ntiles, begin, end, ti, sp, bi;
+};
+
+// ================================ MMA issuer (CTA 0) ============================================
+// One thread, an event loop: P.V of the oldest tile whose P and V are in place in both CTAs, else the next
+// chunk (four MMAs) of the q.K^T in progress, else the start of the next q.K^T once both CTAs' keys are in
+// place and both CTAs' softmax warps have read the score buffer it overwrites.
+__device__ __forceinline__ void pair_role_mma(const SfaParams& p, const PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const int ntiles = c.ntiles;
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t idesc_qk = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 0, 128, kPT);
+    const uint32_t idesc_pv = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 1, 128, 256);
+    const uint32_t q_base = c.base + kSmemQ, k_base = c.base + kSmemK, v_base = c.base + kSmemV, p_base = c.base + kSmemP;
+    auto issue_qk_chunk = [&](int j, int ch) {
+      const uint32_t d = c.tmem_base + kPairColS + 64 * (j & 1);
+      const uint64_t a_desc = umma_desc_kmajor_sw128(q_base + ch * kChunk);
+      const uint64_t b_desc = umma_desc_kmajor_sw128(k_base + ch * kChunk);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) mma2_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (ch | k) != 0 ? 1u : 0u);
+      if (ch == kQChunks - 1) tc2_commit(smem_u32(&ctl->sfull[j & 1]));
+    };
+    auto issue_pv = [&](int j) {
+#pragma unroll 1
+      for (int dp = 0; dp < 2; ++dp) {  // value columns: 128 per CTA and MMA, two chunks of 64
+#pragma unroll 1
+        for (int kh = 0; kh < 2; ++kh) {  // keys 0-63, keys 64-127
+          const uint64_t a_desc = umma_desc_kmajor_sw128(p_base + kh * kChunk);
+          const uint64_t b_desc = desc_mnmajor_sw128(v_base + kh * kVHalfBytes + dp * 2 * kChunk, kChunk, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            mma2_f16_ss(c.tmem_base + kPairColO + 128 * dp, a_desc + 2 * k, b_desc + k * ((16 * 128) >> 4), idesc_pv,
+                        (j > 0 || kh > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+      }
+      tc2_commit(smem_u32(&ctl->pvdone));
+    };
+    auto done = [&](uint64_t* bar, uint32_t parity) -> bool { return mbar_test_wait(smem_u32(bar), parity); };
+    bool ok = true;
+    int qk_i = 0, qk_c = -1, pv_i = 0;  // qk_c: next chunk of the q.K^T in progress, -1 = not started
+    long long t_last = clock64();
+#ifdef PTO_PAIR_TIMELINE
+    int seen_k = 0, seen_v = 0, seen_p = 0;
+#endif
+    while (pv_i < ntiles) {
+      bool progressed = false;
+#ifdef PTO_PAIR_TIMELINE
+      if (seen_k < qk_i && done(&ctl->sfull[seen_k & 1], (seen_k >> 1) & 1)) { TLP(2, seen_k); ++seen_k; }  // q.K^T complete
+      if (seen_v < ntiles && seen_v <= pv_i && done(&ctl->vpeer, seen_v & 1)) { TLP(3, seen_v); ++seen_v; }
+      if (seen_p < ntiles && seen_p <= pv_i && done(&ctl->ppeer, seen_p & 1)) { TLP(15, seen_p); ++seen_p; }
+#endif
+#ifdef PAIR_EXP_PVFIRST
+      if (pv_i < qk_i && done(&ctl->pfull, pv_i & 1) && done(&ctl->ppeer, pv_i & 1) &&
+          done(&ctl->vfull, pv_i & 1) && done(&ctl->vpeer, pv_i & 1)) {
+        // (No cluster-scope fence here: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700 cycles per
+        // use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive on their
+        // own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA that this
+        // thread issues after seeing the notice reads CTA 1's shared memory from CTA 1's side.)
+        tc_fence_after();
+        TLP(8, pv_i);
+        issue_pv(pv_i);
+        TLP(9, pv_i);
+        ++pv_i;
+        progressed = true;
+      }
+      if (qk_c < 0 && qk_i < ntiles && done(&ctl->kfull, qk_i & 1) && done(&ctl->kpeer, qk_i & 1) &&
+          (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
+                        done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
+        tc_fence_after();
+        TLP(6, qk_i);
+        qk_c = 0;
+      }
+      if (qk_c >= 0) {
+        // all nine chunks at once: issuing them one per loop iteration was measured 2.5 times slower
+        for (; qk_c < kQChunks - 1; ++qk_c) issue_qk_chunk(qk_i, qk_c);
+        issue_qk_chunk(qk_i, qk_c);
+        if (++qk_c == kQChunks) {
+          TLP(7, qk_i);
+          qk_c = -1;
+          ++qk_i;
+        }
+        progressed = true;
+      }
+#else
+      if (qk_c < 0 && qk_i < ntiles && done(&ctl->kfull, qk_i & 1) && done(&ctl->kpeer, qk_i & 1) &&
+          (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
+                        done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
+        tc_fence_after();
+        TLP(6, qk_i);
+        qk_c = 0;
+      }
+      if (qk_c >= 0) {
+        // all nine chunks at once: issuing them one per loop iteration was measured 2.5 times slower
+        for (; qk_c < kQChunks - 1; ++qk_c) issue_qk_chunk(qk_i, qk_c);
+        issue_qk_chunk(qk_i, qk_c);
+        if (++qk_c == kQChunks) {
+          TLP(7, qk_i);
+          qk_c = -1;
+          ++qk_i;
+        }
+        progressed = true;
+      }
+      if (pv_i < qk_i && done(&ctl->pfull, pv_i & 1) && done(&ctl->ppeer, pv_i & 1) &&
+          done(&ctl->vfull, pv_i & 1) && done(&ctl->vpeer, pv_i & 1)) {
+        // (No cluster-scope fence here: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700 cycles per
+        // use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive on their
+        // own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA that this
+        // thread issues after seeing the notice reads CTA 1's shared memory from CTA 1's side.)
+        tc_fence_after();
+        TLP(8, pv_i);
+        issue_pv(pv_i);
+        TLP(9, pv_i);
+        ++pv_i;
+        progressed = true;
+      }
+#endif
+      if (progressed) {
+        t_last = clock64();
+      } else {
+        __nanosleep(20);
+        if (clock64() - t_last > kWaitBudgetCycles) {
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (!ok) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 50);
+    }
+  }
+  __syncwarp();
+}
+
+// ================================ forwarding (CTA 1) ============================================
+// One thread: whenever one of this CTA's four per-tile events completes, tell CTA 0.
+__device__ __forceinline__ void pair_role_relay(const SfaParams& p, const PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const int ntiles = c.ntiles;
+  if ((threadIdx.x & 31) == 0) {
+    int k_i = 0, v_i = 0, p_i = 0, s_i = 0;  // s_i: scores of tile s_i read (only tiles that have a successor two on)
+    const int s_n = ntiles > 2 ? ntiles - 2 : 0;
+    long long t_last = clock64();
+    bool ok = true;
+    while (k_i < ntiles || v_i < ntiles || p_i < ntiles || s_i < s_n) {
+      bool progressed = false;
+      if (p_i < ntiles && mbar_test_wait(smem_u32(&ctl->pfull), p_i & 1)) {
+        pair_signal(smem_u32(&ctl->ppeer));
+        TLP(15, p_i);
+        ++p_i;
+        progressed = true;
+      }
+      if (k_i < ntiles && mbar_test_wait(smem_u32(&ctl->kfull), k_i & 1)) {
+        pair_signal(smem_u32(&ctl->kpeer));
+        TLP(2, k_i);
+        ++k_i;
+        progressed = true;
+      }
+      if (v_i < ntiles && mbar_test_wait(smem_u32(&ctl->vfull), v_i & 1)) {
+        pair_signal(smem_u32(&ctl->vpeer));
+        TLP(3, v_i);
+        ++v_i;
+        progressed = true;
+      }
+      if (s_i < s_n && mbar_test_wait(smem_u32(&ctl->sread[s_i & 1]), (s_i >> 1) & 1)) {
+        pair_signal(smem_u32(&ctl->speer[s_i & 1]));
+        ++s_i;
+        progressed = true;
+      }
+      if (progressed) {
+        t_last = clock64();
+      } else {
+        __nanosleep(20);
+        if (clock64() - t_last > kWaitBudgetCycles) {
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (!ok) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 54);
+    }
+  }
+  __syncwarp();
+}
+
+// ================================ softmax =======================================================
+// Thread (TMEM lane L, column half ch): head L % 64, keys 64 (L / 64) + 32 ch .. +31 of the 128-key tile.
+__device__ __forceinline__ void pair_role_softmax(const SfaParams& p, const PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const uint32_t tmem_base = c.tmem_base;
+  const int ntiles = c.ntiles;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = warp & 3;                            // TMEM lane quarter this warp may access
+  const int ch = (warp - kPairSoftmaxWarp0) >> 2;      // column half
+  const int kh = sub >> 1;                             // key half of the tile
+  const int hg = sub & 1;                              // head group: heads 32 hg .. +31
+  const int head = 32 * hg + lane;
+  const int slot = kh * 2 + ch;                        // which of the head's four threads
+  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(sub * 32) << 16);
+  const uint32_t p_row = c.base + kSmemP + kh * kChunk + head * 128;
+  const int psw = head & 7;
+  const bool tl = threadIdx.x == 32 * kPairSoftmaxWarp0;
+  float m_seen = -INFINITY;  // the head's reference max (identical in its four threads)
+  float l_run = 0.f;         // this thread's share of the row sum
+  bool ok = true;
+  const bool first_warp = warp == kPairSoftmaxWarp0;
+  uint32_t nwait = 0;
+  auto meet = [&]() {  // the four warps of a head group: orders their mt writes before the reads (named barriers 4, 5)
+    if (hg == 0) asm volatile("bar.sync 4, 128;" ::: "memory");
+    else asm volatile("bar.sync 5, 128;" ::: "memory");
+  };
+  for (int j = 0; j < ntiles; ++j) {
+    const int b = j & 1;
+    ok = pair_group_wait<20, 1, 256, 0>(ctl, nwait, smem_u32(&ctl->sfull[b]), (j >> 1) & 1, first_warp);
+    if (!ok) break;
+    if (tl) TLP(10, j);
+    tc_fence_after();
+    float s[32];
+    {
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(lane_addr + kPairColS + 64 * b + 32 * ch, v);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(v[i]);
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->sread[b]));  // the score buffer may be overwritten
+    // ---- mask rows past the token's selected count (last tile only) --------------------------------
+    const int key0 = c.begin + j * kPT + 64 * kh + 32 * ch;
+    if (key0 + 32 > c.end) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (key0 + i >= c.end) s[i] = -INFINITY;
+      }
+    }
+    float mt2[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) mt2[i & 1] = fmaxf(mt2[i & 1], s[i]);
+    const float mt_part = fmaxf(mt2[0], mt2[1]) * p.scale_log2;  // scale > 0
+    ctl->mt[b][slot][head] = mt_part;
+    // ---- exponentials against a speculative reference (corrected by one factor once the head's max is known) --
+    float m_spec = (m_seen == -INFINITY || mt_part > m_seen + kPairRescale) ? mt_part : m_seen;
+    if (m_spec == -INFINITY) m_spec = 0.f;
+    const float neg_spec = -m_spec;
+    float ls2[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      s[i] = ex2f(fmaf(s[i], p.scale_log2, neg_spec));
+      ls2[i & 1] += s[i];
+    }
+    const float lsum = ls2[0] + ls2[1];
+    if (tl) TLP(11, j);
+    meet();
+    if (tl) TLP(12, j);
+    const float mt = fmaxf(fmaxf(ctl->mt[b][0][head], ctl->mt[b][1][head]), fmaxf(ctl->mt[b][2][head], ctl->mt[b][3][head]));
+    const float m_new = fmaxf(m_seen, mt);
+    const bool need = (m_new > m_seen + kPairRescale) || (m_seen == -INFINITY && m_new > -INFINITY);
+    float alpha = 1.f;
+    if (need) {
+      alpha = (m_seen == -INFINITY) ? 0.f : ex2f(m_seen - m_new);
+      m_seen = m_new;
+    }
+    const float m_ref = (m_seen == -INFINITY) ? 0.f : m_seen;
+    const float factor = ex2f(m_spec - m_ref);
+    l_run = l_run * alpha + lsum * factor;
+    // ---- the previous tile's P.V is complete: P may be overwritten, O is at rest ----------------------
+    if (j > 0) {
+      ok = pair_group_wait<20, 1, 256, 0>(ctl, nwait, smem_u32(&ctl->pvdone), (j - 1) & 1, first_warp);
+      if (!ok) break;
+      tc_fence_after();
+    }
+    if (tl) TLP(13, j);
+    if (j > 0 && __any_sync(0xffffffffu, need)) {  // rare: rescale this thread's 128 output columns
+#pragma unroll 1
+      for (int cc = 0; cc < 8; ++cc) {
+        uint32_t o[16];
+        tmem_ld_32x32b_x16(lane_addr + kPairColO + ch * 128 + cc * 16, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32b_x16(lane_addr + kPairColO + ch * 128 + cc * 16, o);
+      }
+      tc_wait_st();
+    }
+    // ---- P row piece into shared memory (A operand of P.V): 32 keys = four 16-byte units 4 ch .. 4 ch + 3 ----
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint4 w;
+      w.x = pack_bf16x2(s[8 * u] * factor, s[8 * u + 1] * factor);
+      w.y = pack_bf16x2(s[8 * u + 2] * factor, s[8 * u + 3] * factor);
+      w.z = pack_bf16x2(s[8 * u + 4] * factor, s[8 * u + 5] * factor);
+      w.w = pack_bf16x2(s[8 * u + 6] * factor, s[8 * u + 7] * factor);
+      sts_v4u(p_row + (((4 * ch + u) ^ psw) << 4), w);
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->pfull));
+    if (tl) TLP(14, j);
+  }
+  // ---- output ---------------------------------------------------------------------------------------
+  if (ok) ok = pair_group_wait<20, 1, 256, 0>(ctl, nwait, smem_u32(&ctl->pvdone), (ntiles - 1) & 1, first_warp);
+  if (tl) TLP(5, 20);  // last P.V complete
+  float l_tot = 0.f;
+  if (ok) {
+    ctl->mt[ntiles & 1][slot][head] = l_run;
+    meet();
+    const int b = ntiles & 1;
+    l_tot = (ctl->mt[b][0][head] + ctl->mt[b][1][head]) + (ctl->mt[b][2][head] + ctl->mt[b][3][head]);
+  }
+  if (ok) {
+    tc_fence_after();
+    const int head_g = 64 * static_cast<int>(c.crank) + head;  // head of the token
+    const int dv0 = 256 * kh + 128 * ch;                         // this thread's 128 output values
+    if (p.n_split == 1) {
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* dst = p.out + (c.q_row0 + head_g) * 512 + dv0;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(lane_addr + kPairColO + ch * 128 + cc * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = w;
+        }
+      }
+    } else {
+      const int64_t prow = (static_cast<int64_t>(c.ti) * p.n_split + c.sp) * p.nq + head_g;
+      float* dst = p.part_o + prow * 512 + dv0;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(lane_addr + kPairColO + ch * 128 + cc * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+        }
+      }
+      if (slot == 0) {
+        p.part_ml[prow * 2] = m_seen;
+        p.part_ml[prow * 2 + 1] = l_tot;
+      }
+    }
+  }
+  if (!ok && lane == 0) {
+    ctl->abort = 1;
+    set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 51);
+  }
+}
+
+// ================================ K producers ===================================================
+// 256 threads; warp w owns rows 8w .. 8w+7 of this CTA's 64. A gather instruction reads ONE row with the whole
+// warp (lane l takes the 16 latent bytes l of the row's 512: four full 128-byte lines per instruction), so a
+// thread holds unit l of eight rows. (Four threads per row, each reading its own 16 bytes of eight different
+// lines, cost eight lines per instruction; with the V producers' gathers on top, the load/store unit's queue
+// then delayed the tensor core's operand reads: q.K^T took 5-6 k cycles instead of 2.5 k.)
+// Unit l (16 int8 -> 16 bf16 = two 16-byte stores) goes to chunk l / 4, store units 2 (l % 4) and 2 (l % 4) + 1 of
+// the row's 128 bytes; the lanes of an odd chunk store the second half first, so that the eight lanes of a
+// quarter-warp (two chunks, same row) hit eight different bank groups. Lane r % 8 also walks the look-ahead
+// chain of row 8w + r % 8: the selected index four tiles ahead, its block-table entry three tiles ahead, an L2
+// prefetch of the row two tiles ahead, the row itself (by all lanes) one tile ahead.
+template <bool kPacked>
+__device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const int ntiles = c.ntiles, bi = c.bi;
+  const int lane = threadIdx.x & 31;
+  const int ptid = threadIdx.x - kPairKWarp0 * 32;
+  const int w = ptid >> 5;
+  const int my_row = 64 * static_cast<int>(c.crank) + 8 * w + (lane & 7);  // key of the tile this lane looks ahead for
+  const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
+  const int n_mine = c.end - (c.begin + my_row);  // entry j * 128 of idx_ptr is valid iff j * 128 < n_mine
+  constexpr int stride_n = kPacked ? 656 : 512, stride_r = kPacked ? 656 : 128, stride_s = kPacked ? 656 : 16;
+  // (the base pointers are read from the parameter block where they are used: they would otherwise occupy six
+  // registers across the whole tile loop)
+#define PAIR_KN reinterpret_cast<const uint8_t*>(p.kn)
+#define PAIR_ROPE (kPacked ? PAIR_KN + 512 : reinterpret_cast<const uint8_t*>(p.kr))
+#define PAIR_SCL (kPacked ? PAIR_KN + 640 : reinterpret_cast<const uint8_t*>(p.kn_scales))
+  struct RowRegs {
+    uint4 d[8];  // unit `lane` of rows 8w + 0..7
+    uint4 r[2];  // rope unit lane % 8 of rows 8w + 4i + lane / 8
+    float sc;    // scale lane % 4 of row 8w + lane / 4
+  };
+  auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
+  // `phys`: this lane's look-ahead row of the tile (-1: padding or rejected -> zeros with scale 0)
+  auto issue_loads = [&](RowRegs& r, int phys) {
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int pm = __shfl_sync(0xffffffffu, phys, m);
+      r.d[m] = make_uint4(0, 0, 0, 0);
+      if (pm >= 0) r.d[m] = ldg_pinned_v4(PAIR_KN + static_cast<int64_t>(pm) * stride_n + lane * 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int pr = __shfl_sync(0xffffffffu, phys, 4 * i + (lane >> 3));
+      r.r[i] = make_uint4(0, 0, 0, 0);
+      if (pr >= 0) r.r[i] = ldg_pinned_v4(PAIR_ROPE + static_cast<int64_t>(pr) * stride_r + (lane & 7) * 16);
+    }
+    const int ps = __shfl_sync(0xffffffffu, phys, lane >> 2);
+    r.sc = 0.f;
+    if (ps >= 0) asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(r.sc) : "l"(PAIR_SCL + static_cast<int64_t>(ps) * stride_s + (lane & 3) * 4));
+  };
+  auto prefetch_row = [&](int phys) {  // lanes r, r+8, r+16, r+24 share a row: one of its four latent lines each, two of them the rest
+    if (phys < 0) return;
+    if (kPacked) {
+      const uint8_t* a = PAIR_KN + static_cast<int64_t>(phys) * 656;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a + (lane >> 3) * 128));
+      if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 512 + (lane >> 3) * 128));
+    } else {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(PAIR_KN + static_cast<int64_t>(phys) * 512 + (lane >> 3) * 128));
+      if (lane < 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(PAIR_ROPE + static_cast<int64_t>(phys) * 128));
+      else if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(PAIR_SCL + static_cast<int64_t>(phys) * 16));
+    }
+  };
+  const uint32_t k_rows = c.base + kSmemK + 8 * w * 128;  // row 8w of chunk 0
+  const int chunk_off = (lane >> 2) * kChunk;
+  const bool odd = ((lane >> 2) & 1) != 0;
+  bool ok = true;
+  uint32_t nwait = 0;
+  RowRegs ra;
+  pdl_wait();          // the selected indices come from the kernel before this one, which may still be running
+  int row_n;           // this lane's row of tile j+1
+  int idx_a, entry_a;  // tile j+2
+  int idx_b;           // tile j+3
+  {
+    const int idx0 = load_idx(0), idx1 = load_idx(1);
+    idx_a = load_idx(2);
+    idx_b = load_idx(3);
+    const int e0 = tc_table_entry(p, bi, idx0);
+    const int e1 = tc_table_entry(p, bi, idx1);
+    entry_a = tc_table_entry(p, bi, idx_a);
+    issue_loads(ra, pair_row(p, idx0, e0));
+    row_n = pair_row(p, idx1, e1);
+    prefetch_row(row_n);
+  }
+  for (int j = 0; j < ntiles; ++j) {
+    if (j > 0) {  // the q.K^T of the previous tile has read the chunks
+      ok = pair_group_wait<32, 2, 256, 1>(ctl, nwait, smem_u32(&ctl->sfull[(j - 1) & 1]), ((j - 1) >> 1) & 1, ptid < 32);
+      if (!ok) break;
+    }
+    if (ptid == 0) TLP(0, j);
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {  // row 8w + m (its swizzle term is m)
+      const float scale = __shfl_sync(0xffffffffu, ra.sc, 4 * m + (lane >> 3));
+      const uint32_t row_addr = k_rows + chunk_off + m * 128;
+      const uint32_t a = ((2 * (lane & 3)) ^ m) << 4, b = ((2 * (lane & 3) + 1) ^ m) << 4;
+      // first half of the unit (bytes 0-7) belongs at `a`, second half at `b`; odd chunks store the second first
+      sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? ra.d[m].z : ra.d[m].x, odd ? ra.d[m].w : ra.d[m].y, scale));
+      sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? ra.d[m].x : ra.d[m].z, odd ? ra.d[m].y : ra.d[m].w, scale));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // rope of row 8w + 4i + lane / 8
+      const int r8 = 4 * i + (lane >> 3);
+      sts_v4u(k_rows + 8 * kChunk + r8 * 128 + (((lane & 7) ^ r8) << 4), ra.r[i]);
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->kfull));
+    if (ptid == 0) TLP(1, j);
+    if (j + 1 < ntiles) issue_loads(ra, row_n);  // rows of tile j+1 (in L2: prefetched a tile ago)
+    row_n = pair_row(p, idx_a, entry_a);         // tile j+2: into L2
+    prefetch_row(row_n);
+    idx_a = idx_b;
+    entry_a = tc_table_entry(p, bi, idx_a);      // block-table entries of tile j+3
+    idx_b = load_idx(j + 4);
+  }
+  if (!ok && lane == 0) {
+    ctl->abort = 1;
+    set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 52);
+  }
+}
+
+// ================================ V producers ===================================================
+// 256 threads; warp w owns rows 16w .. 16w+15 of the tile's 128. A gather instruction reads this CTA's half of
+// the value columns (256 of the 512 latent bytes) of TWO rows: lane l takes unit l % 16 of row 2m + l / 16, again
+// whole 128-byte lines (the other CTA's K producers have fetched or are fetching the same lines: L2 hits). Unit u
+// goes to V chunk u / 4 of the row's key half, store units 2 (u % 4) and 2 (u % 4) + 1, second half first in odd
+// chunks as in the K producers. Lane r % 16 walks the look-ahead chain of row 16w + r % 16 (no L2 prefetch: the
+// row's owner issues it).
+template <bool kPacked>
+__device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const int ntiles = c.ntiles;
+  const int lane = threadIdx.x & 31;
+  const int vtid = threadIdx.x - kPairVWarp0 * 32;
+  const int w = vtid >> 5;
+  const int u = lane & 15, s2 = lane >> 4;
+  const int my_row = 16 * w + u;  // key of the tile this lane looks ahead for
+  const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
+  const int n_mine = c.end - (c.begin + my_row);
+  const int col0 = 256 * static_cast<int>(c.crank);  // first latent byte of this CTA's value columns
+  constexpr int stride_n = kPacked ? 656 : 512, stride_s = kPacked ? 656 : 16;
+  struct RowRegs {
+    uint4 d[8];  // unit u of rows 16w + 2m + s2
+    float sc;    // scale lane % 2 (of this CTA's two) of row 16w + lane / 2
+  };
+  auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
+  auto issue_loads = [&](RowRegs& r, int phys) {
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int pm = __shfl_sync(0xffffffffu, phys, 2 * m + s2);
+      r.d[m] = make_uint4(0, 0, 0, 0);
+      if (pm >= 0) r.d[m] = ldg_pinned_v4(PAIR_KN + static_cast<int64_t>(pm) * stride_n + col0 + u * 16);
+    }
+    const int ps = __shfl_sync(0xffffffffu, phys, lane >> 1);
+    r.sc = 0.f;
+    if (ps >= 0) asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(r.sc) : "l"(PAIR_SCL + static_cast<int64_t>(ps) * stride_s + (col0 >> 5) + (lane & 1) * 4));
+  };
+  // rows 16w .. 16w+15 lie in key half w / 4; row (16w + x) % 64 of chunk u / 4
+  const uint32_t v_rows = c.base + kSmemV + (w >> 2) * kVHalfBytes + (u >> 2) * kChunk + ((16 * w) & 63) * 128;
+  const bool odd = ((u >> 2) & 1) != 0;
+  bool ok = true;
+  uint32_t nwait = 0;
+  RowRegs ra;
+  pdl_wait();
+  int row_n, idx_a, entry_a;  // this lane's row of tile j+1; index and block-table entry of tile j+2
+  {
+    const int idx0 = load_idx(0), idx1 = load_idx(1);
+    idx_a = load_idx(2);
+    const int e0 = tc_table_entry(p, c.bi, idx0);
+    const int e1 = tc_table_entry(p, c.bi, idx1);
+    entry_a = tc_table_entry(p, c.bi, idx_a);
+    issue_loads(ra, pair_row(p, idx0, e0));
+    row_n = pair_row(p, idx1, e1);
+  }
+  for (int j = 0; j < ntiles; ++j) {
+    if (j > 0) {  // the P.V of the previous tile has read the V regions
+      ok = pair_group_wait<32, 3, 256, 2>(ctl, nwait, smem_u32(&ctl->pvdone), (j - 1) & 1, vtid < 32);
+      if (!ok) break;
+    }
+    if (vtid == 0) TLP(4, j);
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {  // row 16w + 2m + s2: swizzle term (2m + s2) % 8, scale held by lane 2 (2m + s2) + u / 8
+      const float scale = __shfl_sync(0xffffffffu, ra.sc, 2 * (2 * m + s2) + (u >> 3));
+      const int x = (2 * m + s2) & 7;
+      const uint32_t row_addr = v_rows + (2 * m + s2) * 128;
+      const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
+      sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? ra.d[m].z : ra.d[m].x, odd ? ra.d[m].w : ra.d[m].y, scale));
+      sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? ra.d[m].x : ra.d[m].z, odd ? ra.d[m].y : ra.d[m].w, scale));
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->vfull));
+    if (vtid == 0) TLP(5, j);
+    if (j + 1 < ntiles) issue_loads(ra, row_n);
+    row_n = pair_row(p, idx_a, entry_a);
+    idx_a = load_idx(j + 3);
+    entry_a = tc_table_entry(p, c.bi, idx_a);  // (the index was requested this iteration: one trip to L2 here, after the
+                                               // tile's stores, a whole tile before the next wait)
+  }
+  if (!ok && lane == 0) {
+    ctl->abort = 1;
+    set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 53);
+  }
+}
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+sfa_pair_kernel(const __grid_constant__ SfaParams p) {
+  extern __shared__ __align__(1024) uint8_t sfa_pair_smem[];
+  const uint32_t base = smem_u32(sfa_pair_smem);
+  if ((base & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) set_status(p.status, PTO_ST_WAIT_EXPIRED, static_cast<int>(base), 55);
+    return;
+  }
+  if (threadIdx.x == 0) TLP(0, 20);  // kernel entry
+  PairCtx c;
+  c.base = base;
+  c.ctl = reinterpret_cast<PairCtl*>(sfa_pair_smem + kSmemCtl);
+  PairCtl* ctl = c.ctl;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  c.crank = pair_ctarank();
+  const uint32_t crank = c.crank;
+  const int bid = blockIdx.x >> 1;  // cluster index
+  c.sp = bid % p.n_split;
+  c.ti = bid / p.n_split;
+  c.bi = c.ti / p.s1;
+  const int si = c.ti % p.s1;
+
+  int n = p.act_seq[c.bi] - p.s1 + 1 + si;
+  n = max(0, min(n, p.topk_k));
+  const int tiles_total = (n + kPT - 1) / kPT;
+  const int tiles_per_split = (tiles_total + p.n_split - 1) / p.n_split;
+  c.begin = min(n, c.sp * tiles_per_split * kPT);
+  c.end = min(n, (c.sp + 1) * tiles_per_split * kPT);
+  c.ntiles = (c.end - c.begin + kPT - 1) / kPT;
+  c.idx_row = p.topk + static_cast<int64_t>(c.ti) * p.topk_k;
+  c.q_row0 = static_cast<int64_t>(c.ti) * p.nq_total + p.head_begin;
+
+  if (c.ntiles == 0) {  // same decision in both CTAs of the pair
+    if (p.n_split == 1) {
+      for (int e = tid; e < 64 * 64; e += kPairThreads) {
+        const int r = e >> 6, cc = e & 63;
+        *reinterpret_cast<uint4*>(p.out + (c.q_row0 + 64 * crank + r) * 512 + cc * 8) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      for (int r = tid; r < 64; r += kPairThreads) {
+        float* ml = p.part_ml + ((static_cast<int64_t>(c.ti) * p.n_split + c.sp) * p.nq + 64 * crank + r) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+    }
+    return;
+  }
+
+  // ---- setup ------------------------------------------------------------------------------------
+  if (tid == 0) {
+    mbar_init(smem_u32(&ctl->kfull), kPairKWarps);
+    mbar_init(smem_u32(&ctl->vfull), kPairVWarps);
+    mbar_init(smem_u32(&ctl->pvdone), 1);
+    mbar_init(smem_u32(&ctl->pfull), kPairSoftmaxWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->sfull[b]), 1);
+      mbar_init(smem_u32(&ctl->sread[b]), kPairSoftmaxWarps);
+      mbar_init(smem_u32(&ctl->speer[b]), 1);
+    }
+    mbar_init(smem_u32(&ctl->kpeer), 1);
+    mbar_init(smem_u32(&ctl->vpeer), 1);
+    mbar_init(smem_u32(&ctl->ppeer), 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(kPairTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  // this CTA's 64 query rows into shared memory, nine swizzled chunks of 64 dims (A operand of q.K^T): 64 x 72
+  // 16-byte units, six per thread, all loads in flight before the first store
+  {
+    const int64_t row0 = c.q_row0 + 64 * crank;
+    uint4 w[6];
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+      const int e = tid + i * kPairThreads;
+      if (e < 64 * 72) {
+        const int r = e / 72, u = e % 72;
+        w[i] = (u < 64) ? __ldg(reinterpret_cast<const uint4*>(p.q_nope + (row0 + r) * 512) + u)
+                        : __ldg(reinterpret_cast<const uint4*>(p.q_rope + (row0 + r) * 64) + (u - 64));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+      const int e = tid + i * kPairThreads;
+      if (e < 64 * 72) {
+        const int r = e / 72, u = e % 72;
+        sts_v4u(base + kSmemQ + (u >> 3) * kChunk + r * 128 + (((u & 7) ^ (r & 7)) << 4), w[i]);
+      }
+    }
+    fence_proxy_async();
+  }
+  tc_fence_before();
+  __syncthreads();
+  pair_cluster_sync();  // both CTAs' barriers are initialised and both Q halves are in place
+  tc_fence_after();
+  c.tmem_base = ctl->tmem_base;
+  if (threadIdx.x == 0) TLP(1, 20);  // roles start
+
+#ifdef PAIR_EXP_NOREG
+#define PAIR_SETREG(x)
+#else
+#define PAIR_SETREG(x) asm volatile(x)
+#endif
+  if (warp < kPairSoftmaxWarp0) {
+    PAIR_SETREG("setmaxnreg.dec.sync.aligned.u32 24;");
+    if (warp == 0 && crank == 0) pair_role_mma(p, c);
+    if (warp == 1 && crank == 1) pair_role_relay(p, c);
+  } else if (warp < kPairKWarp0) {
+    PAIR_SETREG("setmaxnreg.inc.sync.aligned.u32 104;");
+    pair_role_softmax(p, c);
+  } else if (warp < kPairVWarp0) {
+    PAIR_SETREG("setmaxnreg.inc.sync.aligned.u32 72;");  // (no change of the count; without it ptxas spills in this role)
+    if (p.packed) pair_role_kproducer<true>(p, c);
+    else pair_role_kproducer<false>(p, c);
+  } else {
+    PAIR_SETREG("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (p.packed) pair_role_vproducer<true>(p, c);
+    else pair_role_vproducer<false>(p, c);
+  }
+
+  // ---- teardown: neither CTA may leave while the peer's MMAs can still read its shared memory --------
+  // (nothing is kept in registers across the roles: what the teardown needs is read again)
+  if (threadIdx.x == 32 * kPairSoftmaxWarp0) TLP(2, 20);  // first softmax warp done with its output
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) TLP(3, 20);
+  pair_cluster_sync();
+  if ((threadIdx.x >> 5) == 0) {
+    tc_fence_after();
+    const uint32_t tmem = reinterpret_cast<const PairCtl*>(sfa_pair_smem + kSmemCtl)->tmem_base;
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPairTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0) TLP(4, 20);  // exit
+}
+
+}  // namespace
+
+#ifdef PTO_PAIR_TIMELINE
+extern "C" int pto_debug_pair_timeline(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_pair_tl, sizeof(long long) * n));
+}
+#endif
+
+// split of a token's selected rows over clusters so that the grid fills the SM pairs once
+int sfa_pair_split(int t, int num_sms) {
+  const int pairs = num_sms / 2;
+  if (t >= pairs) return 1;
+  int s = pairs / (t > 0 ? t : 1);
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+cudaError_t launch_sfa_pair(const SfaParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(sfa_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kPairSmemBytes));
+  if (e != cudaSuccess) return e;
+  const int t = p.b * p.s1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(t) * p.n_split * 2, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 2 : 1;
+  count_launch();
+  return cudaLaunchKernelEx(&cfg, sfa_pair_kernel, p);
+}
+
+}  // namespace pto

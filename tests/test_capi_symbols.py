@@ -48,7 +48,7 @@ def test_host_only_calls(lib):
     assert lib.pto_li_workspace_bytes(0, 256, 128) == 0
     # 64 tokens x 2 head blocks fill the device: unsplit, status words only
     assert lib.pto_sfa_workspace_bytes(80, 128) == 256
-    assert lib.pto_sfa_workspace_bytes(2, 128) > 2 * 32 * 128 * 512 * 4
+    assert lib.pto_sfa_workspace_bytes(2, 128) > 2 * 16 * 128 * 512 * 4
     assert lib.pto_decode_workspace_bytes(64, 512, 128, 128) == 256 + 64 * 512 * 128 * 4 + lib.pto_sfa_workspace_bytes(64, 128) - 256
 
 

@@ -115,14 +115,16 @@ def test_bf16_cache_matches_reference_fixture(name):
                 _check(got[bi, i], want[bi, i])
             else:
                 assert torch.all(got[bi, i] == 0)
-    # same values in the K tiles, same arithmetic after them: bit-identical to the int8 path
-    assert torch.equal(got, _run(d))
+    # same values in the key tiles as the int8 path dequantises to; the two caches run on different kernels
+    # (the int8 cache on the pair of SMs that shares every MMA, the bf16 cache on the pair that splits the
+    # contraction), so the outputs agree to the rounding of another summation order, not bit for bit
+    _check(got, _run(d))
 
 
 def test_bf16_cache_many_tokens_and_split():
     """Both launch shapes of the bf16 branch: config 0 (2 tokens, split over CTAs) and 80 ragged tokens."""
     d = gen.make_config(0)
-    assert torch.equal(_run(d, bf16_cache=True), _run(d))
+    _check(_run(d, bf16_cache=True), _run(d))
     g = torch.Generator().manual_seed(18)
     act = torch.randint(1, 900, (40,), generator=g).tolist()
     d = gen.make_inputs(act, s1=2, seed=23, with_indexer=False, with_topk=True)
@@ -130,10 +132,17 @@ def test_bf16_cache_many_tokens_and_split():
                                    d.key_rope_2d, None, d.topk_indices, d.block_table, d.act_seq, d.s1)
     got = _run(d, bf16_cache=True, prefill=True)
     _check(got, want)
-    assert torch.equal(got, _run(d))
+    _check(got, _run(d))
 
 
 def test_bf16_cache_head_slice_is_refused():
     d = gen.make_inputs([300], s1=1, seed=3, with_indexer=False, with_topk=True, attn_heads=16)
     with pytest.raises(RuntimeError, match="128 heads"):
         _run(d, nq=16, bf16_cache=True)
+
+
+@pytest.mark.parametrize("name", SFA_CASES)
+def test_packed_rows_equal_split_arrays_bit_for_bit(name):
+    """The packed 656-byte rows and the three split arrays hold the same bytes and go through the same kernel."""
+    d, _ = load_case(name)
+    assert torch.equal(_run(d, packed=True), _run(d, packed=False))
