@@ -63,14 +63,18 @@ constexpr uint32_t kPairColO = 0, kPairColS = 256;        // S buffer b at kPair
 constexpr float kPairRescale = 8.0f;
 
 struct PairCtl {
-  uint64_t kfull;      // K producers filled this CTA's K chunks of tile j               (8 warps)
-  uint64_t vfull;      // V producers filled this CTA's V regions of tile j              (8 warps)
-  uint64_t sfull[2];   // q.K^T of a tile complete                                      (tcgen05.commit, both CTAs)
+  // The K chunks and the V regions are each handed over in two halves, so that a refill runs behind the MMAs that
+  // read the other half: K half 0 = chunks 0-3, half 1 = chunks 4-8 (with the rope chunk); V half h = keys 64h..+63.
+  uint64_t kfull[2];   // K producers filled half h of this CTA's K chunks of tile j     (8 warps)
+  uint64_t kfree[2];   // the q.K^T MMAs that read half h are complete                   (tcgen05.commit, both CTAs)
+  uint64_t vfull[2];   // V producers filled this CTA's V region of key half h           (8 warps)
+  uint64_t vfree[2];   // the P.V MMAs that read key half h are complete                 (tcgen05.commit, both CTAs)
+  uint64_t sfull[2];   // q.K^T of a tile complete (score buffer b)                      (tcgen05.commit, both CTAs)
   uint64_t pvdone;     // P.V of a tile complete                                        (tcgen05.commit, both CTAs)
   uint64_t pfull;      // this CTA's P of tile j written                                (8 warps)
   uint64_t sread[2];   // this CTA's softmax warps have the scores in registers         (8 warps)
-  // in CTA 0 only: the same four events of CTA 1, forwarded (one arrival each)
-  uint64_t kpeer, vpeer, ppeer, speer[2];
+  // in CTA 0 only: the same events of CTA 1, forwarded (one arrival each)
+  uint64_t kpeer[2], vpeer[2], ppeer, speer[2];
   uint32_t tmem_base;
   int abort;
   int go[3][2];        // outcome of a role's latest waits (softmax, K producers, V producers)
@@ -200,120 +204,111 @@ struct PairCtx {
   int ntiles, begin, end, ti, sp, bi;
 };
 
+// The one meeting of all threads of the pair before the tile loop: barriers initialised, tensor memory allocated,
+// both Q halves in shared memory. Every role calls it exactly once; the producers call it after they have
+// requested their first rows, so that the index -> block table -> row chain of the first tile (three dependent
+// trips to memory) runs beside the set-up instead of after it.
+__device__ __forceinline__ uint32_t pair_setup_sync(PairCtl* ctl) {
+  tc_fence_before();
+  __syncthreads();
+  pair_cluster_sync();
+  tc_fence_after();
+  if (threadIdx.x == 0) TLP(1, 20);  // roles start
+  return ctl->tmem_base;
+}
+
 // ================================ MMA issuer (CTA 0) ============================================
-// One thread, an event loop: P.V of the oldest tile whose P and V are in place in both CTAs, else the next
-// chunk (four MMAs) of the q.K^T in progress, else the start of the next q.K^T once both CTAs' keys are in
-// place and both CTAs' softmax warps have read the score buffer it overwrites.
-__device__ __forceinline__ void pair_role_mma(const SfaParams& p, const PairCtx c) {
+// One thread, an event loop over four actions, each as soon as both CTAs' operands for it are in place:
+//   q.K^T first half  (chunks 0-3: 16 MMAs)  needs K half 0 of the tile and the score buffer it overwrites read
+//   q.K^T second half (chunks 4-8: 20 MMAs)  needs K half 1; completes the tile's scores
+//   P.V first half    (keys 0-63:   8 MMAs)  needs P of the tile and V key half 0
+//   P.V second half   (keys 64-127: 8 MMAs)  needs V key half 1; completes the tile's P.V
+// After each action a commit hands the half it read back to its producers, so that the refill for the next tile
+// runs behind the MMAs that read the other half. An operation in progress is finished before another starts.
+__device__ __forceinline__ void pair_role_mma(const SfaParams& p, PairCtx c) {
   PairCtl* ctl = c.ctl;
   const int ntiles = c.ntiles;
+  c.tmem_base = pair_setup_sync(ctl);
   if ((threadIdx.x & 31) == 0) {
     const uint32_t idesc_qk = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 0, 128, kPT);
     const uint32_t idesc_pv = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 1, 128, 256);
     const uint32_t q_base = c.base + kSmemQ, k_base = c.base + kSmemK, v_base = c.base + kSmemV, p_base = c.base + kSmemP;
-    auto issue_qk_chunk = [&](int j, int ch) {
+    auto issue_qk_chunks = [&](int j, int ch0, int ch1) {
       const uint32_t d = c.tmem_base + kPairColS + 64 * (j & 1);
-      const uint64_t a_desc = umma_desc_kmajor_sw128(q_base + ch * kChunk);
-      const uint64_t b_desc = umma_desc_kmajor_sw128(k_base + ch * kChunk);
+#pragma unroll 1
+      for (int ch = ch0; ch < ch1; ++ch) {
+        const uint64_t a_desc = umma_desc_kmajor_sw128(q_base + ch * kChunk);
+        const uint64_t b_desc = umma_desc_kmajor_sw128(k_base + ch * kChunk);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) mma2_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (ch | k) != 0 ? 1u : 0u);
-      if (ch == kQChunks - 1) tc2_commit(smem_u32(&ctl->sfull[j & 1]));
+        for (int k = 0; k < 4; ++k) mma2_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (ch | k) != 0 ? 1u : 0u);
+      }
     };
-    auto issue_pv = [&](int j) {
+    auto issue_pv_half = [&](int j, int kh) {  // keys 64 kh .. +63 into both pairs of value columns
+      const uint64_t a_desc = umma_desc_kmajor_sw128(p_base + kh * kChunk);
 #pragma unroll 1
       for (int dp = 0; dp < 2; ++dp) {  // value columns: 128 per CTA and MMA, two chunks of 64
-#pragma unroll 1
-        for (int kh = 0; kh < 2; ++kh) {  // keys 0-63, keys 64-127
-          const uint64_t a_desc = umma_desc_kmajor_sw128(p_base + kh * kChunk);
-          const uint64_t b_desc = desc_mnmajor_sw128(v_base + kh * kVHalfBytes + dp * 2 * kChunk, kChunk, 1024);
+        const uint64_t b_desc = desc_mnmajor_sw128(v_base + kh * kVHalfBytes + dp * 2 * kChunk, kChunk, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            mma2_f16_ss(c.tmem_base + kPairColO + 128 * dp, a_desc + 2 * k, b_desc + k * ((16 * 128) >> 4), idesc_pv,
-                        (j > 0 || kh > 0 || k > 0) ? 1u : 0u);
-          }
+        for (int k = 0; k < 4; ++k) {
+          mma2_f16_ss(c.tmem_base + kPairColO + 128 * dp, a_desc + 2 * k, b_desc + k * ((16 * 128) >> 4), idesc_pv,
+                      (j > 0 || kh > 0 || k > 0) ? 1u : 0u);
         }
       }
-      tc2_commit(smem_u32(&ctl->pvdone));
     };
     auto done = [&](uint64_t* bar, uint32_t parity) -> bool { return mbar_test_wait(smem_u32(bar), parity); };
     bool ok = true;
-    int qk_i = 0, qk_c = -1, pv_i = 0;  // qk_c: next chunk of the q.K^T in progress, -1 = not started
+    int qk_i = 0, qk_h = 0, pv_i = 0, pv_h = 0;  // next tile and half of each operation
     long long t_last = clock64();
 #ifdef PTO_PAIR_TIMELINE
-    int seen_k = 0, seen_v = 0, seen_p = 0;
+    int seen_s = 0, seen_p = 0;
 #endif
+    // (No cluster-scope fence before the MMAs: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700
+    // cycles per use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive
+    // on their own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA
+    // issued here after the notice reads CTA 1's shared memory from CTA 1's side.)
     while (pv_i < ntiles) {
       bool progressed = false;
 #ifdef PTO_PAIR_TIMELINE
-      if (seen_k < qk_i && done(&ctl->sfull[seen_k & 1], (seen_k >> 1) & 1)) { TLP(2, seen_k); ++seen_k; }  // q.K^T complete
-      if (seen_v < ntiles && seen_v <= pv_i && done(&ctl->vpeer, seen_v & 1)) { TLP(3, seen_v); ++seen_v; }
+      if (seen_s < qk_i && done(&ctl->sfull[seen_s & 1], (seen_s >> 1) & 1)) { TLP(2, seen_s); ++seen_s; }  // q.K^T complete
       if (seen_p < ntiles && seen_p <= pv_i && done(&ctl->ppeer, seen_p & 1)) { TLP(15, seen_p); ++seen_p; }
 #endif
-#ifdef PAIR_EXP_PVFIRST
-      if (pv_i < qk_i && done(&ctl->pfull, pv_i & 1) && done(&ctl->ppeer, pv_i & 1) &&
-          done(&ctl->vfull, pv_i & 1) && done(&ctl->vpeer, pv_i & 1)) {
-        // (No cluster-scope fence here: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700 cycles per
-        // use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive on their
-        // own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA that this
-        // thread issues after seeing the notice reads CTA 1's shared memory from CTA 1's side.)
+      const uint32_t qph = qk_i & 1, pph = pv_i & 1;
+      if (qk_i < ntiles && qk_h == 1 && done(&ctl->kfull[1], qph) && done(&ctl->kpeer[1], qph)) {
         tc_fence_after();
-        TLP(8, pv_i);
-        issue_pv(pv_i);
+        issue_qk_chunks(qk_i, 4, kQChunks);
+        tc2_commit(smem_u32(&ctl->kfree[1]));
+        tc2_commit(smem_u32(&ctl->sfull[qk_i & 1]));
+        TLP(7, qk_i);
+        qk_h = 0;
+        ++qk_i;
+        progressed = true;
+      } else if (pv_h == 1 && done(&ctl->vfull[1], pph) && done(&ctl->vpeer[1], pph)) {
+        tc_fence_after();
+        issue_pv_half(pv_i, 1);
+        tc2_commit(smem_u32(&ctl->vfree[1]));
+        tc2_commit(smem_u32(&ctl->pvdone));
         TLP(9, pv_i);
+        pv_h = 0;
         ++pv_i;
         progressed = true;
-      }
-      if (qk_c < 0 && qk_i < ntiles && done(&ctl->kfull, qk_i & 1) && done(&ctl->kpeer, qk_i & 1) &&
-          (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
-                        done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
-        tc_fence_after();
-        TLP(6, qk_i);
-        qk_c = 0;
-      }
-      if (qk_c >= 0) {
-        // all nine chunks at once: issuing them one per loop iteration was measured 2.5 times slower
-        for (; qk_c < kQChunks - 1; ++qk_c) issue_qk_chunk(qk_i, qk_c);
-        issue_qk_chunk(qk_i, qk_c);
-        if (++qk_c == kQChunks) {
-          TLP(7, qk_i);
-          qk_c = -1;
-          ++qk_i;
-        }
-        progressed = true;
-      }
-#else
-      if (qk_c < 0 && qk_i < ntiles && done(&ctl->kfull, qk_i & 1) && done(&ctl->kpeer, qk_i & 1) &&
-          (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
-                        done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
-        tc_fence_after();
-        TLP(6, qk_i);
-        qk_c = 0;
-      }
-      if (qk_c >= 0) {
-        // all nine chunks at once: issuing them one per loop iteration was measured 2.5 times slower
-        for (; qk_c < kQChunks - 1; ++qk_c) issue_qk_chunk(qk_i, qk_c);
-        issue_qk_chunk(qk_i, qk_c);
-        if (++qk_c == kQChunks) {
-          TLP(7, qk_i);
-          qk_c = -1;
-          ++qk_i;
-        }
-        progressed = true;
-      }
-      if (pv_i < qk_i && done(&ctl->pfull, pv_i & 1) && done(&ctl->ppeer, pv_i & 1) &&
-          done(&ctl->vfull, pv_i & 1) && done(&ctl->vpeer, pv_i & 1)) {
-        // (No cluster-scope fence here: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700 cycles per
-        // use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive on their
-        // own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA that this
-        // thread issues after seeing the notice reads CTA 1's shared memory from CTA 1's side.)
+      } else if (pv_h == 0 && pv_i < qk_i && done(&ctl->pfull, pph) && done(&ctl->ppeer, pph) &&
+                 done(&ctl->vfull[0], pph) && done(&ctl->vpeer[0], pph)) {
         tc_fence_after();
         TLP(8, pv_i);
-        issue_pv(pv_i);
-        TLP(9, pv_i);
-        ++pv_i;
+        issue_pv_half(pv_i, 0);
+        tc2_commit(smem_u32(&ctl->vfree[0]));
+        pv_h = 1;
+        progressed = true;
+      } else if (qk_i < ntiles && qk_h == 0 && done(&ctl->kfull[0], qph) && done(&ctl->kpeer[0], qph) &&
+                 (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
+                               done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
+        tc_fence_after();
+        TLP(6, qk_i);
+        issue_qk_chunks(qk_i, 0, 4);
+        tc2_commit(smem_u32(&ctl->kfree[0]));
+        qk_h = 1;
         progressed = true;
       }
-#endif
       if (progressed) {
         t_last = clock64();
       } else {
@@ -333,34 +328,35 @@ __device__ __forceinline__ void pair_role_mma(const SfaParams& p, const PairCtx 
 }
 
 // ================================ forwarding (CTA 1) ============================================
-// One thread: whenever one of this CTA's four per-tile events completes, tell CTA 0.
-__device__ __forceinline__ void pair_role_relay(const SfaParams& p, const PairCtx c) {
+// One thread: whenever one of this CTA's per-tile events completes, tell CTA 0.
+__device__ __forceinline__ void pair_role_relay(const SfaParams& p, PairCtx c) {
   PairCtl* ctl = c.ctl;
   const int ntiles = c.ntiles;
+  pair_setup_sync(ctl);
   if ((threadIdx.x & 31) == 0) {
-    int k_i = 0, v_i = 0, p_i = 0, s_i = 0;  // s_i: scores of tile s_i read (only tiles that have a successor two on)
+    int k_i[2] = {0, 0}, v_i[2] = {0, 0}, p_i = 0, s_i = 0;  // s_i: scores of tile s_i read (only tiles that have a successor two on)
     const int s_n = ntiles > 2 ? ntiles - 2 : 0;
     long long t_last = clock64();
     bool ok = true;
-    while (k_i < ntiles || v_i < ntiles || p_i < ntiles || s_i < s_n) {
+    while (k_i[0] < ntiles || k_i[1] < ntiles || v_i[0] < ntiles || v_i[1] < ntiles || p_i < ntiles || s_i < s_n) {
       bool progressed = false;
       if (p_i < ntiles && mbar_test_wait(smem_u32(&ctl->pfull), p_i & 1)) {
         pair_signal(smem_u32(&ctl->ppeer));
-        TLP(15, p_i);
         ++p_i;
         progressed = true;
       }
-      if (k_i < ntiles && mbar_test_wait(smem_u32(&ctl->kfull), k_i & 1)) {
-        pair_signal(smem_u32(&ctl->kpeer));
-        TLP(2, k_i);
-        ++k_i;
-        progressed = true;
-      }
-      if (v_i < ntiles && mbar_test_wait(smem_u32(&ctl->vfull), v_i & 1)) {
-        pair_signal(smem_u32(&ctl->vpeer));
-        TLP(3, v_i);
-        ++v_i;
-        progressed = true;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (k_i[h] < ntiles && mbar_test_wait(smem_u32(&ctl->kfull[h]), k_i[h] & 1)) {
+          pair_signal(smem_u32(&ctl->kpeer[h]));
+          ++k_i[h];
+          progressed = true;
+        }
+        if (v_i[h] < ntiles && mbar_test_wait(smem_u32(&ctl->vfull[h]), v_i[h] & 1)) {
+          pair_signal(smem_u32(&ctl->vpeer[h]));
+          ++v_i[h];
+          progressed = true;
+        }
       }
       if (s_i < s_n && mbar_test_wait(smem_u32(&ctl->sread[s_i & 1]), (s_i >> 1) & 1)) {
         pair_signal(smem_u32(&ctl->speer[s_i & 1]));
@@ -387,9 +383,9 @@ __device__ __forceinline__ void pair_role_relay(const SfaParams& p, const PairCt
 
 // ================================ softmax =======================================================
 // Thread (TMEM lane L, column half ch): head L % 64, keys 64 (L / 64) + 32 ch .. +31 of the 128-key tile.
-__device__ __forceinline__ void pair_role_softmax(const SfaParams& p, const PairCtx c) {
+__device__ __forceinline__ void pair_role_softmax(const SfaParams& p, PairCtx c) {
   PairCtl* ctl = c.ctl;
-  const uint32_t tmem_base = c.tmem_base;
+  const uint32_t tmem_base = pair_setup_sync(ctl);
   const int ntiles = c.ntiles;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = warp & 3;                            // TMEM lane quarter this warp may access
@@ -559,16 +555,19 @@ __device__ __forceinline__ void pair_role_softmax(const SfaParams& p, const Pair
 }
 
 // ================================ K producers ===================================================
-// 256 threads; warp w owns rows 8w .. 8w+7 of this CTA's 64. A gather instruction reads ONE row with the whole
-// warp (lane l takes the 16 latent bytes l of the row's 512: four full 128-byte lines per instruction), so a
-// thread holds unit l of eight rows. (Four threads per row, each reading its own 16 bytes of eight different
-// lines, cost eight lines per instruction; with the V producers' gathers on top, the load/store unit's queue
-// then delayed the tensor core's operand reads: q.K^T took 5-6 k cycles instead of 2.5 k.)
-// Unit l (16 int8 -> 16 bf16 = two 16-byte stores) goes to chunk l / 4, store units 2 (l % 4) and 2 (l % 4) + 1 of
+// 256 threads; warp w owns rows 8w .. 8w+7 of this CTA's 64. A gather instruction reads half a row's latent bytes
+// (256 = two whole 128-byte lines) of TWO rows: lane l takes unit l % 16 of row 2m + l / 16, once for the first
+// half of the row (chunks 0-3) and once for the second (chunks 4-7), so a thread holds unit l % 16 and unit
+// 16 + l % 16 of four rows. (Four threads per row, each reading its own 16 bytes of eight different lines, cost
+// eight lines per instruction; with the V producers' gathers on top, the load/store unit's queue then delayed
+// the tensor core's operand reads: q.K^T took 5-6 k cycles instead of 2.5 k.)
+// Unit u (16 int8 -> 16 bf16 = two 16-byte stores) goes to chunk u / 4, store units 2 (u % 4) and 2 (u % 4) + 1 of
 // the row's 128 bytes; the lanes of an odd chunk store the second half first, so that the eight lanes of a
-// quarter-warp (two chunks, same row) hit eight different bank groups. Lane r % 8 also walks the look-ahead
-// chain of row 8w + r % 8: the selected index four tiles ahead, its block-table entry three tiles ahead, an L2
-// prefetch of the row two tiles ahead, the row itself (by all lanes) one tile ahead.
+// quarter-warp (two chunks, same row) hit eight different bank groups. The first-half units are stored when the
+// q.K^T of the previous tile has read chunks 0-3, the second-half units and the rope when it has read the rest.
+// Lane r % 8 also walks the look-ahead chain of row 8w + r % 8: the selected index four tiles ahead, its
+// block-table entry three tiles ahead, an L2 prefetch of the row two tiles ahead, the row itself (by all lanes)
+// one tile ahead.
 template <bool kPacked>
 __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const PairCtx c) {
   PairCtl* ctl = c.ctl;
@@ -576,6 +575,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   const int lane = threadIdx.x & 31;
   const int ptid = threadIdx.x - kPairKWarp0 * 32;
   const int w = ptid >> 5;
+  const int u = lane & 15, s2 = lane >> 4;
   const int my_row = 64 * static_cast<int>(c.crank) + 8 * w + (lane & 7);  // key of the tile this lane looks ahead for
   const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
   const int n_mine = c.end - (c.begin + my_row);  // entry j * 128 of idx_ptr is valid iff j * 128 < n_mine
@@ -586,18 +586,23 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
 #define PAIR_ROPE (kPacked ? PAIR_KN + 512 : reinterpret_cast<const uint8_t*>(p.kr))
 #define PAIR_SCL (kPacked ? PAIR_KN + 640 : reinterpret_cast<const uint8_t*>(p.kn_scales))
   struct RowRegs {
-    uint4 d[8];  // unit `lane` of rows 8w + 0..7
-    uint4 r[2];  // rope unit lane % 8 of rows 8w + 4i + lane / 8
-    float sc;    // scale lane % 4 of row 8w + lane / 4
+    uint4 d[2][4];  // [row half][m]: unit 16 half + u of row 8w + 2m + s2
+    uint4 r[2];     // rope unit lane % 8 of rows 8w + 4i + lane / 8
+    float sc;       // scale lane % 4 of row 8w + lane / 4
   };
   auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
   // `phys`: this lane's look-ahead row of the tile (-1: padding or rejected -> zeros with scale 0)
   auto issue_loads = [&](RowRegs& r, int phys) {
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {
-      const int pm = __shfl_sync(0xffffffffu, phys, m);
-      r.d[m] = make_uint4(0, 0, 0, 0);
-      if (pm >= 0) r.d[m] = ldg_pinned_v4(PAIR_KN + static_cast<int64_t>(pm) * stride_n + lane * 16);
+    for (int m = 0; m < 4; ++m) {
+      const int pm = __shfl_sync(0xffffffffu, phys, 2 * m + s2);
+      r.d[0][m] = make_uint4(0, 0, 0, 0);
+      r.d[1][m] = make_uint4(0, 0, 0, 0);
+      if (pm >= 0) {
+        const uint8_t* a = PAIR_KN + static_cast<int64_t>(pm) * stride_n + u * 16;
+        r.d[0][m] = ldg_pinned_v4(a);
+        r.d[1][m] = ldg_pinned_v4(a + 256);
+      }
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -621,9 +626,8 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
       else if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(PAIR_SCL + static_cast<int64_t>(phys) * 16));
     }
   };
-  const uint32_t k_rows = c.base + kSmemK + 8 * w * 128;  // row 8w of chunk 0
-  const int chunk_off = (lane >> 2) * kChunk;
-  const bool odd = ((lane >> 2) & 1) != 0;
+  const uint32_t k_rows = c.base + kSmemK + (u >> 2) * kChunk + 8 * w * 128;  // row 8w of this lane's chunk of half 0
+  const bool odd = ((u >> 2) & 1) != 0;
   bool ok = true;
   uint32_t nwait = 0;
   RowRegs ra;
@@ -642,30 +646,39 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
     row_n = pair_row(p, idx1, e1);
     prefetch_row(row_n);
   }
-  for (int j = 0; j < ntiles; ++j) {
-    if (j > 0) {  // the q.K^T of the previous tile has read the chunks
-      ok = pair_group_wait<32, 2, 256, 1>(ctl, nwait, smem_u32(&ctl->sfull[(j - 1) & 1]), ((j - 1) >> 1) & 1, ptid < 32);
-      if (!ok) break;
-    }
-    if (ptid == 0) TLP(0, j);
+  pair_setup_sync(ctl);
+  for (int j = 0; j < ntiles && ok; ++j) {
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {  // row 8w + m (its swizzle term is m)
-      const float scale = __shfl_sync(0xffffffffu, ra.sc, 4 * m + (lane >> 3));
-      const uint32_t row_addr = k_rows + chunk_off + m * 128;
-      const uint32_t a = ((2 * (lane & 3)) ^ m) << 4, b = ((2 * (lane & 3) + 1) ^ m) << 4;
-      // first half of the unit (bytes 0-7) belongs at `a`, second half at `b`; odd chunks store the second first
-      sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? ra.d[m].z : ra.d[m].x, odd ? ra.d[m].w : ra.d[m].y, scale));
-      sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? ra.d[m].x : ra.d[m].z, odd ? ra.d[m].y : ra.d[m].w, scale));
-    }
+    for (int half = 0; half < 2; ++half) {
+      if (j > 0) {  // the q.K^T MMAs of the previous tile that read this half of the chunks are complete
+        ok = pair_group_wait<32, 2, 256, 1>(ctl, nwait, smem_u32(&ctl->kfree[half]), (j - 1) & 1, ptid < 32);
+        if (!ok) break;
+      }
+      if (ptid == 0 && half == 0) TLP(0, j);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {  // rope of row 8w + 4i + lane / 8
-      const int r8 = 4 * i + (lane >> 3);
-      sts_v4u(k_rows + 8 * kChunk + r8 * 128 + (((lane & 7) ^ r8) << 4), ra.r[i]);
+      for (int m = 0; m < 4; ++m) {  // row 8w + 2m + s2 (its swizzle term is 2m + s2); scale 2 half + u / 8 of that row
+        const int x = 2 * m + s2;
+        const float scale = __shfl_sync(0xffffffffu, ra.sc, 4 * x + 2 * half + (u >> 3));
+        const uint32_t row_addr = k_rows + half * 4 * kChunk + x * 128;
+        const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
+        const uint4 v = ra.d[half][m];
+        // first half of the unit (bytes 0-7) belongs at `a`, second half at `b`; odd chunks store the second first
+        sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
+        sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+      }
+      if (half == 1) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // rope of row 8w + 4i + lane / 8
+          const int r8 = 4 * i + (lane >> 3);
+          sts_v4u(c.base + kSmemK + 8 * kChunk + (8 * w + r8) * 128 + (((lane & 7) ^ r8) << 4), ra.r[i]);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->kfull[half]));
+      if (ptid == 0 && half == 1) TLP(1, j);
     }
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->kfull));
-    if (ptid == 0) TLP(1, j);
+    if (!ok) break;
     if (j + 1 < ntiles) issue_loads(ra, row_n);  // rows of tile j+1 (in L2: prefetched a tile ago)
     row_n = pair_row(p, idx_a, entry_a);         // tile j+2: into L2
     prefetch_row(row_n);
@@ -680,12 +693,13 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
 }
 
 // ================================ V producers ===================================================
-// 256 threads; warp w owns rows 16w .. 16w+15 of the tile's 128. A gather instruction reads this CTA's half of
-// the value columns (256 of the 512 latent bytes) of TWO rows: lane l takes unit l % 16 of row 2m + l / 16, again
-// whole 128-byte lines (the other CTA's K producers have fetched or are fetching the same lines: L2 hits). Unit u
-// goes to V chunk u / 4 of the row's key half, store units 2 (u % 4) and 2 (u % 4) + 1, second half first in odd
-// chunks as in the K producers. Lane r % 16 walks the look-ahead chain of row 16w + r % 16 (no L2 prefetch: the
-// row's owner issues it).
+// 256 threads; warp w owns rows 8w .. 8w+7 of EACH key half of the tile (keys 64 h + 8w ..). A gather instruction
+// reads this CTA's half of the value columns (256 of the 512 latent bytes) of TWO rows: lane l takes unit l % 16
+// of row 2m + l / 16, again whole 128-byte lines (the other CTA's K producers have fetched or are fetching the
+// same lines: L2 hits). Unit u goes to V chunk u / 4 of the row's key half, store units 2 (u % 4) and 2 (u % 4) + 1,
+// second half first in odd chunks as in the K producers. Key half 0 is stored when the P.V of the previous tile
+// has read keys 0-63, key half 1 when it has read the rest. Lane r % 16 walks the look-ahead chain of row
+// 64 (r / 8) + 8w + r % 8 (no L2 prefetch: the row's owner issues it).
 template <bool kPacked>
 __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const PairCtx c) {
   PairCtl* ctl = c.ctl;
@@ -694,29 +708,32 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
   const int vtid = threadIdx.x - kPairVWarp0 * 32;
   const int w = vtid >> 5;
   const int u = lane & 15, s2 = lane >> 4;
-  const int my_row = 16 * w + u;  // key of the tile this lane looks ahead for
+  const int my_row = 64 * ((lane >> 3) & 1) + 8 * w + (lane & 7);  // key of the tile this lane looks ahead for
   const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
   const int n_mine = c.end - (c.begin + my_row);
   const int col0 = 256 * static_cast<int>(c.crank);  // first latent byte of this CTA's value columns
   constexpr int stride_n = kPacked ? 656 : 512, stride_s = kPacked ? 656 : 16;
   struct RowRegs {
-    uint4 d[8];  // unit u of rows 16w + 2m + s2
-    float sc;    // scale lane % 2 (of this CTA's two) of row 16w + lane / 2
+    uint4 d[2][4];  // [key half][m]: unit u of row 64 half + 8w + 2m + s2
+    float sc;       // scale lane % 2 (of this CTA's two) of the row lane / 2 (chain order: half * 8 + r)
   };
   auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
   auto issue_loads = [&](RowRegs& r, int phys) {
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {
-      const int pm = __shfl_sync(0xffffffffu, phys, 2 * m + s2);
-      r.d[m] = make_uint4(0, 0, 0, 0);
-      if (pm >= 0) r.d[m] = ldg_pinned_v4(PAIR_KN + static_cast<int64_t>(pm) * stride_n + col0 + u * 16);
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int pm = __shfl_sync(0xffffffffu, phys, 8 * half + 2 * m + s2);
+        r.d[half][m] = make_uint4(0, 0, 0, 0);
+        if (pm >= 0) r.d[half][m] = ldg_pinned_v4(PAIR_KN + static_cast<int64_t>(pm) * stride_n + col0 + u * 16);
+      }
     }
     const int ps = __shfl_sync(0xffffffffu, phys, lane >> 1);
     r.sc = 0.f;
     if (ps >= 0) asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(r.sc) : "l"(PAIR_SCL + static_cast<int64_t>(ps) * stride_s + (col0 >> 5) + (lane & 1) * 4));
   };
-  // rows 16w .. 16w+15 lie in key half w / 4; row (16w + x) % 64 of chunk u / 4
-  const uint32_t v_rows = c.base + kSmemV + (w >> 2) * kVHalfBytes + (u >> 2) * kChunk + ((16 * w) & 63) * 128;
+  // row 8w of chunk u / 4 in the V region of key half 0
+  const uint32_t v_rows = c.base + kSmemV + (u >> 2) * kChunk + 8 * w * 128;
   const bool odd = ((u >> 2) & 1) != 0;
   bool ok = true;
   uint32_t nwait = 0;
@@ -732,25 +749,31 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
     issue_loads(ra, pair_row(p, idx0, e0));
     row_n = pair_row(p, idx1, e1);
   }
-  for (int j = 0; j < ntiles; ++j) {
-    if (j > 0) {  // the P.V of the previous tile has read the V regions
-      ok = pair_group_wait<32, 3, 256, 2>(ctl, nwait, smem_u32(&ctl->pvdone), (j - 1) & 1, vtid < 32);
-      if (!ok) break;
-    }
-    if (vtid == 0) TLP(4, j);
+  pair_setup_sync(ctl);
+  for (int j = 0; j < ntiles && ok; ++j) {
 #pragma unroll
-    for (int m = 0; m < 8; ++m) {  // row 16w + 2m + s2: swizzle term (2m + s2) % 8, scale held by lane 2 (2m + s2) + u / 8
-      const float scale = __shfl_sync(0xffffffffu, ra.sc, 2 * (2 * m + s2) + (u >> 3));
-      const int x = (2 * m + s2) & 7;
-      const uint32_t row_addr = v_rows + (2 * m + s2) * 128;
-      const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
-      sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? ra.d[m].z : ra.d[m].x, odd ? ra.d[m].w : ra.d[m].y, scale));
-      sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? ra.d[m].x : ra.d[m].z, odd ? ra.d[m].y : ra.d[m].w, scale));
+    for (int half = 0; half < 2; ++half) {
+      if (j > 0) {  // the P.V MMAs of the previous tile that read this key half are complete
+        ok = pair_group_wait<32, 3, 256, 2>(ctl, nwait, smem_u32(&ctl->vfree[half]), (j - 1) & 1, vtid < 32);
+        if (!ok) break;
+      }
+      if (vtid == 0 && half == 0) TLP(4, j);
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {  // row 64 half + 8w + 2m + s2: swizzle term 2m + s2, scale held by lane 2 (8 half + 2m + s2) + u / 8
+        const int x = 2 * m + s2;
+        const float scale = __shfl_sync(0xffffffffu, ra.sc, 2 * (8 * half + x) + (u >> 3));
+        const uint32_t row_addr = v_rows + half * kVHalfBytes + x * 128;
+        const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
+        const uint4 v = ra.d[half][m];
+        sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
+        sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->vfull[half]));
+      if (vtid == 0 && half == 1) TLP(5, j);
     }
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->vfull));
-    if (vtid == 0) TLP(5, j);
+    if (!ok) break;
     if (j + 1 < ntiles) issue_loads(ra, row_n);
     row_n = pair_row(p, idx_a, entry_a);
     idx_a = load_idx(j + 3);
@@ -814,18 +837,20 @@ sfa_pair_kernel(const __grid_constant__ SfaParams p) {
 
   // ---- setup ------------------------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(smem_u32(&ctl->kfull), kPairKWarps);
-    mbar_init(smem_u32(&ctl->vfull), kPairVWarps);
     mbar_init(smem_u32(&ctl->pvdone), 1);
     mbar_init(smem_u32(&ctl->pfull), kPairSoftmaxWarps);
+    mbar_init(smem_u32(&ctl->ppeer), 1);
     for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->kfull[b]), kPairKWarps);
+      mbar_init(smem_u32(&ctl->vfull[b]), kPairVWarps);
+      mbar_init(smem_u32(&ctl->kfree[b]), 1);
+      mbar_init(smem_u32(&ctl->vfree[b]), 1);
       mbar_init(smem_u32(&ctl->sfull[b]), 1);
       mbar_init(smem_u32(&ctl->sread[b]), kPairSoftmaxWarps);
+      mbar_init(smem_u32(&ctl->kpeer[b]), 1);
+      mbar_init(smem_u32(&ctl->vpeer[b]), 1);
       mbar_init(smem_u32(&ctl->speer[b]), 1);
     }
-    mbar_init(smem_u32(&ctl->kpeer), 1);
-    mbar_init(smem_u32(&ctl->vpeer), 1);
-    mbar_init(smem_u32(&ctl->ppeer), 1);
     ctl->abort = 0;
     fence_mbar_init();
   }
@@ -836,45 +861,35 @@ sfa_pair_kernel(const __grid_constant__ SfaParams p) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   // this CTA's 64 query rows into shared memory, nine swizzled chunks of 64 dims (A operand of q.K^T): 64 x 72
-  // 16-byte units, six per thread, all loads in flight before the first store
-  {
+  // 16-byte units, twelve per thread of the twelve warps that are not producers, all loads in flight before the
+  // first store. The producers go straight to their first rows.
+  if (warp < kPairKWarp0) {
+    constexpr int kLoaders = 32 * kPairKWarp0;
     const int64_t row0 = c.q_row0 + 64 * crank;
-    uint4 w[6];
+    uint4 w[12];
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-      const int e = tid + i * kPairThreads;
-      if (e < 64 * 72) {
-        const int r = e / 72, u = e % 72;
-        w[i] = (u < 64) ? __ldg(reinterpret_cast<const uint4*>(p.q_nope + (row0 + r) * 512) + u)
-                        : __ldg(reinterpret_cast<const uint4*>(p.q_rope + (row0 + r) * 64) + (u - 64));
-      }
+    for (int i = 0; i < 12; ++i) {
+      const int e = tid + i * kLoaders;
+      const int r = e / 72, u = e % 72;
+      w[i] = (u < 64) ? __ldg(reinterpret_cast<const uint4*>(p.q_nope + (row0 + r) * 512) + u)
+                      : __ldg(reinterpret_cast<const uint4*>(p.q_rope + (row0 + r) * 64) + (u - 64));
     }
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-      const int e = tid + i * kPairThreads;
-      if (e < 64 * 72) {
-        const int r = e / 72, u = e % 72;
-        sts_v4u(base + kSmemQ + (u >> 3) * kChunk + r * 128 + (((u & 7) ^ (r & 7)) << 4), w[i]);
-      }
+    for (int i = 0; i < 12; ++i) {
+      const int e = tid + i * kLoaders;
+      const int r = e / 72, u = e % 72;
+      sts_v4u(base + kSmemQ + (u >> 3) * kChunk + r * 128 + (((u & 7) ^ (r & 7)) << 4), w[i]);
     }
     fence_proxy_async();
   }
-  tc_fence_before();
-  __syncthreads();
-  pair_cluster_sync();  // both CTAs' barriers are initialised and both Q halves are in place
-  tc_fence_after();
-  c.tmem_base = ctl->tmem_base;
-  if (threadIdx.x == 0) TLP(1, 20);  // roles start
+  static_assert(12 * 32 * kPairKWarp0 == 64 * 72, "Q units per loader thread");
 
-#ifdef PAIR_EXP_NOREG
-#define PAIR_SETREG(x)
-#else
 #define PAIR_SETREG(x) asm volatile(x)
-#endif
   if (warp < kPairSoftmaxWarp0) {
     PAIR_SETREG("setmaxnreg.dec.sync.aligned.u32 24;");
     if (warp == 0 && crank == 0) pair_role_mma(p, c);
-    if (warp == 1 && crank == 1) pair_role_relay(p, c);
+    else if (warp == 1 && crank == 1) pair_role_relay(p, c);
+    else pair_setup_sync(ctl);
   } else if (warp < kPairKWarp0) {
     PAIR_SETREG("setmaxnreg.inc.sync.aligned.u32 104;");
     pair_role_softmax(p, c);
