@@ -836,7 +836,7 @@ def main():
                    # 65536 (profiles/); the extra is the 4 B/key score write, which scales with the keys
                    "traffic": int(by_score * per_gpu * 143.93 / 138.58), "peak_source": peak_src,
                    "algorithmic_bytes_per_launch": int(by_score * per_gpu), "ms_per_launch": li_ms}
-        sfa_kernel = "sfa_cluster_kernel" if nq == 128 else "sfa_mma_kernel"
+        sfa_kernel = "sfa_pair_kernel" if nq == 128 else "sfa_mma_kernel"
         tensor_bound = fl_sfa / (tf_peak * 1e12) >= by_sfa / (peak * 1e9)
         roof_sfa = {"bound": "tensor" if tensor_bound else "hbm", "kernel": sfa_kernel,
                     "achieved": sfa_tfs if tensor_bound else sfa_gbs, "peak": tf_peak if tensor_bound else peak,

@@ -113,6 +113,27 @@ int pto_li_scores(const int8_t* idx_query, const void* idx_query_scale, const in
                   int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
                   int max_blocks, int flags, void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
+/* Non-quantised lightning indexer. Replaces `LightningIndexerTopk` / `LightningIndexerTopkImpl` with isQuant = false
+ * (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:113-147, :23-58; golden
+ * `indexer_topk_compute(is_quant=False)`,
+ * framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_lightning_indexer.py:189-279).
+ *
+ *   idx_query      bf16 [t, 64, 128]       idx_key_cache  bf16 [block_num, 128, 1, 128]
+ *   idx_weight     bf16 [t, 64]            no scale tensors
+ *
+ * score[pos] = sum_h fp32(weight_h) * relu(fp32(q_h . k[pos])), top-k as above. `flags`: PTO_LI_UNSORTED only.
+ * `pto_li_scores_bf16` is the score stage alone (the reference's `tmpOut` hook, lightning_indexer.cpp:142-145):
+ * scores f32 [t, max_blocks*block_size], positions >= S_b left untouched. */
+int pto_li_decode_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                       const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res,
+                       int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
+                       int max_blocks, int selected_count, int flags,
+                       void* workspace, size_t workspace_bytes, pto_stream_t stream);
+int pto_li_scores_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                       const int32_t* act_seq_key, const int32_t* block_table, float* scores,
+                       int b, int s1, int n_heads, int head_dim, int block_size, int block_num,
+                       int max_blocks, int flags, void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
 /* Lightning indexer for callers that cannot allocate device memory. No counterpart in the
  * reference: it exists for hosts of this library that run where cudaMalloc is off limits - inside
  * a serving engine whose memory pool owns all of HBM, or in a process that must not touch the
@@ -271,6 +292,19 @@ int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const
                      int b, int s1, int block_num, int max_blocks, int selected_count, int nq,
                      float softmax_scale, int flags,
                      void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
+/* The non-quantised chain: bf16 indexer -> top-k -> sparse attention over the bf16 latent cache, the part of
+ * `DecodeIndexerAttention` behind its two prologs
+ * (framework/src/operator/models/deepseek_v3.2_exp/decode_indexer_attention.cpp:108-129:
+ * LightningIndexerTopk -> GatherAfterPrologCompute -> SparseFlashAttentionCompute). key_nope_2d is
+ * bf16 [block_num*128, 512]; nq must be 128. Workspace: pto_decode_workspace_bytes. */
+int pto_decode_fused_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                          const void* query_nope, const void* query_rope, const void* key_nope_2d,
+                          const void* key_rope_2d, const int32_t* act_seq, const int32_t* block_table,
+                          int32_t* topk_res, void* attention_out,
+                          int b, int s1, int block_num, int max_blocks, int selected_count, int nq,
+                          float softmax_scale, int flags,
+                          void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
 #ifdef __cplusplus
 }

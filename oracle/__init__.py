@@ -8,7 +8,8 @@ Parity is pinned: the restatement is checked (tests/test_oracle_golden.py) again
 reference's own golden functions, produced by importing the reference's example drivers with
 tests/golden/make_golden.py and committed under tests/golden/.
 """
-from .li_oracle import li_scores, li_scores_fp16_chain, li_topk, lightning_indexer  # noqa: F401
+from .li_oracle import (li_scores, li_scores_fp16_chain, li_scores_nonquant, li_topk, lightning_indexer,  # noqa: F401
+                        lightning_indexer_nonquant)
 from .sfa_oracle import (dequantised_cache, sparse_attention, sparse_attention_online,  # noqa: F401
                          sparse_attention_packed)
 from .compare import attention_errors, topk_set_diff  # noqa: F401

@@ -94,6 +94,39 @@ def li_scores_fp16_chain(idx_query, idx_query_scale, idx_key_cache, idx_key_scal
     return rows_out
 
 
+def li_scores_nonquant(idx_query, idx_key_cache, idx_weight, act_seq, block_table, s1):
+    """The non-quantised formulation, `LightningIndexerTopkImpl` with isQuant = false
+    (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:113-147; golden
+    `indexer_topk_compute(is_quant=False)`, framework/tests/st/operator/src/test_deepseek_v3.2_exp/
+    gen_lightning_indexer.py:258-266):
+
+      mm    = fp32(q) @ fp32(k)^T            bf16 inputs, fp32 product        (:258)
+      score = sum_h relu(mm_h) * fp32(w_h)   fp32                             (:260-263)
+
+    Same return value as `li_scores`."""
+    t, n_heads, dim = idx_query.shape
+    block_num, block_size = idx_key_cache.shape[0], idx_key_cache.shape[1]
+    keys2d = idx_key_cache.reshape(block_num * block_size, dim)
+    b = len(act_seq)
+    rows_out = []
+    for bi in range(b):
+        seq = int(act_seq[bi])
+        k, _ = _gather_pages(keys2d, block_table[bi], seq, block_size)
+        kf = k.to(torch.float32)
+        for i in range(s1):
+            ti = bi * s1 + i
+            mm = idx_query[ti].to(torch.float32) @ kf.T  # [64, S]
+            w = idx_weight[ti].to(torch.float32).reshape(-1, 1)
+            rows_out.append((torch.relu(mm) * w).sum(dim=0))
+    return rows_out
+
+
+def lightning_indexer_nonquant(idx_query, idx_key_cache, idx_weight, act_seq, block_table, s1, selected_count=2048):
+    rows = li_scores_nonquant(idx_query, idx_key_cache, idx_weight, act_seq, block_table, s1)
+    idx, vals = li_topk(rows, act_seq, s1, selected_count)
+    return idx, vals, rows
+
+
 def li_topk(score_rows, act_seq, s1, selected_count=2048):
     """Exact top-k per row over the causal prefix; value-descending; -1 padding."""
     t = len(score_rows)

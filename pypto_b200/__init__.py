@@ -6,6 +6,7 @@ from .compat import LightningIndexerConfigs, SaTileShapeConfig, Tensor, from_tor
 
 _OPS = (
     "lightning_indexer_decode", "lightning_indexer_scores", "lightning_indexer_topk",
+    "lightning_indexer_topk_nonquant", "decode_indexer_attention",
     "sparse_flash_attention_quant_d", "sparse_flash_attention_quant_p",
     "sparse_attention_antiquant_d", "sparse_attention_antiquant_p",
     "mla_indexer_prolog_quant_d", "mla_indexer_prolog_quant_p", "pack_kv_cache",

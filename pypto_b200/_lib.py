@@ -31,6 +31,8 @@ SIGNATURES = {
     "pto_li_decode_static": (_i, [_vp] * 5 + [_i] + [_vp] * 3 + [_i] * 9 + [_vp, _vp]),
     "pto_li_static_status": (_i, [_vp, _vp]),
     "pto_li_scores": (_i, [_vp] * 5 + [_i] + [_vp] * 4 + [_i] * 8 + [_vp, _sz, _vp]),
+    "pto_li_decode_bf16": (_i, [_vp] * 6 + [_i] * 9 + [_vp, _sz, _vp]),
+    "pto_li_scores_bf16": (_i, [_vp] * 6 + [_i] * 8 + [_vp, _sz, _vp]),
     "pto_li_topk": (_i, [_vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pto_sfa_workspace_bytes": (_sz, [_i, _i]),
     "pto_sfa_quant": (_i, [_vp] * 9 + [_i, _i, _i, _i, _f, _i, _i, _i64, _i, _i, _i, _vp, _sz, _vp]),
@@ -42,6 +44,7 @@ SIGNATURES = {
     "pto_mla_indexer_prolog_quant": (_i, [_vp] * 31 + [_i, _i, _i, _i64, _f, _f, _f, _vp, _sz, _vp]),
     "pto_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pto_decode_fused": (_i, [_vp] * 5 + [_i] + [_vp] * 9 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]),
+    "pto_decode_fused_bf16": (_i, [_vp] * 11 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]),
 }
 
 _lib = None

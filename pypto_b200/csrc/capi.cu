@@ -17,6 +17,7 @@ namespace pto {
 static std::atomic<long long> g_launch_count{0};
 void count_launch(int n) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
 int li_max_s1();
+int li_max_s1_bf16();
 int li_max_sequences();
 int topk_max_k();
 }  // namespace pto
@@ -167,6 +168,18 @@ int check_li_common(const void* q, const void* qs, const void* kc, const void* k
   return PTO_OK;
 }
 
+// Internal flag (never part of the ABI's `flags`): the non-quantised formulation, bf16 q / k_cache / weight.
+constexpr int kLiFlagBf16 = 0x1000;
+
+int check_li_bf16(const void* q, const void* kc, const void* w, const void* act, const void* bt, int b, int s1,
+                  int n_heads, int head_dim, int block_size, int block_num, int max_blocks, int flags) {
+  PTO_REQUIRE((flags & (PTO_LI_SCORE_SIMT | PTO_LI_FP16_CHAIN)) == 0,
+              "flags 0x%x: the non-quantised indexer has one formulation and runs on the tensor cores only", flags);
+  // the shape checks of the quantised entry, with the key cache standing in for the absent scale tensors
+  return check_li_common(q, kc, kc, kc, w, PTO_DT_F16, act, bt, b, s1, n_heads, head_dim, block_size, block_num,
+                         max_blocks);
+}
+
 // Score stage for tokens-per-sequence s1 (any s1 >= 1: groups of up to 4 tokens per launch).
 int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void* ks, const void* w, int scale_dtype,
                   const int32_t* act, const int32_t* bt, float* scores, void* first_mm, int b, int s1, int block_num,
@@ -190,15 +203,19 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
   const bool simt = (flags & PTO_LI_SCORE_SIMT) != 0;
   PTO_REQUIRE(simt || first_mm == nullptr, "first_mm is only produced with PTO_LI_SCORE_SIMT");
   p.fp16_chain = (flags & PTO_LI_FP16_CHAIN) != 0 ? 1 : 0;
+  p.bf16 = (flags & kLiFlagBf16) != 0 ? 1 : 0;
   PTO_REQUIRE(!p.fp16_chain || scale_dtype == PTO_DT_F16, "PTO_LI_FP16_CHAIN needs fp16 scales and weights");
   PTO_REQUIRE(!p.fp16_chain || first_mm == nullptr, "first_mm is not produced with PTO_LI_FP16_CHAIN");
   DeviceInfo di;
   CUtensorMap tmap_k, tmap_q;
-  const int group = s1 < pto::li_max_s1() ? s1 : pto::li_max_s1();
+  const int max_group = p.bf16 ? pto::li_max_s1_bf16() : pto::li_max_s1();
+  const int group = s1 < max_group ? s1 : max_group;
   if (!simt) {
     int rc = get_device_info(&di);
     if (rc != PTO_OK) return rc;
-    rc = make_rows128_map(&tmap_k, kc, static_cast<uint64_t>(block_num) * 128, 128);
+    // bf16 rows are 256 bytes: the map's box is one 128-byte half of 128 rows
+    rc = p.bf16 ? make_bytes_map(&tmap_k, kc, 256, static_cast<uint64_t>(block_num) * 128, 256, 128)
+                : make_rows128_map(&tmap_k, kc, static_cast<uint64_t>(block_num) * 128, 128);
     if (rc != PTO_OK) return rc;
   }
   // more than four query tokens per sequence (prefill chunks): groups of four tokens; the tensor-core kernel
@@ -214,7 +231,8 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
     } else {
       const int full = (s1 - off) / group;
       if (p.s1 == group && full > 1) p.groups = full < 16 ? full : 16;
-      int rc = make_rows128_map(&tmap_q, q, static_cast<uint64_t>(b) * s1 * 64, static_cast<uint32_t>(64 * p.s1));
+      int rc = p.bf16 ? make_bytes_map(&tmap_q, q, 256, static_cast<uint64_t>(b) * s1 * 64, 256, static_cast<uint32_t>(64 * p.s1))
+                      : make_rows128_map(&tmap_q, q, static_cast<uint64_t>(b) * s1 * 64, static_cast<uint32_t>(64 * p.s1));
       if (rc != PTO_OK) return rc;
       PTO_CUDA(pto::launch_li_score_tc(p, &tmap_k, &tmap_q, di.num_sms, stream));
     }
@@ -542,6 +560,41 @@ int pto_li_decode(const int8_t* idx_query, const void* idx_query_scale, const in
                      selected_count, flags, status, stream);
 }
 
+int pto_li_scores_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                       const int32_t* act_seq_key, const int32_t* block_table, float* scores, int b, int s1, int n_heads,
+                       int head_dim, int block_size, int block_num, int max_blocks, int flags, void* workspace,
+                       size_t workspace_bytes, pto_stream_t stream) {
+  int rc = check_li_bf16(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table, b, s1, n_heads, head_dim,
+                         block_size, block_num, max_blocks, flags);
+  if (rc != PTO_OK) return rc;
+  PTO_REQUIRE(scores != nullptr && aligned16(scores), "scores must be a 16-byte aligned device pointer");
+  rc = check_workspace(workspace, workspace_bytes, kStatusBytes);
+  if (rc != PTO_OK) return rc;
+  return run_li_scores(reinterpret_cast<const int8_t*>(idx_query), nullptr, reinterpret_cast<const int8_t*>(idx_key_cache),
+                       nullptr, idx_weight, PTO_DT_F16, act_seq_key, block_table, scores, nullptr, b, s1, block_num,
+                       max_blocks, kLiFlagBf16, reinterpret_cast<int32_t*>(workspace), stream);
+}
+
+int pto_li_decode_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                       const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res, int b, int s1,
+                       int n_heads, int head_dim, int block_size, int block_num, int max_blocks, int selected_count,
+                       int flags, void* workspace, size_t workspace_bytes, pto_stream_t stream) {
+  int rc = check_li_bf16(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table, b, s1, n_heads, head_dim,
+                         block_size, block_num, max_blocks, flags);
+  if (rc != PTO_OK) return rc;
+  PTO_REQUIRE(topk_res != nullptr, "topk_res is null");
+  rc = check_workspace(workspace, workspace_bytes, pto_li_workspace_bytes(b * s1, max_blocks, block_size));
+  if (rc != PTO_OK) return rc;
+  int32_t* status = reinterpret_cast<int32_t*>(workspace);
+  float* scores = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kStatusBytes);
+  rc = run_li_scores(reinterpret_cast<const int8_t*>(idx_query), nullptr, reinterpret_cast<const int8_t*>(idx_key_cache),
+                     nullptr, idx_weight, PTO_DT_F16, act_seq_key, block_table, scores, nullptr, b, s1, block_num,
+                     max_blocks, kLiFlagBf16, status, stream);
+  if (rc != PTO_OK) return rc;
+  return run_li_topk(scores, static_cast<int64_t>(max_blocks) * block_size, act_seq_key, topk_res, b, s1,
+                     selected_count, flags, status, stream);
+}
+
 int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
                          const void* idx_key_scale, const void* idx_weight, int scale_dtype,
                          const int32_t* act_seq_key, const int32_t* block_table, int32_t* topk_res, int b, int s1,
@@ -819,6 +872,35 @@ int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const
   return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, 0, topk_res, block_table, act_seq,
                  attention_out, b, s1, nq, 1, softmax_scale, selected_count, 128, static_cast<int64_t>(block_num) * 128,
                  max_blocks, nq, 0, part, sfa_part_bytes(b * s1, nq), status, stream, /*behind_topk=*/1);
+}
+
+int pto_decode_fused_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
+                          const void* query_nope, const void* query_rope, const void* key_nope_2d,
+                          const void* key_rope_2d, const int32_t* act_seq, const int32_t* block_table,
+                          int32_t* topk_res, void* attention_out, int b, int s1, int block_num, int max_blocks,
+                          int selected_count, int nq, float softmax_scale, int flags, void* workspace,
+                          size_t workspace_bytes, pto_stream_t stream) {
+  int rc = check_li_bf16(idx_query, idx_key_cache, idx_weight, act_seq, block_table, b, s1, 64, 128, 128, block_num,
+                         max_blocks, flags);
+  if (rc != PTO_OK) return rc;
+  PTO_REQUIRE(topk_res != nullptr, "topk_res is null");
+  rc = check_workspace(workspace, workspace_bytes, pto_decode_workspace_bytes(b * s1, max_blocks, 128, nq));
+  if (rc != PTO_OK) return rc;
+  uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(base);
+  float* scores = reinterpret_cast<float*>(base + kStatusBytes);
+  uint8_t* part = base + kStatusBytes + li_scores_bytes(b * s1, max_blocks, 128);
+  rc = run_li_scores(reinterpret_cast<const int8_t*>(idx_query), nullptr, reinterpret_cast<const int8_t*>(idx_key_cache),
+                     nullptr, idx_weight, PTO_DT_F16, act_seq, block_table, scores, nullptr, b, s1, block_num, max_blocks,
+                     kLiFlagBf16, status, stream);
+  if (rc != PTO_OK) return rc;
+  rc = run_li_topk(scores, static_cast<int64_t>(max_blocks) * 128, act_seq, topk_res, b, s1, selected_count, flags,
+                   status, stream);
+  if (rc != PTO_OK) return rc;
+  return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, nullptr, kSfaSplitBf16, topk_res, block_table,
+                 act_seq, attention_out, b, s1, nq, 1, softmax_scale, selected_count, 128,
+                 static_cast<int64_t>(block_num) * 128, max_blocks, nq, 0, part, sfa_part_bytes(b * s1, nq), status, stream,
+                 /*behind_topk=*/1);
 }
 
 }  // extern "C"

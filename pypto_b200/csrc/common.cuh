@@ -281,6 +281,7 @@ struct LiParams {
   int64_t row_stride;
   int b, s1, block_num, max_blocks;
   int fp16_chain;  // PTO_LI_FP16_CHAIN: the older formulation of the score
+  int bf16;        // non-quantised formulation: q, k_cache and weight are bf16, the scales are not read
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
   int groups;      // token groups of s1 tokens taken by one launch (grid y; tensor-core kernel), >= 1

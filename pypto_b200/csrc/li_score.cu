@@ -16,6 +16,14 @@
 // warps 3..18 epilogue (four groups of four warps that take pages round-robin; a single warp is
 // latency-bound on the conversion chain, so thread-level parallelism has to come from many warps).
 // A ring of 8 slots pairs one shared-memory stage with one TMEM accumulator. All waits are bounded.
+//
+// Non-quantised formulation (bf16 queries, keys and weights; reference LightningIndexerTopkImpl with isQuant =
+// false, framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:113-147, golden
+// indexer_topk_compute(is_quant=False), framework/tests/st/operator/src/test_deepseek_v3.2_exp/
+// gen_lightning_indexer.py:189-279):   score[pos] = sum_h fp32(w_h) * relu( fp32( q[h, :] . k[pos, :] ) ).
+// Same kernel and ring, mode kLiBf16: a key page is 32 KB (two 128-byte-swizzled halves of the 128 dims), the
+// product is tcgen05.mma kind::f16 (bf16 x bf16 -> fp32, eight MMAs of K = 16 per page), four ring slots, at
+// most two query tokens of a sequence per launch, and the epilogue is max/fma on the fp32 accumulators.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -37,6 +45,13 @@ constexpr int kLiThreads = 32 * (kLiEpilogueWarp0 + 4 * kLiEpilogueGroups);
 constexpr int kMaxS1 = 4;
 constexpr int kMaxSeqPerLaunch = 2048;
 constexpr int kTmemCols = 512;
+// score formulations the tensor-core kernel is instantiated for
+enum { kLiQuant = 0, kLiChain = 1, kLiBf16 = 2 };
+constexpr int kBf16PageBytes = kPageKeys * 256;  // one stage of the bf16 ring: the page's two 16 KB halves
+constexpr int kBf16Slots = 4;                    // 4 x 32 KB fit where the int8 ring keeps 8 x 17 KB
+constexpr int kBf16MaxS1 = 2;                    // 2 tokens x 64 heads x 256 B of queries fit the int8 Q area
+static_assert(kBf16Slots * kBf16PageBytes <= kLiSlots * kStageBytes, "bf16 ring exceeds the stage area");
+static_assert(kBf16MaxS1 * kHeads * 256 <= kMaxS1 * kQBytesPerToken, "bf16 queries exceed the Q area");
 
 struct LiCtl {
   uint64_t full[kLiSlots];     // TMA bytes of the slot's page landed
@@ -110,7 +125,21 @@ __device__ __forceinline__ float weighted_sum_32(const uint32_t (&v)[32], const 
   return (a0 + a1) + (a2 + a3);
 }
 
-template <bool kChain>
+// Non-quantised formulation, 32 heads of one key: the accumulators are fp32 dots.
+__device__ __forceinline__ float weighted_relu_sum_32(const uint32_t (&v)[32], const float* ws) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const float4 w = *reinterpret_cast<const float4*>(ws + c);
+    a0 = fmaf(w.x, fmaxf(__uint_as_float(v[c]), 0.f), a0);
+    a1 = fmaf(w.y, fmaxf(__uint_as_float(v[c + 1]), 0.f), a1);
+    a2 = fmaf(w.z, fmaxf(__uint_as_float(v[c + 2]), 0.f), a2);
+    a3 = fmaf(w.w, fmaxf(__uint_as_float(v[c + 3]), 0.f), a3);
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
+template <int kMode>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q, LiParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -121,6 +150,9 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const uint32_t q_base = base + kLiSlots * kStageBytes;
   LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken);
 
+  constexpr bool kChain = kMode == kLiChain;
+  constexpr bool kBf16 = kMode == kLiBf16;
+  constexpr uint32_t kStage = kBf16 ? kBf16PageBytes : kStageBytes;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -129,7 +161,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   if (tid == 0) pdl_trigger();
   const int s1 = p.s1;
   const int n_cols = kHeads * s1;                                // accumulator columns per page
-  const uint32_t n_slots = min(kLiSlots, kTmemCols / n_cols);   // 8, 4, 2, 2 for s1 = 1..4
+  const uint32_t n_slots = min(kBf16 ? kBf16Slots : kLiSlots, kTmemCols / n_cols);   // int8: 8, 4, 2, 2 for s1 = 1..4
 
   if (tid == 0) {
     for (int i = 0; i < kLiSlots; ++i) {
@@ -178,8 +210,10 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const int it0 = static_cast<int>(static_cast<long long>(total) * blockIdx.x / gridDim.x);
   const int it1 = static_cast<int>(static_cast<long long>(total) * (blockIdx.x + 1) / gridDim.x);
 
-  const uint32_t idesc = umma_idesc(kCFmtS32, kABFmtS8, kABFmtS8, 0, 0, 128, n_cols);
-  const uint32_t scale_bytes = kPageKeys * (p.scale_dtype == PTO_DT_F16 ? 2u : 4u);
+  const uint32_t idesc = kBf16 ? umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 0, 128, n_cols)
+                               : umma_idesc(kCFmtS32, kABFmtS8, kABFmtS8, 0, 0, 128, n_cols);
+  const uint32_t scale_bytes = kBf16 ? 0u : kPageKeys * (p.scale_dtype == PTO_DT_F16 ? 2u : 4u);
+  const uint32_t q_half_bytes = static_cast<uint32_t>(n_cols) * 128u;  // bf16: one 64-dim half of the query tile
 
   int cur = it0;
   int bi = 0;
@@ -207,12 +241,20 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const bool aborted = ctl->abort != 0;
     if (!aborted) {
       if (warp == 0 && lane == 0) {
-        mbar_arrive_expect_tx(smem_u32(&ctl->qfull), s1 * kQBytesPerToken);
-        tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
+        if (kBf16) {
+          mbar_arrive_expect_tx(smem_u32(&ctl->qfull), 2 * q_half_bytes);
+          tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
+          tma_load_2d(q_base + q_half_bytes, &tmap_q, 128, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
+        } else {
+          mbar_arrive_expect_tx(smem_u32(&ctl->qfull), s1 * kQBytesPerToken);
+          tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
+        }
       }
       const int e = tid - 32 * kLiEpilogueWarp0;
       if (e >= 0 && e < s1 * kHeads) {
-        if (kChain) {
+        if (kBf16) {
+          ctl->ws[e] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weight)[tok0 * kHeads + e]);
+        } else if (kChain) {
           // pairs of heads: even slot = the two query scales, odd slot = the two weights (fp16 bit patterns)
           const __half* src = reinterpret_cast<const __half*>((e & 1) ? p.weight : p.q_scale) + tok0 * kHeads + (e & ~1);
           const __half2 two = __halves2half2(src[0], src[1]);
@@ -250,12 +292,18 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                   scale_page = 0;      // any valid scales: the dots are zero
                 }
                 const uint32_t bar = smem_u32(&ctl->full[slot]);
-                const uint32_t dst = stage_base + slot * kStageBytes;
-                mbar_arrive_expect_tx(bar, kPageBytes + scale_bytes);
-                tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
-                bulk_load_1d(dst + kPageBytes,
-                             reinterpret_cast<const uint8_t*>(p.k_scale) + static_cast<int64_t>(scale_page) * scale_bytes,
-                             scale_bytes, bar);
+                const uint32_t dst = stage_base + slot * kStage;
+                if (kBf16) {
+                  mbar_arrive_expect_tx(bar, kBf16PageBytes);
+                  tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
+                  tma_load_2d(dst + kPageBytes, &tmap_k, 128, phys * kPageKeys, bar);
+                } else {
+                  mbar_arrive_expect_tx(bar, kPageBytes + scale_bytes);
+                  tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
+                  bulk_load_1d(dst + kPageBytes,
+                               reinterpret_cast<const uint8_t*>(p.k_scale) + static_cast<int64_t>(scale_page) * scale_bytes,
+                               scale_bytes, bar);
+                }
               }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -280,10 +328,20 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
               break;
             }
             tc_fence_after();
-            const uint64_t a_desc = a_desc0 + ((slot * kStageBytes) >> 4);
+            const uint64_t a_desc = a_desc0 + ((slot * kStage) >> 4);
             const uint32_t d = tmem_base + slot * n_cols;
+            if (kBf16) {
+              // K = 16 bf16 (32 bytes) per instruction: four steps inside each 64-dim half
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_i8_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+              for (int k = 0; k < 8; ++k) {
+                const uint64_t a = a_desc + ((k >> 2) * (kPageBytes >> 4)) + 2 * (k & 3);
+                const uint64_t bq = b_desc + ((k >> 2) * (q_half_bytes >> 4)) + 2 * (k & 3);
+                mma_f16_ss(d, a, bq, idesc, k > 0 ? 1u : 0u);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mma_i8_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+            }
             tc_commit(smem_u32(&ctl->accfull[slot]));
           }
           if (!ok) ctl->abort = 1;
@@ -311,10 +369,13 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
           tc_fence_after();
           // the page's scales came in with the page; its `full` phase has completed (the MMA issuer
           // waited on it); observing it here orders this thread after the bulk copy
-          mbar_wait(smem_u32(&ctl->full[slot]), ph);
-          const uint8_t* sc_smem = smem + slot * kStageBytes + kPageBytes;
-          const float ks = (p.scale_dtype == PTO_DT_F16) ? __half2float(reinterpret_cast<const __half*>(sc_smem)[row])
-                                                         : reinterpret_cast<const float*>(sc_smem)[row];
+          if (!kBf16) mbar_wait(smem_u32(&ctl->full[slot]), ph);
+          const uint8_t* sc_smem = smem + slot * kStage + kPageBytes;
+          float ks = 1.f;
+          if (!kBf16) {
+            ks = (p.scale_dtype == PTO_DT_F16) ? __half2float(reinterpret_cast<const __half*>(sc_smem)[row])
+                                               : reinterpret_cast<const float*>(sc_smem)[row];
+          }
           const int pos = (page0 + j) * kPageKeys + row;
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * n_cols;
           float res[kMaxS1];
@@ -331,7 +392,9 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[slot]));
               }
-              if (kChain) {
+              if (kBf16) {
+                res[i] = weighted_relu_sum_32(v0, ctl->ws + i * kHeads) + weighted_relu_sum_32(v1, ctl->ws + i * kHeads + 32);
+              } else if (kChain) {
                 const __half2 ks2 = __half2half2(reinterpret_cast<const __half*>(sc_smem)[row]);
                 res[i] = __fadd_rn(chain_sum_32(v0, ctl->ws + i * kHeads, ks2), chain_sum_32(v1, ctl->ws + i * kHeads + 32, ks2));
               } else {
@@ -451,7 +514,8 @@ li_score_simt_kernel(LiParams p) {
 
 cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void* tmap_q, int num_sms,
                                cudaStream_t stream) {
-  auto kernel = p.fp16_chain ? li_score_tc_kernel<true> : li_score_tc_kernel<false>;
+  auto kernel = p.bf16 ? li_score_tc_kernel<kLiBf16>
+                       : (p.fp16_chain ? li_score_tc_kernel<kLiChain> : li_score_tc_kernel<kLiQuant>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kLiSmemBytes));
   if (e != cudaSuccess) return e;
@@ -477,6 +541,7 @@ cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream) {
 }
 
 int li_max_s1() { return kMaxS1; }
+int li_max_s1_bf16() { return kBf16MaxS1; }
 int li_max_sequences() { return kMaxSeqPerLaunch; }
 
 }  // namespace pto

@@ -151,6 +151,33 @@ def make_inputs(
     return d
 
 
+def make_nonquant_inputs(act_seq: Sequence[int], s1: int = 1, seed: int = 4321, device="cpu",
+                         with_attention: bool = True, max_blocks: Optional[int] = None) -> DecodeInputs:
+    """Inputs of the non-quantised formulation: bf16 indexer queries, keys and weights drawn as the reference's
+    ST does (standard normal, gen_lightning_indexer.py:123-133), no scale tensors, and a bf16 latent cache."""
+    device = torch.device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    act_seq = [int(s) for s in act_seq]
+    b = len(act_seq)
+    t = b * s1
+    block_num, max_blocks, table = make_block_table(act_seq, gen, device, max_blocks)
+    d = DecodeInputs(b, s1, act_seq, block_num, max_blocks)
+    d.block_table = table
+    d.act_seq_key = torch.tensor(act_seq, dtype=torch.int32, device=device)
+    n_rows = block_num * BLOCK_SIZE
+    bf = torch.bfloat16
+    d.idx_query = torch.randn((t, IDX_HEADS, IDX_DIM), generator=gen, device=device).to(bf)
+    d.idx_key_cache = torch.randn((block_num, BLOCK_SIZE, 1, IDX_DIM), generator=gen, device=device).to(bf)
+    d.idx_weight = torch.randn((t, IDX_HEADS), generator=gen, device=device).to(bf)
+    if with_attention:
+        d.query_nope = torch.randn((t * ATT_HEADS, KV_LORA), generator=gen, device=device).to(bf)
+        d.query_rope = torch.randn((t * ATT_HEADS, ROPE_DIM), generator=gen, device=device).to(bf)
+        d.key_nope_2d = (torch.randn((n_rows, KV_LORA), generator=gen, device=device) * 0.35).to(bf)
+        d.key_rope_2d = torch.randn((n_rows, ROPE_DIM), generator=gen, device=device).to(bf)
+    return d
+
+
 def pack_kv_rows(key_nope_2d, key_rope_2d, k_nope_scales):
     """One 656-byte int8 row per token: 512 int8 latent | 64 bf16 rope | 4 fp32 scales
     (deepseekv32_sparse_attention_antiquant.py:258-268)."""

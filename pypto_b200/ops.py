@@ -114,12 +114,76 @@ def _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weigh
                                                    max_blocks=bt.shape[1], scale_dtype=sd)
 
 
+def _li_args_bf16(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table):
+    """Argument check of the non-quantised indexer: bf16 queries, keys and weights, no scales."""
+    q = unwrap(idx_query, "idx_query")
+    kc = unwrap(idx_key_cache, "idx_key_cache")
+    w = unwrap(idx_weight, "idx_weight")
+    act = unwrap(act_seq_key, "act_seq_key")
+    bt = unwrap(block_table, "block_table")
+    bf = torch.bfloat16
+    _need(q.dtype == bf and q.numel() % (64 * 128) == 0, "idx_query: bfloat16 [t, 64, 128] (or [b, s1, 64, 128])")
+    t = q.numel() // (64 * 128)
+    _need(kc.dtype == bf and kc.dim() == 4 and tuple(kc.shape[1:]) == (128, 1, 128),
+          "idx_key_cache: bfloat16 [block_num, 128, 1, 128]")
+    _need(w.dtype == bf and w.numel() == t * 64, "idx_weight: bfloat16 [t, 64]")
+    _need(act.dtype == torch.int32 and act.dim() == 1, "act_seq_key: int32 [b]")
+    b = act.shape[0]
+    _need(b >= 1 and t % b == 0, "t must be a multiple of the batch size")
+    _need(bt.dtype == torch.int32 and bt.dim() == 2 and bt.shape[0] == b, "block_table: int32 [b, max_blocks]")
+    return (q, kc, w, act, bt), dict(t=t, b=b, s1=t // b, block_num=kc.shape[0], max_blocks=bt.shape[1])
+
+
+def lightning_indexer_topk_nonquant(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table, topk_res,
+                                    selected_count=2048, tile_config=None, unroll_list=None, *, sort=True,
+                                    scores_out=None):
+    """The non-quantised indexer, `LightningIndexerTopk(query, key, weights, actSeqKey, blockTable, topkRes,
+    selectedCount, tileConfig, unrollList)` (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:
+    198-203, body :23-147 with isQuant = false): score = sum_h w_h * relu(q_h . k) over bf16 tensors in fp32, top-
+    `selected_count` per query token. `scores_out` (float32 [t, max_blocks*128], optional) receives the score rows
+    instead of the top-k running (the reference's `tmpOut` hook)."""
+    (q, kc, w, act, bt), m = _li_args_bf16(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table)
+    lib = _lib.load()
+    common = (m["b"], m["s1"], 64, 128, 128, m["block_num"], m["max_blocks"])
+    if scores_out is not None:
+        sc = unwrap(scores_out, "scores_out")
+        _need(sc.dtype == torch.float32 and sc.numel() == m["t"] * m["max_blocks"] * 128,
+              "scores_out: float32 [t, max_blocks*128]")
+        dev = _same_device([q, kc, w, act, bt, sc])
+        with torch.cuda.device(dev):
+            ws = _workspace(dev, lib.pto_li_workspace_bytes(1, 1, 128))
+            _lib.check(lib.pto_li_scores_bf16(q.data_ptr(), kc.data_ptr(), w.data_ptr(), act.data_ptr(), bt.data_ptr(),
+                                              sc.data_ptr(), *common, 0, ws.data_ptr(), ws.numel(),
+                                              torch.cuda.current_stream(dev).cuda_stream))
+        return None
+    out = unwrap(topk_res, "topk_res")
+    _need(out.dtype == torch.int32 and out.numel() == m["t"] * selected_count,
+          "topk_res: int32 [t, 1, selected_count]")
+    _need(1 <= selected_count <= 2048, "selected_count must be in [1, 2048]")
+    dev = _same_device([q, kc, w, act, bt, out])
+    nbytes = lib.pto_li_workspace_bytes(m["t"], m["max_blocks"], 128)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_li_decode_bf16(q.data_ptr(), kc.data_ptr(), w.data_ptr(), act.data_ptr(), bt.data_ptr(),
+                                          out.data_ptr(), *common, int(selected_count),
+                                          0 if sort else _lib.PTO_LI_UNSORTED, ws.data_ptr(), ws.numel(),
+                                          torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
 def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
                              block_table, topk_res, unroll_list=None, configs=None, selected_count=2048, *,
                              sort=True, _simt_scores=False, fp16_chain=False):
     """Top-`selected_count` key positions per query token (value-descending, -1 padded).
     `fp16_chain=True` (not in the reference's Python signature) scores with the older formulation of
-    LightningIndexerTopkImpl, lightning_indexer.cpp:150-196 (fp16 scales and weights only)."""
+    LightningIndexerTopkImpl, lightning_indexer.cpp:150-196 (fp16 scales and weights only).
+    A bfloat16 `idx_query` selects the non-quantised formulation (`lightning_indexer_topk_nonquant`; the two scale
+    arguments must then be None)."""
+    if unwrap(idx_query, "idx_query").dtype == torch.bfloat16:
+        _need(idx_query_scale is None and idx_key_scale is None, "bfloat16 idx_query: the scale tensors must be None")
+        _need(not (_simt_scores or fp16_chain), "bfloat16 idx_query: one formulation, tensor cores only")
+        return lightning_indexer_topk_nonquant(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table,
+                                               topk_res, selected_count, sort=sort)
     dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
                                                     idx_weight, act_seq_key, block_table)
     out = unwrap(topk_res, "topk_res")
@@ -494,4 +558,36 @@ def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, id
                                         out.data_ptr(), b, m["s1"], m["block_num"], m["max_blocks"],
                                         int(selected_count), int(nq), float(softmax_scale), flags, ws.data_ptr(),
                                         ws.numel(), torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def decode_indexer_attention(idx_query, idx_key_cache, idx_weight, query_nope, query_rope, key_nope_2d, key_rope_2d,
+                             act_seq, block_table, topk_res, attention_out, nq=128, softmax_scale=576 ** -0.5,
+                             selected_count=2048, *, sort=False):
+    """The non-quantised chain behind the two prologs of `DecodeIndexerAttention`
+    (framework/src/operator/models/deepseek_v3.2_exp/decode_indexer_attention.cpp:108-129): bf16 indexer -> top-k
+    -> sparse attention over the bf16 latent cache with the kernel's own indices. Writes `topk_res` and
+    `attention_out`."""
+    (q, kc, w, act, bt), m = _li_args_bf16(idx_query, idx_key_cache, idx_weight, act_seq, block_table)
+    out_idx = unwrap(topk_res, "topk_res")
+    qn, qr, ti, bt2, act2, out, t, b = _sfa_common(query_nope, query_rope, out_idx, bt, act, attention_out, nq, 1,
+                                                   selected_count)
+    kn = unwrap(key_nope_2d, "key_nope_2d")
+    kr = unwrap(key_rope_2d, "key_rope_2d")
+    _need(t == m["t"], "indexer and attention query token counts differ")
+    _need(int(nq) == 128, "bfloat16 latent cache: all 128 heads of a token")
+    n_rows = m["block_num"] * 128
+    _need(kn.dtype == torch.bfloat16 and tuple(kn.shape) == (n_rows, 512), "key_nope_2d: bfloat16 [block_num*128, 512]")
+    _need(kr.dtype == torch.bfloat16 and tuple(kr.shape) == (n_rows, 64), "key_rope_2d: bfloat16 [block_num*128, 64]")
+    dev = _same_device([q, kc, w, act, bt, qn, qr, kn, kr, out_idx, out])
+    lib = _lib.load()
+    nbytes = lib.pto_decode_workspace_bytes(t, m["max_blocks"], 128, int(nq))
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        _lib.check(lib.pto_decode_fused_bf16(q.data_ptr(), kc.data_ptr(), w.data_ptr(), qn.data_ptr(), qr.data_ptr(),
+                                             kn.data_ptr(), kr.data_ptr(), act.data_ptr(), bt.data_ptr(),
+                                             out_idx.data_ptr(), out.data_ptr(), b, m["s1"], m["block_num"],
+                                             m["max_blocks"], int(selected_count), int(nq), float(softmax_scale),
+                                             0 if sort else _lib.PTO_LI_UNSORTED, ws.data_ptr(), ws.numel(),
+                                             torch.cuda.current_stream(dev).cuda_stream))
     return None

@@ -13,6 +13,7 @@ drivers' pure-torch golden functions are called:
   * lightning_indexer_compute  (examples/models/deepseek_v32_exp/deepseekv32_lightning_indexer_quant.py:184-269)
   * its ST twin that also returns first_mm / mm_out
     (framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_lightning_indexer.py:282-360)
+  * indexer_topk_compute(is_quant=False), the non-quantised indexer   (same ST file, :189-279)
   * compute_attention_no_flash / compute_attention
     (examples/models/deepseek_v32_exp/deepseekv32_sparse_flash_attention_quant.py:169-254, :49-166)
   * compute_attention_aq       (examples/models/deepseek_v32_exp/deepseekv32_sparse_attention_antiquant.py:49-136)
@@ -138,6 +139,33 @@ def make_li(li_mod, st_mod, name, act_seq, s1, dt):
     print(name, "t", d.t, "blocks", d.block_num)
 
 
+NONQUANT_CASES = {
+    # name: (act_seq, s1)
+    "li_nonquant_mtp": ([129, 2500, 3000], 2),
+    "li_nonquant_ragged": ([15, 666, 2049, 4100], 1),
+}
+
+
+def make_li_nonquant(st_mod, name, act_seq, s1):
+    """The ST golden of LightningIndexerTopkImpl with isQuant = false on bf16 inputs of
+    `pypto_b200.inputs.make_nonquant_inputs`."""
+    seed = 13000 + sum(act_seq) + s1
+    d = gen.make_nonquant_inputs(act_seq, s1=s1, seed=seed, with_attention=False)
+    params = dict(block_size=128, selected_count=2048, b=d.b, s1=s1, n1=64, d=128, n2=1, block_num=d.block_num,
+                  max_block_num=d.max_blocks)
+    data = dict(query=d.idx_query.reshape(d.b, s1, 64, 128), key=d.idx_key_cache, weights=d.idx_weight,
+                act_seq=d.act_seq_key, block_table=d.block_table)
+    _, topk, rows = st_mod.indexer_topk_compute(dict(data), params, False)
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed),
+        hashes=np.array([f"{k}={v}" for k, v in input_hashes(d).items()]),
+        topk_res=topk.reshape(d.t, 1, 2048).numpy().astype(np.int32),
+        rows=rows.numpy().astype(np.float32),
+    )
+    print(name, "t", d.t, "blocks", d.block_num)
+
+
 def make_sfa(sfa_mod, aq_mod, name, act_seq, s1):
     seed = 9000 + sum(act_seq) + s1
     d = gen.make_inputs(act_seq, s1=s1, seed=seed, with_indexer=False, with_topk=True)
@@ -242,6 +270,8 @@ def main():
     li_mod, sfa_mod, aq_mod, st_mod = load_reference()
     for name, (act, s1, dt) in LI_CASES.items():
         make_li(li_mod, st_mod, name, act, s1, dt)
+    for name, (act, s1) in NONQUANT_CASES.items():
+        make_li_nonquant(st_mod, name, act, s1)
     for name, (act, s1) in SFA_CASES.items():
         make_sfa(sfa_mod, aq_mod, name, act, s1)
     make_gather_kat()

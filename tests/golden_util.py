@@ -23,7 +23,9 @@ def load_case(name: str, **kw):
     z = np.load(GOLDEN / f"{name}.npz")
     act_seq = [int(x) for x in z["act_seq"]]
     s1 = int(z["s1"])
-    if name.startswith("li_"):
+    if name.startswith("li_nonquant_"):
+        d = gen.make_nonquant_inputs(act_seq, s1=s1, seed=int(z["seed"]), with_attention=False)
+    elif name.startswith("li_"):
         d = gen.make_inputs(act_seq, s1=s1, seed=int(z["seed"]), scale_dtype=getattr(torch, str(z["scale_dtype"])),
                             with_attention=False)
     else:
@@ -48,6 +50,7 @@ def load_prolog_case(name: str):
 
 
 LI_CASES = ["li_ragged_f32", "li_mtp_f16", "li_short_f16"]
+NONQUANT_CASES = ["li_nonquant_mtp", "li_nonquant_ragged"]
 SFA_CASES = ["sfa_ragged_mtp", "sfa_single"]
 
 

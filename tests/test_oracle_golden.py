@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from golden_util import LI_CASES, SFA_CASES, from_np_bf16, load_case, mask_empty_rows, GOLDEN
+from golden_util import LI_CASES, NONQUANT_CASES, SFA_CASES, from_np_bf16, load_case, mask_empty_rows, GOLDEN
 
 
 @pytest.mark.parametrize("name", LI_CASES)
@@ -57,6 +57,27 @@ def test_li_fp16_chain_oracle_matches_reference_golden(name):
                                 d.act_seq, d.block_table, d.s1)
     rel = max(float((a - b).norm() / b.norm()) for a, b in zip(rows, new_rows) if b.numel() > 8)
     assert rel < 5e-3, rel
+
+
+@pytest.mark.parametrize("name", NONQUANT_CASES)
+def test_li_nonquant_oracle_matches_reference_golden(name):
+    """The non-quantised formulation against the ST golden `indexer_topk_compute(is_quant=False)`."""
+    d, z = load_case(name)
+    rows = oracle.li_scores_nonquant(d.idx_query, d.idx_key_cache, d.idx_weight, d.act_seq, d.block_table, d.s1)
+    want_rows = torch.from_numpy(z["rows"])
+    for bi in range(d.b):
+        for i in range(d.s1):
+            ti = bi * d.s1 + i
+            eff = d.act_seq[bi] - (d.s1 - 1 - i)  # the golden fills the causal prefix of each token's row
+            if eff > 0:
+                # fp32 dots of 128 bf16 products and a 64-term head sum: only the summation order differs
+                torch.testing.assert_close(rows[ti][:eff], want_rows[ti, :eff], rtol=1e-5, atol=2e-4)
+    idx, _ = oracle.li_topk(rows, d.act_seq, d.s1)
+    want = torch.from_numpy(z["topk_res"])
+    for ti in range(idx.shape[0]):
+        untied, _ = oracle.topk_set_diff(idx[ti], want[ti], want_rows[ti], rel_tie=1e-5)
+        assert untied == 0, f"row {ti}: {untied} untied differences"
+        assert (idx[ti] >= 0).sum() == (want[ti] >= 0).sum()
 
 
 @pytest.mark.parametrize("name", SFA_CASES)
