@@ -810,7 +810,9 @@ def main():
                      dtype=torch.float64, device=dev)
     # algorithmic bytes and flops summed over the ranks' shards
     by = gen.algorithmic_bytes(d)
-    w = torch.tensor([by["indexer"], by["attention"], gen.score_stage_bytes(d), sfa_flops(d), t], dtype=torch.float64, device=dev)
+    # a head-sharded chunk: every rank holds all query tokens for its 128/N heads, so a token counts once over the ranks
+    t_share = t * d.extras.get("nq", 128) / 128.0
+    w = torch.tensor([by["indexer"], by["attention"], gen.score_stage_bytes(d), sfa_flops(d), t_share], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(v, op=dist.ReduceOp.MAX)
         dist.all_reduce(w, op=dist.ReduceOp.SUM)
@@ -856,7 +858,7 @@ def main():
             "vs_baseline": None, "dtype": "int8+bf16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": f"config{args.config}: fused indexer -> top-2048 -> sparse MLA decode",
                        "step": "the public fused operator, recorded once into a CUDA graph and replayed",
-                       "global_batch": int(t_all) // d.s1 if args.config != 4 else 1, "query_tokens_per_step": int(t_all),
+                       "global_batch": int(round(t_all)) // d.s1 if args.config != 4 else 1, "query_tokens_per_step": int(round(t_all)),
                        "per_gpu_sequences": d.b, "s1": d.s1, "heads_per_gpu": nq,
                        "context": f"{min(d.act_seq)}..{max(d.act_seq)} keys per sequence on rank 0, mean {sum(d.act_seq) / d.b:.0f}",
                        "scale_dtype": args.scale_dtype,

@@ -1,7 +1,6 @@
 // C ABI (include/pypto_b200.h): argument validation, workspace carving, TMA tensor maps, launches.
 // No device memory is allocated here and nothing is kept between calls except cached device
 // attributes.
-#include <cublas_v2.h>
 #include <cuda.h>
 #include <dlfcn.h>
 
@@ -349,103 +348,64 @@ int static_scratch_address(void** out) {
   return PTO_OK;
 }
 
-// ---- cuBLAS for the prolog's projections -------------------------------------------------------------
-// The library is resolved at the first prolog call, not at load time: the indexer and attention entry
-// points have no dependency on it. One handle per device; calls are serialised per device.
-struct Blas {
-  cublasStatus_t (*create)(cublasHandle_t*) = nullptr;
-  cublasStatus_t (*set_stream)(cublasHandle_t, cudaStream_t) = nullptr;
-  cublasStatus_t (*set_workspace)(cublasHandle_t, void*, size_t) = nullptr;
-  cublasStatus_t (*gemm_ex)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
-                            cudaDataType, int, const void*, cudaDataType, int, const void*, void*, cudaDataType, int,
-                            cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
-  cublasStatus_t (*gemm_batched)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
-                                 const void*, cudaDataType, int, long long, const void*, cudaDataType, int, long long,
-                                 const void*, void*, cudaDataType, int, long long, int, cublasComputeType_t,
-                                 cublasGemmAlgo_t) = nullptr;
-  cublasHandle_t handle[64] = {nullptr};
-  // second stream and fork/join events per device: the per-token kernel and the indexer-query kernel run
-  // beside the chain of products they do not depend on
+// ---- per-device side stream of the prolog ------------------------------------------------------------
+// The per-token kernel and the indexer-query kernel run beside the chain of products they do not depend on: a
+// second stream and fork/join events per device, created at the first prolog call on that device.
+struct PrologSide {
   cudaStream_t side[64] = {nullptr};
   cudaEvent_t ev[64][3] = {{nullptr}};
-  std::mutex mu;          // guards the library resolution and the per-device set-up
+  std::mutex mu;          // guards the per-device set-up
   std::mutex dev_mu[64];  // a device's calls enqueue one after the other (they share its side stream and events)
-  bool loaded = false;
 };
 
-Blas& blas() {
-  static Blas b;
-  return b;
+PrologSide& prolog_side() {
+  static PrologSide s;
+  return s;
 }
 
-int blas_handle(cublasHandle_t* out, int* device = nullptr) {
-  Blas& b = blas();
+int prolog_side_stream(int* device) {
+  PrologSide& b = prolog_side();
   std::lock_guard<std::mutex> lock(b.mu);
-  if (!b.loaded) {
-    void* lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
-    if (lib == nullptr) return fail(PTO_ERR_UNSUPPORTED, "libcublas.so.12 not found: %s", dlerror());
-    b.create = reinterpret_cast<decltype(b.create)>(dlsym(lib, "cublasCreate_v2"));
-    b.set_stream = reinterpret_cast<decltype(b.set_stream)>(dlsym(lib, "cublasSetStream_v2"));
-    b.set_workspace = reinterpret_cast<decltype(b.set_workspace)>(dlsym(lib, "cublasSetWorkspace_v2"));
-    b.gemm_ex = reinterpret_cast<decltype(b.gemm_ex)>(dlsym(lib, "cublasGemmEx"));
-    b.gemm_batched = reinterpret_cast<decltype(b.gemm_batched)>(dlsym(lib, "cublasGemmStridedBatchedEx"));
-    if (!b.create || !b.set_stream || !b.set_workspace || !b.gemm_ex || !b.gemm_batched) {
-      return fail(PTO_ERR_UNSUPPORTED, "libcublas.so.12 lacks a required entry point");
-    }
-    b.loaded = true;
-  }
   int dev = 0;
   PTO_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(PTO_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (b.handle[dev] == nullptr) {
-    cublasStatus_t st = b.create(&b.handle[dev]);
-    if (st != CUBLAS_STATUS_SUCCESS) return fail(PTO_ERR_CUDA, "cublasCreate failed with %d", static_cast<int>(st));
-  }
   if (b.side[dev] == nullptr) {
     PTO_CUDA(cudaStreamCreateWithFlags(&b.side[dev], cudaStreamNonBlocking));
     for (int i = 0; i < 3; ++i) PTO_CUDA(cudaEventCreateWithFlags(&b.ev[dev][i], cudaEventDisableTiming));
   }
-  *out = b.handle[dev];
-  if (device != nullptr) *device = dev;
+  *device = dev;
   return PTO_OK;
 }
 
-#define PTO_BLAS(expr)                                                                          \
-  do {                                                                                          \
-    cublasStatus_t s__ = (expr);                                                                \
-    if (s__ != CUBLAS_STATUS_SUCCESS) return fail(PTO_ERR_CUDA, "%s: cuBLAS status %d", #expr, static_cast<int>(s__)); \
-  } while (0)
-
-// C[t, n] (row-major, type `ctype`) = A[t, k] @ W[k, n], both row-major: in cuBLAS's column-major terms
-// C^T[n, t] = W^T[n, k] . A^T[k, t], i.e. an untransposed product with W as the left operand.
-int gemm_rowmajor(cublasHandle_t h, int t, int n, int k, const void* a, int lda, const void* w, int ldw, void* c, int ldc,
-                  cudaDataType in_type, cudaDataType ctype) {
-  Blas& b = blas();
-  if (in_type == CUDA_R_8I) {
-    const int32_t one = 1, zero = 0;
-    PTO_BLAS(b.gemm_ex(h, CUBLAS_OP_N, CUBLAS_OP_N, n, t, k, &one, w, CUDA_R_8I, ldw, a, CUDA_R_8I, lda, &zero, c,
-                       CUDA_R_32I, ldc, CUBLAS_COMPUTE_32I, CUBLAS_GEMM_DEFAULT));
-  } else {
-    const float one = 1.f, zero = 0.f;
-    PTO_BLAS(b.gemm_ex(h, CUBLAS_OP_N, CUBLAS_OP_N, n, t, k, &one, w, in_type, ldw, a, in_type, lda, &zero, c, ctype,
-                       ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
-  }
+// One weight-streaming product (prolog_sgemm.cu): out = x[t, k] . W[k, n] per problem of the batch.
+// kind 0: bf16 -> fp32 partials, 1: bf16 -> bf16, 2: int8 -> int32. Row pitches in bytes.
+int run_sgemm(int kind, const void* x, size_t x_pitch, const void* w, size_t w_pitch, int64_t w_rows, void* out, int t,
+              int n, int k, int batch, int w_batch_rows, int x_batch_bytes, long long out_batch, long long ld_out,
+              int splits, long long split_stride, int num_sms, int32_t* status, cudaStream_t stream, bool pdl = false) {
+  alignas(64) CUtensorMap map_w, map_x;
+  int rc = make_bytes_map(&map_w, w, w_pitch, static_cast<uint64_t>(w_rows), w_pitch, kind == 2 ? 128 : 64);
+  if (rc != PTO_OK) return rc;
+  rc = make_bytes_map(&map_x, x, x_pitch, static_cast<uint64_t>(t), x_pitch, static_cast<uint32_t>(pto::prolog_sgemm_rows(t)));
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_prolog_sgemm(kind, &map_w, &map_x, out, t, n, k, batch, w_batch_rows, x_batch_bytes, out_batch,
+                                    ld_out, splits, split_stride, num_sms, status, stream, pdl));
   return PTO_OK;
 }
 
-constexpr size_t kBlasWorkspace = 32u << 20;
+// SM count the K-split of the hidden-state projections is planned for (the workspace size must not depend on the
+// device the call later runs on; this library targets the 148-SM B200 only)
+constexpr int kPlanSms = 148;
 
 struct PrologWs {
-  size_t status, blas, xproj, q_norm, q_norm_scale, qb_i32, q_b, qi_i32, total;
+  size_t status, xproj, q_norm, q_norm_scale, qb_i32, q_b, qi_i32, total;
+  int splits;  // K-split partials of the hidden-state projections
 };
 constexpr int kXProjExtra = 576 + 128 + 64;  // columns after the q_lora ones: latent+rope key | indexer key | weights
 
-// The int8 products run with at least 64 rows: below that the library falls back to a kernel for narrow
-// outputs that is several times slower (measured: 104 + 55 us at 8 tokens against 17 + 11 us at 64). The
-// padding rows are workspace contents; their results are never read.
+// Rows of the int8 activation buffer: the resident-activation kernel's tensor map covers whole 16-row groups.
 inline int prolog_int8_rows(int t) { return t < 64 ? 64 : t; }
 
-PrologWs prolog_ws(int t, int q_lora) {
+PrologWs prolog_ws(int t, int hidden, int q_lora) {
   PrologWs w{};
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -456,8 +416,8 @@ PrologWs prolog_ws(int t, int q_lora) {
   const size_t tt = static_cast<size_t>(t);
   const size_t tp = static_cast<size_t>(prolog_int8_rows(t));
   w.status = take(kStatusBytes);
-  w.blas = take(kBlasWorkspace);
-  w.xproj = take(tt * (q_lora + kXProjExtra) * 4);  // fp32 [t, q_lora | 576 | 128 | 64]
+  w.splits = pto::prolog_sgemm_splits(t, q_lora + kXProjExtra, hidden, kPlanSms);
+  w.xproj = take(w.splits * tt * (q_lora + kXProjExtra) * 4);  // fp32 [splits, t, q_lora | 576 | 128 | 64]
   w.q_norm = take(tp * q_lora);
   w.q_norm_scale = take(tt * 4);
   w.qb_i32 = take(tp * 128 * 192 * 4);
@@ -692,7 +652,7 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
 
 size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora) {
   if (t < 1 || hidden < 1 || q_lora < 1) return 0;
-  return prolog_ws(t, q_lora).total;
+  return prolog_ws(t, hidden, q_lora).total;
 }
 
 int pto_kv_pack_rows(const int8_t* key_nope_2d, const void* key_rope_2d, const float* k_nope_scales, int64_t n_rows,
@@ -755,7 +715,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   DeviceInfo di;
   int rc = get_device_info(&di);
   if (rc != PTO_OK) return rc;
-  const PrologWs w = prolog_ws(t, q_lora);
+  const PrologWs w = prolog_ws(t, hidden, q_lora);
   rc = check_workspace(workspace, workspace_bytes, w.total);
   if (rc != PTO_OK) return rc;
   uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
@@ -771,41 +731,46 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   void* q_b = base + w.q_b;
   int32_t* qi_i32 = reinterpret_cast<int32_t*>(base + w.qi_i32);
 
-  cublasHandle_t h;
   int dev = 0;
-  rc = blas_handle(&h, &dev);
+  rc = prolog_side_stream(&dev);
   if (rc != PTO_OK) return rc;
-  std::lock_guard<std::mutex> lock(blas().dev_mu[dev]);
-  cudaStream_t side = blas().side[dev];
-  cudaEvent_t* ev = blas().ev[dev];
-  PTO_BLAS(blas().set_stream(h, stream));
-  PTO_BLAS(blas().set_workspace(h, base + w.blas, kBlasWorkspace));  // no allocation inside a captured call
+  std::lock_guard<std::mutex> lock(prolog_side().dev_mu[dev]);
+  cudaStream_t side = prolog_side().side[dev];
+  cudaEvent_t* ev = prolog_side().ev[dev];
 
-  // projections of the token: fp32 results [t, q_lora | 576 | 128 | 64], rounded where the golden rounds by the
-  // kernels that read them. One product when the caller has packed the four weights side by side, else four.
+  // projections of the token: fp32 partials [splits][t, q_lora | 576 | 128 | 64] (K split over CTAs), added and
+  // rounded where the golden rounds by the kernels that read them. One product when the caller has packed the four
+  // weights side by side, else four.
+  const int splits = w.splits;
+  const long long split_stride = static_cast<long long>(t) * ld;
+  const size_t x_pitch = static_cast<size_t>(hidden) * 2;
   if (w_x_packed != nullptr) {
     PTO_REQUIRE(aligned16(w_x_packed), "w_x_packed must be 16-byte aligned");
-    rc = gemm_rowmajor(h, t, ld, hidden, token_x, hidden, w_x_packed, ld, qa, ld, CUDA_R_16BF, CUDA_R_32F);
+    rc = run_sgemm(0, token_x, x_pitch, w_x_packed, static_cast<size_t>(ld) * 2, hidden, qa, t, ld, hidden, 1, 0, 0, 0, ld,
+                   splits, split_stride, di.num_sms, status, stream);
     if (rc != PTO_OK) return rc;
   } else {
-    rc = gemm_rowmajor(h, t, q_lora, hidden, token_x, hidden, w_dq, q_lora, qa, ld, CUDA_R_16BF, CUDA_R_32F);
-    if (rc != PTO_OK) return rc;
-    rc = gemm_rowmajor(h, t, 576, hidden, token_x, hidden, w_dkvkr, 576, kv, ld, CUDA_R_16BF, CUDA_R_32F);
-    if (rc != PTO_OK) return rc;
-    rc = gemm_rowmajor(h, t, 128, hidden, token_x, hidden, w_idx_k, 128, ki, ld, CUDA_R_16BF, CUDA_R_32F);
-    if (rc != PTO_OK) return rc;
-    rc = gemm_rowmajor(h, t, 64, hidden, token_x, hidden, w_idx_proj, 64, wp, ld, CUDA_R_16BF, CUDA_R_32F);
-    if (rc != PTO_OK) return rc;
+    const void* ws[4] = {w_dq, w_dkvkr, w_idx_k, w_idx_proj};
+    float* outs[4] = {qa, kv, ki, wp};
+    const int ns[4] = {q_lora, 576, 128, 64};
+    for (int i = 0; i < 4; ++i) {
+      rc = run_sgemm(0, token_x, x_pitch, ws[i], static_cast<size_t>(ns[i]) * 2, hidden, outs[i], t, ns[i], hidden, 1, 0, 0,
+                     0, ld, splits, split_stride, di.num_sms, status, stream);
+      if (rc != PTO_OK) return rc;
+    }
   }
   // fork: the per-token kernel (caches, indexer key, weights) needs only the projections
   PTO_CUDA(cudaEventRecord(ev[0], stream));
   PTO_CUDA(cudaStreamWaitEvent(side, ev[0], 0));
-  PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, ld, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k, cache_index, cache_rows,
-                                 t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache, idx_k_cache, idx_k_scale_cache,
-                                 weights_out, packed_kv_cache, status, side));
-  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale, stream));
-  // int8 up-projections of the normalised query: one tcgen05 weight-streaming launch for both when the token
-  // rows fit its resident activation buffer (decode), else two library products
+  PTO_CUDA(pto::launch_prolog_kv(kv, ki, wp, ld, splits, split_stride, gamma_ckv, cos, sin, ln_gamma, ln_beta, hadamard_k,
+                                 cache_index, cache_rows, t, eps_ckv, ln_eps, kv_cache, kr_cache, kv_scale_cache,
+                                 idx_k_cache, idx_k_scale_cache, weights_out, packed_kv_cache, status, side));
+  // from here on every kernel of the caller's stream follows a kernel of this call: each may be scheduled while
+  // the one before it drains (it waits before it reads)
+  PTO_CUDA(pto::launch_prolog_qnorm_quant(qa, ld, splits, split_stride, gamma_cq, t, q_lora, eps_cq, q_norm, q_norm_scale,
+                                          stream, /*pdl=*/true));
+  // int8 up-projections of the normalised query: one launch for both with the activations resident in shared
+  // memory when the token rows fit (decode), else one streaming product per weight over blocks of 256 tokens
   const int tp = prolog_int8_rows(t);
   if (pto::prolog_i8_gemm_supported(t, q_lora)) {
     alignas(64) CUtensorMap map_w0, map_w1, map_x;
@@ -816,11 +781,13 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
     rc = make_bytes_map(&map_x, q_norm, q_lora, tp, q_lora, static_cast<uint32_t>((t + 15) / 16 * 16));
     if (rc != PTO_OK) return rc;
     PTO_CUDA(pto::launch_prolog_i8_gemm(&map_w0, &map_w1, &map_x, qb_i32, 128 * 192, qi_i32, 64 * 128, q_lora, t,
-                                        di.num_sms, status, stream));
+                                        di.num_sms, status, stream, /*pdl=*/true));
   } else {
-    rc = gemm_rowmajor(h, tp, 128 * 192, q_lora, q_norm, q_lora, w_uqqr, 128 * 192, qb_i32, 128 * 192, CUDA_R_8I, CUDA_R_32I);
+    rc = run_sgemm(2, q_norm, q_lora, w_uqqr, 128 * 192, q_lora, qb_i32, t, 128 * 192, q_lora, 1, 0, 0, 0, 128 * 192, 1, 0,
+                   di.num_sms, status, stream, /*pdl=*/true);
     if (rc != PTO_OK) return rc;
-    rc = gemm_rowmajor(h, tp, 64 * 128, q_lora, q_norm, q_lora, w_idx_qb, 64 * 128, qi_i32, 64 * 128, CUDA_R_8I, CUDA_R_32I);
+    rc = run_sgemm(2, q_norm, q_lora, w_idx_qb, 64 * 128, q_lora, qi_i32, t, 64 * 128, q_lora, 1, 0, 0, 0, 64 * 128, 1, 0,
+                   di.num_sms, status, stream, /*pdl=*/true);
     if (rc != PTO_OK) return rc;
   }
   // the indexer-query kernel joins the side stream; the attention query finishes on the caller's
@@ -829,14 +796,12 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
   PTO_CUDA(pto::launch_prolog_idxq(qi_i32, q_norm_scale, w_idx_qb_scale, cos, sin, hadamard_q, t, q_int8_out, q_scale_out,
                                    side));
   PTO_CUDA(cudaEventRecord(ev[2], side));
-  PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream));
-  // absorbed nope part: per head [t, 128] (row stride 128*192, head stride 192) @ w_uk[head] [128, 512] -> bf16
-  {
-    const float one = 1.f, zero = 0.f;
-    PTO_BLAS(blas().gemm_batched(h, CUBLAS_OP_N, CUBLAS_OP_N, 512, t, 128, &one, w_uk, CUDA_R_16BF, 512, 128LL * 512, q_b,
-                                 CUDA_R_16BF, 128 * 192, 192LL, &zero, query_nope_out, CUDA_R_16BF, 128 * 512, 512LL, 128,
-                                 CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
-  }
+  PTO_CUDA(pto::launch_prolog_qb_dequant_rope(qb_i32, q_norm_scale, w_qb_scale, cos, sin, t, q_b, query_rope_out, stream,
+                                              /*pdl=*/true));
+  // absorbed nope part: per head [t, 128] (row pitch 128*192, head pitch 192 elements) @ w_uk[head] [128, 512] -> bf16
+  rc = run_sgemm(1, q_b, 128 * 192 * 2, w_uk, 512 * 2, 128 * 128, query_nope_out, t, 512, 128, 128, 128, 192 * 2, 512,
+                 128 * 512, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
+  if (rc != PTO_OK) return rc;
   PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));  // join: everything is ordered before what the caller enqueues next
   return PTO_OK;
 }

@@ -325,15 +325,35 @@ cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq 
 cudaError_t launch_sfa_pair(const SfaParams& p, cudaStream_t stream);     // nq == 128, int8 cache: 2-SM MMAs, heads split over the pair
 int sfa_pair_split(int t, int num_sms);
 
+// Launch with the programmatic-serialization attribute when `pdl`: the grid may be scheduled while the kernel
+// before it in the stream drains, and must execute pdl_wait() before it touches global memory that kernel wrote.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_maybe_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Prolog stages between the projections (prolog.cu). Fixed widths: 128 heads x (128 + 64), latent 512,
-// rope 64, indexer 64 x 128. `ld`: row stride (elements) of the fp32 projection results.
-cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
-                                      int8_t* q_norm, float* q_norm_scale, cudaStream_t stream);
+// rope 64, indexer 64 x 128. `ld`: row stride (elements) of the fp32 projection results, which arrive as `n_split`
+// K-split partials `split_stride` elements apart and are added in split order by the kernels that read them.
+cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, int n_split, long long split_stride, const void* gamma_cq,
+                                      int t, int q_lora, float eps, int8_t* q_norm, float* q_norm_scale,
+                                      cudaStream_t stream, bool pdl = false);
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
                                           const void* cos, const void* sin, int t, void* q_b, void* q_rope,
-                                          cudaStream_t stream);
-cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, const void* gamma_ckv, const void* cos,
-                             const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
+                                          cudaStream_t stream, bool pdl = false);
+cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, int n_split,
+                             long long split_stride, const void* gamma_ckv, const void* cos, const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
                              void* idx_k_scale_cache, void* weights, int8_t* packed_cache, int32_t* status,
@@ -341,7 +361,15 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
 // both int8 up-projections of the prolog in one tcgen05 launch (prolog_gemm.cu); t <= 64 token rows
 bool prolog_i8_gemm_supported(int t, int k);
 cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, const void* tmap_x, int32_t* out0, int n0,
-                                  int32_t* out1, int n1, int k, int t, int num_sms, int32_t* status, cudaStream_t stream);
+                                  int32_t* out1, int n1, int k, int t, int num_sms, int32_t* status, cudaStream_t stream,
+                                  bool pdl = false);
+// the weight-streaming products of the prolog (prolog_sgemm.cu)
+int prolog_sgemm_rows(int t);
+int prolog_sgemm_splits(int t, int n, int k, int num_sms);
+cudaError_t launch_prolog_sgemm(int kind, const void* tmap_w, const void* tmap_x, void* out, int t, int n, int k,
+                                int batch, int w_batch_rows, int x_batch_bytes, long long out_batch, long long ld_out,
+                                int splits, long long split_stride, int num_sms, int32_t* status, cudaStream_t stream,
+                                bool pdl = false);
 cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* sc, int64_t rows, int8_t* packed,
                                 int num_sms, cudaStream_t stream);
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,

@@ -65,10 +65,13 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale_q) {
 // ---- query down-projection: bf16 rounding, RMSNorm, per-token int8 ------------------------------------
 // grid = tokens, 512 threads, dynamic shared memory = q_lora floats (16-byte aligned rows: ld and q_lora multiples of 4)
 __global__ void __launch_bounds__(512)
-prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, const __nv_bfloat16* __restrict__ gamma, int q_lora,
-                          float eps, int8_t* __restrict__ q_norm, float* __restrict__ q_norm_scale) {
+prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, int n_split, long long split_stride,
+                          const __nv_bfloat16* __restrict__ gamma, int q_lora, float eps, int8_t* __restrict__ q_norm,
+                          float* __restrict__ q_norm_scale) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
+  pdl_wait();  // the projection before it may still be running when this grid is scheduled
+  if (threadIdx.x == 0) pdl_trigger();
   const int ti = blockIdx.x;
   const float4* src = reinterpret_cast<const float4*>(qa + static_cast<int64_t>(ti) * ld);
   float4* row4 = reinterpret_cast<float4*>(row);
@@ -76,7 +79,21 @@ prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, const __nv_bfloa
   const float inv_n = 1.0f / static_cast<float>(q_lora);
   float ss = 0.f;
   for (int g = threadIdx.x; g < groups; g += blockDim.x) {
-    float4 v = __ldg(src + g);
+    float4 part[8];  // K-split partials of the projection (n_split <= 8): requested together, added in split order
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) {
+      part[sp] = sp < n_split ? __ldg(src + g + sp * (split_stride >> 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 v = part[0];
+#pragma unroll
+    for (int sp = 1; sp < 8; ++sp) {
+      if (sp < n_split) {
+        v.x = __fadd_rn(v.x, part[sp].x);
+        v.y = __fadd_rn(v.y, part[sp].y);
+        v.z = __fadd_rn(v.z, part[sp].z);
+        v.w = __fadd_rn(v.w, part[sp].w);
+      }
+    }
     v.x = bf16_round(v.x);
     v.y = bf16_round(v.y);
     v.z = bf16_round(v.z);
@@ -123,6 +140,8 @@ prolog_qb_dequant_rope_kernel(const int32_t* __restrict__ qb_i32, const float* _
                               const __nv_bfloat16* __restrict__ sin, __nv_bfloat16* __restrict__ q_b,
                               __nv_bfloat16* __restrict__ q_rope) {
   __shared__ float pe[kQbHeadsPerBlock][kRope];
+  pdl_wait();
+  if (threadIdx.x == 0) pdl_trigger();
   const int hg = blockIdx.x, ti = blockIdx.y;
   const float rs = q_norm_scale[ti];
   const int64_t col0 = static_cast<int64_t>(hg) * kQbHeadsPerBlock * kQHead;
@@ -156,7 +175,7 @@ prolog_qb_dequant_rope_kernel(const int32_t* __restrict__ qb_i32, const float* _
 // grid = tokens, block = 128 (thread i owns latent dims 4i..4i+3: warp w = 128-wide quantisation tile w)
 __global__ void __launch_bounds__(128)
 prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, const float* __restrict__ wp, int ld,
-                 const __nv_bfloat16* __restrict__ gamma_ckv, const __nv_bfloat16* __restrict__ cos,
+                 int n_split, long long split_stride, const __nv_bfloat16* __restrict__ gamma_ckv, const __nv_bfloat16* __restrict__ cos,
                  const __nv_bfloat16* __restrict__ sin, const __nv_bfloat16* __restrict__ ln_gamma,
                  const __nv_bfloat16* __restrict__ ln_beta, const __nv_bfloat16* __restrict__ hadamard_k,
                  const int64_t* __restrict__ cache_index, int64_t cache_rows, float eps_ckv, float ln_eps,
@@ -178,13 +197,25 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   const bool row_ok = row >= 0 && row < cache_rows;
   if (!row_ok && i == 0) set_status(status, PTO_ST_BAD_PAGE, static_cast<int>(row), 60);
 
+  // a projection value: its K-split partials added in split order
+  auto proj = [&](const float* p) {
+    float part[8];  // all partials requested before the first is used (n_split <= 8)
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) part[sp] = sp < n_split ? __ldg(p + sp * split_stride) : 0.f;
+    float a = part[0];
+#pragma unroll
+    for (int sp = 1; sp < 8; ++sp) {
+      if (sp < n_split) a = __fadd_rn(a, part[sp]);
+    }
+    return a;
+  };
   // latent part: bf16 rounding, RMSNorm, int8 per 128-wide tile
   const float* src = kv + static_cast<int64_t>(ti) * ld;
   float v[4];
   float ss = 0.f;
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    v[e] = bf16_round(src[4 * i + e]);
+    v[e] = bf16_round(proj(src + 4 * i + e));
     ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v[e], v[e]), 1.0f / kLora));
   }
   const float rms = sqrtf(block_sum(ss, red) + eps_ckv);
@@ -212,7 +243,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   }
 
   // rope key: the 64 values after the latent part, de-interleaved rope
-  if (i < kRope) pe[i] = bf16_round(src[kLora + i]);
+  if (i < kRope) pe[i] = bf16_round(proj(src + kLora + i));
   __syncthreads();
   if (i < kRope && row_ok) {
     const int j = i & 31;
@@ -226,7 +257,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
   }
 
   // indexer key: LayerNorm in fp32 -> bf16, rope on the first 64 dims (halves, no de-interleave), Hadamard, int8
-  const float x = ki[static_cast<int64_t>(ti) * ld + i];
+  const float x = proj(ki + static_cast<int64_t>(ti) * ld + i);
   const float mean = block_sum(x, red) * (1.0f / kIdxDim);
   const float dx = x - mean;
   const float var = block_sum(__fmul_rn(dx, dx), red) * (1.0f / kIdxDim);
@@ -255,7 +286,7 @@ prolog_kv_kernel(const float* __restrict__ kv, const float* __restrict__ ki, con
 
   // indexer weights: bf16 rounding, then heads^-1/2 and dim^-1/2 in fp32, fp16 out
   if (i < kIdxHeads) {
-    const float w = bf16_round(wp[static_cast<int64_t>(ti) * ld + i]);
+    const float w = bf16_round(proj(wp + static_cast<int64_t>(ti) * ld + i));
     weights[static_cast<int64_t>(ti) * kIdxHeads + i] =
         __float2half_rn(__fmul_rn(__fmul_rn(w, 0.125f), 0.08838834764831845f));
   }
@@ -365,8 +396,9 @@ cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* s
   return cudaGetLastError();
 }
 
-cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma_cq, int t, int q_lora, float eps,
-                                      int8_t* q_norm, float* q_norm_scale, cudaStream_t stream) {
+cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, int n_split, long long split_stride, const void* gamma_cq,
+                                      int t, int q_lora, float eps, int8_t* q_norm, float* q_norm_scale,
+                                      cudaStream_t stream, bool pdl) {
   const size_t dyn = static_cast<size_t>(q_lora) * sizeof(float);
   if (dyn > 40 * 1024) {  // beyond what fits the default 48 KB next to the kernel's static shared memory
     cudaError_t e = cudaFuncSetAttribute(prolog_qnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -374,23 +406,22 @@ cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, const void* gamma
     if (e != cudaSuccess) return e;
   }
   count_launch();
-  prolog_qnorm_quant_kernel<<<t, 512, dyn, stream>>>(
-      qa, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
-  return cudaGetLastError();
+  return launch_maybe_pdl(prolog_qnorm_quant_kernel, dim3(t), dim3(512), dyn, stream, pdl, qa, ld, n_split, split_stride,
+                          reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
 }
 
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
                                           const void* cos, const void* sin, int t, void* q_b, void* q_rope,
-                                          cudaStream_t stream) {
+                                          cudaStream_t stream, bool pdl) {
   count_launch();
-  prolog_qb_dequant_rope_kernel<<<dim3(kHeads / kQbHeadsPerBlock, t), 256, 0, stream>>>(
-      qb_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
-      reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_b),
-      reinterpret_cast<__nv_bfloat16*>(q_rope));
-  return cudaGetLastError();
+  return launch_maybe_pdl(prolog_qb_dequant_rope_kernel, dim3(kHeads / kQbHeadsPerBlock, t), dim3(256), 0, stream, pdl,
+                          qb_i32, q_norm_scale, w_scale, reinterpret_cast<const __nv_bfloat16*>(cos),
+                          reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_b),
+                          reinterpret_cast<__nv_bfloat16*>(q_rope));
 }
 
-cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, const void* gamma_ckv, const void* cos,
+cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, int ld, int n_split,
+                             long long split_stride, const void* gamma_ckv, const void* cos,
                              const void* sin, const void* ln_gamma, const void* ln_beta, const void* hadamard_k,
                              const int64_t* cache_index, int64_t cache_rows, int t, float eps_ckv, float ln_eps,
                              int8_t* kv_cache, void* kr_cache, float* kv_scale_cache, int8_t* idx_k_cache,
@@ -398,7 +429,8 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
                              cudaStream_t stream) {
   count_launch();
   prolog_kv_kernel<<<t, 128, 0, stream>>>(
-      kv, ki, wp, ld, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv), reinterpret_cast<const __nv_bfloat16*>(cos),
+      kv, ki, wp, ld, n_split, split_stride, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv),
+      reinterpret_cast<const __nv_bfloat16*>(cos),
       reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<const __nv_bfloat16*>(ln_gamma),
       reinterpret_cast<const __nv_bfloat16*>(ln_beta), reinterpret_cast<const __nv_bfloat16*>(hadamard_k), cache_index,
       cache_rows, eps_ckv, ln_eps, kv_cache, reinterpret_cast<__nv_bfloat16*>(kr_cache), kv_scale_cache, idx_k_cache,

@@ -90,6 +90,9 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  // the set-up above overlaps the tail of the kernel before it; its results are read from here on
+  pdl_wait();
+  if (tid == 0) pdl_trigger();
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -204,7 +207,8 @@ bool prolog_i8_gemm_supported(int t, int k) {
 }
 
 cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, const void* tmap_x, int32_t* out0, int n0,
-                                  int32_t* out1, int n1, int k, int t, int num_sms, int32_t* status, cudaStream_t stream) {
+                                  int32_t* out1, int n1, int k, int t, int num_sms, int32_t* status, cudaStream_t stream,
+                                  bool pdl) {
   cudaError_t e = cudaFuncSetAttribute(prolog_i8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGSmemBytes);
   if (e != cudaSuccess) return e;
   GemmParams p{};
@@ -221,10 +225,9 @@ cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, cons
   const int n_tiles = p.tiles[0] + p.tiles[1];
   const int grid = n_tiles < num_sms ? n_tiles : num_sms;
   count_launch();
-  prolog_i8_gemm_kernel<<<grid, kGThreads, kGSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_w0),
-                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_w1),
-                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_x), p);
-  return cudaGetLastError();
+  return launch_maybe_pdl(prolog_i8_gemm_kernel, dim3(grid), dim3(kGThreads), kGSmemBytes, stream, pdl,
+                          *reinterpret_cast<const CUtensorMap*>(tmap_w0), *reinterpret_cast<const CUtensorMap*>(tmap_w1),
+                          *reinterpret_cast<const CUtensorMap*>(tmap_x), p);
 }
 
 }  // namespace pto
