@@ -19,8 +19,7 @@
  *   - the library allocates no device memory; the indexer, attention and fused entry points keep no
  *     state between calls and are re-entrant (calls on different streams need different
  *     workspaces). The prolog entry point is the exception: per device it creates, at its first
- *     call, a second stream and three events (and, as long as a projection is still issued to the
- *     GEMM library, that library's handle), and its calls on one device are serialised by a
+ *     call, a second stream and three events, and its calls on one device are serialised by a
  *     per-device mutex while they enqueue. A prolog call must not be enqueued on a device while
  *     another stream of that device is capturing a prolog call: both would use the same side
  *     stream.
@@ -67,7 +66,7 @@ typedef struct CUstream_st* pto_stream_t; /* cudaStream_t */
 int pto_abi_version(void);
 const char* pto_strerror(int code);
 const char* pto_last_error(void);
-/* Kernels of this library enqueued so far by this process (library GEMMs of the prolog are not counted): a
+/* Kernels of this library enqueued so far by this process (every kernel of every entry point): a
  * diagnostic that a call reached the CUDA path. A launch recorded during stream capture counts once, at
  * capture time. No counterpart in the reference. */
 long long pto_launch_count(void);
@@ -240,9 +239,10 @@ int pto_sfa_packed(const void* query_nope, const void* query_rope, const int8_t*
  *   query_nope_out bf16 [t, 128, 512]   query_rope_out bf16 [t, 128, 64]
  *   q_int8_out int8 [t, 64, 128]        q_scale_out f16 [t, 64]        weights_out f16 [t, 64]
  *
- * The seven projections are plain GEMMs issued to cuBLAS (libcublas.so.12, resolved at the first call;
- * PTO_ERR_UNSUPPORTED if absent); everything between them is this library's kernels. No allocation:
- * the workspace also holds cuBLAS's own scratch, so the call can be recorded into a CUDA graph.
+ * The seven projections and everything between them are this library's kernels (no GEMM library is loaded):
+ * the bf16 projections of the hidden state are split over K and leave fp32 partials in the workspace that the
+ * kernels reading them add in a fixed order, so the call is deterministic. No allocation: the call can be
+ * recorded into a CUDA graph.
  * ------------------------------------------------------------------------------------------ */
 size_t pto_prolog_workspace_bytes(int t, int hidden, int q_lora);
 

@@ -1,5 +1,5 @@
-// MLA + lightning-indexer prolog: everything between the projections (plain library GEMMs, issued by the
-// C entry point) — RMSNorm / LayerNorm, rope, Hadamard rotation, dynamic int8 quantisation, dequantisation of
+// MLA + lightning-indexer prolog: everything between the projections (the weight-streaming products of
+// prolog_gemm.cu and prolog_sgemm.cu, issued by the C entry point) — RMSNorm / LayerNorm, rope, Hadamard rotation, dynamic int8 quantisation, dequantisation of
 // the int32 products, and the scatter of the new token's rows into the paged caches.
 //
 // Arithmetic follows the reference's torch goldens step by step, including every intermediate rounding to

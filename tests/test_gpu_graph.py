@@ -55,7 +55,7 @@ def test_captured_step_replays_and_tracks_input_updates():
 
 
 def test_captured_prolog_then_decode_layer():
-    """The prolog (library products on two streams, own kernels between them) and the decode chain behind it in ONE
+    """The prolog (eight kernels on two streams) and the decode chain behind it in ONE
     graph: a replay reproduces the eager sequence bit for bit, tracks a new token batch written into the static
     input, and allocates nothing."""
     act = [3000, 700, 4500, 129]
