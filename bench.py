@@ -288,7 +288,13 @@ def run_stage(args, dev):
     if args.stage == "sfa_bf16":  # the non-quantised latent cache holding the values the int8 one dequantises to
         kn_bf16 = (d.key_nope_2d.to(torch.float32).reshape(-1, 4, 128) * d.k_nope_scales.reshape(-1, 4, 1)
                    ).reshape(-1, 512).to(torch.bfloat16)
+    packed = torch.empty((d.key_nope_2d.shape[0], 656), dtype=torch.int8, device=dev) if args.stage == "kv_pack" else None
+    nq_d = gen.make_nonquant_inputs([args.ctx] * args.batch, s1=args.s1, seed=4321, device=dev,
+                                    with_attention=False) if args.stage == "li_score_nonquant" else None
     fns = {
+        "kv_pack": lambda: pto.pack_kv_cache(d.key_nope_2d, d.key_rope_2d, d.k_nope_scales, packed),
+        "li_score_nonquant": lambda: pto.lightning_indexer_topk_nonquant(
+            nq_d.idx_query, nq_d.idx_key_cache, nq_d.idx_weight, nq_d.act_seq_key, nq_d.block_table, None, scores_out=sc),
         "li_score": lambda: pto.lightning_indexer_scores(*li, sc),
         "li_score_chain": lambda: pto.lightning_indexer_scores(*li, sc, fp16_chain=True),  # needs --scale-dtype float16
         "li_decode": lambda: pto.lightning_indexer_decode(*li, idx, None, None, 2048),
@@ -526,7 +532,8 @@ def main():
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--partition", default="heads", choices=["heads", "tokens"], help="configuration 4 on N > 1 GPUs")
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
-    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer", "li_score_chain"],
+    ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer", "li_score_chain",
+                             "kv_pack", "li_score_nonquant"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

@@ -129,6 +129,9 @@ int make_bytes_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t 
   return PTO_OK;
 }
 
+// histogram rows the score kernel leaves for the top-k kernel (LiParams::hist), at the end of a workspace
+size_t li_hist_bytes(int t) { return align_up(static_cast<size_t>(t) * pto::kLiHistBins * sizeof(unsigned int), 256); }
+
 size_t li_scores_bytes(int t, int max_blocks, int block_size) {
   return align_up(static_cast<size_t>(t) * max_blocks * block_size * sizeof(float), 256);
 }
@@ -182,7 +185,7 @@ int check_li_bf16(const void* q, const void* kc, const void* w, const void* act,
 // Score stage for tokens-per-sequence s1 (any s1 >= 1: groups of up to 4 tokens per launch).
 int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void* ks, const void* w, int scale_dtype,
                   const int32_t* act, const int32_t* bt, float* scores, void* first_mm, int b, int s1, int block_num,
-                  int max_blocks, int flags, int32_t* status, cudaStream_t stream) {
+                  int max_blocks, int flags, int32_t* status, cudaStream_t stream, unsigned int* hist = nullptr) {
   pto::LiParams p{};
   p.q = q;
   p.q_scale = qs;
@@ -201,6 +204,10 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
   p.status = status;
   const bool simt = (flags & PTO_LI_SCORE_SIMT) != 0;
   PTO_REQUIRE(simt || first_mm == nullptr, "first_mm is only produced with PTO_LI_SCORE_SIMT");
+  if (hist != nullptr) {  // li_hist_usable() said yes: every launch below takes all s1 tokens of a sequence
+    p.hist = hist;
+    PTO_CUDA(cudaMemsetAsync(hist, 0, li_hist_bytes(b * s1), stream));
+  }
   p.fp16_chain = (flags & PTO_LI_FP16_CHAIN) != 0 ? 1 : 0;
   p.bf16 = (flags & kLiFlagBf16) != 0 ? 1 : 0;
   PTO_REQUIRE(!p.fp16_chain || scale_dtype == PTO_DT_F16, "PTO_LI_FP16_CHAIN needs fp16 scales and weights");
@@ -240,8 +247,12 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
   return PTO_OK;
 }
 
+// Whether the score stage of this call leaves a histogram for the top-k stage: tensor-core kernel, one launch
+// that takes every query token of a sequence.
+bool li_hist_usable(int s1, int flags) { return (flags & PTO_LI_SCORE_SIMT) == 0 && s1 <= pto::kLiHistMaxS1; }
+
 int run_li_topk(const float* scores, int64_t row_stride, const int32_t* act, int32_t* out, int b, int s1, int k,
-                int flags, int32_t* status, cudaStream_t stream) {
+                int flags, int32_t* status, cudaStream_t stream, const unsigned int* hist = nullptr) {
   PTO_REQUIRE(k >= 1 && k <= pto::topk_max_k(), "selected_count %d outside [1, %d]", k, pto::topk_max_k());
   PTO_REQUIRE(row_stride % 4 == 0 && aligned16(scores), "score rows must be 16-byte aligned");
   pto::TopkParams p{};
@@ -253,6 +264,7 @@ int run_li_topk(const float* scores, int64_t row_stride, const int32_t* act, int
   p.s1 = s1;
   p.k = k;
   p.flags = flags;
+  p.hist = hist;
   p.status = status;
   DeviceInfo di;
   const int rc = get_device_info(&di);
@@ -471,7 +483,7 @@ int pto_workspace_reset(void* workspace, pto_stream_t stream) {
 
 size_t pto_li_workspace_bytes(int t, int max_blocks, int block_size) {
   if (t < 1 || max_blocks < 1 || block_size < 1) return 0;
-  return kStatusBytes + li_scores_bytes(t, max_blocks, block_size);
+  return kStatusBytes + li_scores_bytes(t, max_blocks, block_size) + li_hist_bytes(t);
 }
 
 int pto_li_scores(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
@@ -513,11 +525,16 @@ int pto_li_decode(const int8_t* idx_query, const void* idx_query_scale, const in
   if (rc != PTO_OK) return rc;
   int32_t* status = reinterpret_cast<int32_t*>(workspace);
   float* scores = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kStatusBytes);
+  unsigned int* hist = nullptr;  // behind the score rows
+  if (li_hist_usable(s1, flags)) {
+    hist = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(workspace) + kStatusBytes +
+                                           li_scores_bytes(b * s1, max_blocks, block_size));
+  }
   rc = run_li_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, scale_dtype, act_seq_key,
-                     block_table, scores, nullptr, b, s1, block_num, max_blocks, flags, status, stream);
+                     block_table, scores, nullptr, b, s1, block_num, max_blocks, flags, status, stream, hist);
   if (rc != PTO_OK) return rc;
   return run_li_topk(scores, static_cast<int64_t>(max_blocks) * block_size, act_seq_key, topk_res, b, s1,
-                     selected_count, flags, status, stream);
+                     selected_count, flags, status, stream, hist);
 }
 
 int pto_li_scores_bf16(const void* idx_query, const void* idx_key_cache, const void* idx_weight,
@@ -547,12 +564,17 @@ int pto_li_decode_bf16(const void* idx_query, const void* idx_key_cache, const v
   if (rc != PTO_OK) return rc;
   int32_t* status = reinterpret_cast<int32_t*>(workspace);
   float* scores = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kStatusBytes);
+  unsigned int* hist = nullptr;  // behind the score rows
+  if (li_hist_usable(s1, flags)) {
+    hist = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(workspace) + kStatusBytes +
+                                           li_scores_bytes(b * s1, max_blocks, block_size));
+  }
   rc = run_li_scores(reinterpret_cast<const int8_t*>(idx_query), nullptr, reinterpret_cast<const int8_t*>(idx_key_cache),
                      nullptr, idx_weight, PTO_DT_F16, act_seq_key, block_table, scores, nullptr, b, s1, block_num,
-                     max_blocks, kLiFlagBf16, status, stream);
+                     max_blocks, kLiFlagBf16, status, stream, hist);
   if (rc != PTO_OK) return rc;
   return run_li_topk(scores, static_cast<int64_t>(max_blocks) * block_size, act_seq_key, topk_res, b, s1,
-                     selected_count, flags, status, stream);
+                     selected_count, flags, status, stream, hist);
 }
 
 int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
@@ -570,7 +592,8 @@ int pto_li_decode_static(const int8_t* idx_query, const void* idx_query_scale, c
     PTO_REQUIRE(cap == cudaStreamCaptureStatusNone,
                 "status_out must be NULL while the stream is being captured (read the words with pto_li_static_status)");
   }
-  const size_t need = pto_li_workspace_bytes(b * s1, max_blocks, block_size);
+  // status words and score rows; this entry keeps no histogram (the selection scans the row for its own)
+  const size_t need = (b < 1 || s1 < 1) ? 0 : kStatusBytes + li_scores_bytes(b * s1, max_blocks, block_size);
   if (need == 0 || need > PTO_LI_STATIC_SCRATCH_BYTES) {
     return fail(PTO_ERR_WORKSPACE,
                 "%d tokens x %d keys need %zu bytes of scratch, the static array holds %u: use pto_li_decode with "
@@ -808,7 +831,7 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
 
 size_t pto_decode_workspace_bytes(int t, int max_blocks, int block_size, int nq) {
   if (t < 1 || max_blocks < 1 || block_size < 1 || nq < 1) return 0;
-  return kStatusBytes + li_scores_bytes(t, max_blocks, block_size) + sfa_part_bytes(t, nq);
+  return kStatusBytes + li_scores_bytes(t, max_blocks, block_size) + sfa_part_bytes(t, nq) + li_hist_bytes(t);
 }
 
 int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const int8_t* idx_key_cache,
@@ -828,11 +851,13 @@ int pto_decode_fused(const int8_t* idx_query, const void* idx_query_scale, const
   int32_t* status = reinterpret_cast<int32_t*>(base);
   float* scores = reinterpret_cast<float*>(base + kStatusBytes);
   uint8_t* part = base + kStatusBytes + li_scores_bytes(b * s1, max_blocks, 128);
+  unsigned int* hist =  // behind the attention partials
+      li_hist_usable(s1, flags) ? reinterpret_cast<unsigned int*>(part + sfa_part_bytes(b * s1, nq)) : nullptr;
   rc = run_li_scores(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, scale_dtype, act_seq,
-                     block_table, scores, nullptr, b, s1, block_num, max_blocks, flags, status, stream);
+                     block_table, scores, nullptr, b, s1, block_num, max_blocks, flags, status, stream, hist);
   if (rc != PTO_OK) return rc;
   rc = run_li_topk(scores, static_cast<int64_t>(max_blocks) * 128, act_seq, topk_res, b, s1, selected_count, flags,
-                   status, stream);
+                   status, stream, hist);
   if (rc != PTO_OK) return rc;
   return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, k_nope_scales, 0, topk_res, block_table, act_seq,
                  attention_out, b, s1, nq, 1, softmax_scale, selected_count, 128, static_cast<int64_t>(block_num) * 128,
@@ -855,12 +880,14 @@ int pto_decode_fused_bf16(const void* idx_query, const void* idx_key_cache, cons
   int32_t* status = reinterpret_cast<int32_t*>(base);
   float* scores = reinterpret_cast<float*>(base + kStatusBytes);
   uint8_t* part = base + kStatusBytes + li_scores_bytes(b * s1, max_blocks, 128);
+  unsigned int* hist =  // behind the attention partials
+      li_hist_usable(s1, flags) ? reinterpret_cast<unsigned int*>(part + sfa_part_bytes(b * s1, nq)) : nullptr;
   rc = run_li_scores(reinterpret_cast<const int8_t*>(idx_query), nullptr, reinterpret_cast<const int8_t*>(idx_key_cache),
                      nullptr, idx_weight, PTO_DT_F16, act_seq, block_table, scores, nullptr, b, s1, block_num, max_blocks,
-                     kLiFlagBf16, status, stream);
+                     kLiFlagBf16, status, stream, hist);
   if (rc != PTO_OK) return rc;
   rc = run_li_topk(scores, static_cast<int64_t>(max_blocks) * 128, act_seq, topk_res, b, s1, selected_count, flags,
-                   status, stream);
+                   status, stream, hist);
   if (rc != PTO_OK) return rc;
   return run_sfa(query_nope, query_rope, key_nope_2d, key_rope_2d, nullptr, kSfaSplitBf16, topk_res, block_table,
                  act_seq, attention_out, b, s1, nq, 1, softmax_scale, selected_count, 128,

@@ -285,8 +285,19 @@ struct LiParams {
   int s1_total;    // query tokens per sequence in memory (>= s1)
   int tok_offset;  // first token of each sequence handled by this launch
   int groups;      // token groups of s1 tokens taken by one launch (grid y; tensor-core kernel), >= 1
+  // optional, tensor-core kernel with s1 <= 2 per launch: per query token a histogram [t, kLiHistBins] (zeroed by the
+  // caller) of the scores at positions below the token's causal end, binned by the top 12 bits of the
+  // order-preserving image of the float; the top-k kernel starts from it instead of scanning the row for one
+  unsigned int* hist;
   int32_t* status;
 };
+constexpr int kLiHistBins = 4096;
+constexpr int kLiHistShift = 20;  // bin = order(score) >> 20: sign, exponent, three mantissa bits
+constexpr int kLiHistMaxS1 = 2;   // tokens per launch the score kernel keeps a shared-memory histogram for
+__device__ __forceinline__ unsigned int li_float_order(float f) {
+  const unsigned int u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
 
 struct TopkParams {
   const float* scores;
@@ -294,6 +305,7 @@ struct TopkParams {
   const int32_t* act_seq;
   int32_t* out;  // [t, k]
   int b, s1, k, flags;
+  const unsigned int* hist;  // optional [t, kLiHistBins] from the score kernel (see LiParams::hist)
   int32_t* status;
 };
 

@@ -64,7 +64,9 @@ struct LiCtl {
   __align__(16) float ws[kMaxS1 * kHeads];
 };
 
+constexpr size_t kLiHistSmemBytes = static_cast<size_t>(kLiHistMaxS1) * kLiHistBins * sizeof(unsigned int) + 16;  // 32 KB (+ alignment of its start)
 constexpr size_t kLiSmemBytes = 1024 /*alignment slack*/ + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken + sizeof(LiCtl);
+static_assert(kLiSmemBytes + kLiHistSmemBytes <= 227 * 1024, "score kernel shared memory");
 
 __device__ __forceinline__ float load_scale(const void* base, int dtype, int64_t i) {
   if (dtype == PTO_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
@@ -149,6 +151,10 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   const uint32_t stage_base = base;
   const uint32_t q_base = base + kLiSlots * kStageBytes;
   LiCtl* ctl = reinterpret_cast<LiCtl*>(smem + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken);
+  // per-CTA histogram of the current sequence's scores (present only when the launch asked for it)
+  unsigned int* hist_sm = reinterpret_cast<unsigned int*>(smem + kLiSlots * kStageBytes + kMaxS1 * kQBytesPerToken +
+                                                          ((sizeof(LiCtl) + 15) & ~size_t(15)));
+  const bool with_hist = p.hist != nullptr;
 
   constexpr bool kChain = kMode == kLiChain;
   constexpr bool kBf16 = kMode == kLiBf16;
@@ -175,6 +181,9 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     fence_proxy_async();
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_q);
+  }
+  if (with_hist) {
+    for (int j = tid; j < s1 * kLiHistBins; j += kLiThreads) hist_sm[j] = 0u;
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -227,6 +236,17 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   }
   uint32_t n_item = 0;
   uint32_t seg = 0;
+  int64_t prev_tok0 = 0;
+  // adds this CTA's counts of the tokens tok_first .. tok_first + s1 - 1 into the global histogram and clears them
+  auto flush_hist = [&](int64_t tok_first) {
+    for (int j = tid; j < s1 * kLiHistBins; j += kLiThreads) {
+      const unsigned int c = hist_sm[j];
+      if (c != 0u) {
+        atomicAdd(p.hist + tok_first * kLiHistBins + j, c);
+        hist_sm[j] = 0u;
+      }
+    }
+  };
 
   while (cur < it1) {
     while (ctl->prefix[bi + 1] <= cur) ++bi;
@@ -238,6 +258,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + static_cast<int>(blockIdx.y) * p.s1;
 
     __syncthreads();  // previous segment fully drained: Q tile and ws may be overwritten
+    if (with_hist && seg > 0) flush_hist(prev_tok0);  // (the barrier below orders it before the next segment's counts)
+    prev_tok0 = tok0;
     const bool aborted = ctl->abort != 0;
     if (!aborted) {
       if (warp == 0 && lane == 0) {
@@ -408,6 +430,16 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
               if (i < s1) p.scores[(tok0 + i) * p.row_stride + pos] = res[i];
             }
           }
+          if (with_hist) {
+            // counts for the top-k kernel: positions below the token's causal end
+#pragma unroll
+            for (int i = 0; i < kLiHistMaxS1; ++i) {
+              if (i < s1) {
+                const int eff = seq_len - (p.s1_total - 1 - (p.tok_offset + static_cast<int>(blockIdx.y) * p.s1 + i));
+                if (pos < eff) atomicAdd(&hist_sm[i * kLiHistBins + (li_float_order(res[i]) >> kLiHistShift)], 1u);
+              }
+            }
+          }
         }
       }
     }
@@ -419,6 +451,7 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   // teardown
   tc_fence_before();
   __syncthreads();
+  if (with_hist && seg > 0) flush_hist(prev_tok0);
   if (ctl->abort) {
     // give copies still in flight time to land before the CTA's shared memory is released
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -516,8 +549,10 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
                                cudaStream_t stream) {
   auto kernel = p.bf16 ? li_score_tc_kernel<kLiBf16>
                        : (p.fp16_chain ? li_score_tc_kernel<kLiChain> : li_score_tc_kernel<kLiQuant>);
+  if (p.hist != nullptr && p.s1 > kLiHistMaxS1) return cudaErrorInvalidValue;
+  const size_t smem_bytes = kLiSmemBytes + (p.hist != nullptr ? kLiHistSmemBytes : 0);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kLiSmemBytes));
+                                       static_cast<int>(kLiSmemBytes + kLiHistSmemBytes));
   if (e != cudaSuccess) return e;
   // a launch that takes several token groups gives each group its share of the SMs: every CTA then walks more
   // pages and the fixed cost of a launch (about 8 us) is paid once for all of them
@@ -528,7 +563,7 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
   if (gx < 1) gx = 1;
   const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(groups), 1);
   count_launch();
-  kernel<<<grid, kLiThreads, kLiSmemBytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
+  kernel<<<grid, kLiThreads, smem_bytes, stream>>>(*reinterpret_cast<const CUtensorMap*>(tmap_k),
                                                                  *reinterpret_cast<const CUtensorMap*>(tmap_q), p);
   return cudaGetLastError();
 }

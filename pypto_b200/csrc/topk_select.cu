@@ -19,6 +19,10 @@
 //   4. candidates sorted (bitonic) and the best `need` appended; if the threshold bucket does not
 //      fit the buffer (massive ties), an MSB-first radix select over the 64-bit keys runs on the row
 //   5. the k selected keys are sorted (bitonic) and the positions written.
+// When the score kernel has left a histogram of the row (4096 bins over the top 12 bits of the order-preserving
+// image of the float, counted over the positions below the row's causal end), passes 1 and 2 are skipped: the
+// threshold bin comes from that histogram and pass 3 is the only scan of the row. The histogram is used only if
+// its total equals the row's length and its threshold bin fits the candidate buffer; otherwise passes 1-2 run.
 #include "common.cuh"
 
 namespace pto {
@@ -27,14 +31,16 @@ namespace {
 
 constexpr int kTopkThreads = 1024;
 constexpr int kBins = 2048;
+constexpr int kHistSlots = kLiHistBins > kBins ? kLiHistBins : kBins;
 constexpr int kMaxK = 2048;
 constexpr int kCandCap = 4096;
 
 struct TopkSmem {
   unsigned long long sel[kMaxK];
   unsigned long long cand[kCandCap];
-  unsigned int hist[kBins];
+  unsigned int hist[kHistSlots];
   unsigned int warp_tot[32];
+  unsigned int hist_total;
   float red_min[32];
   float red_max[32];
   unsigned int n_sel;
@@ -175,15 +181,21 @@ __device__ void bitonic_sort_desc(unsigned long long* buf, int n) {
   __syncthreads();
 }
 
-// Finds, scanning the histogram from the top bin down, the bin where the running count reaches
-// `need`. Results in sm->thr_bin (bin), thr_above (count in bins above it), thr_count (its count).
+// Finds, scanning the histogram of kPer * 1024 bins from the top bin down, the bin where the running count reaches
+// `need`. Results in sm->thr_bin (bin), thr_above (count in bins above it), thr_count (its count), hist_total.
+template <int kPer>
 __device__ void find_threshold_bin(TopkSmem* sm, unsigned int need) {
+  constexpr int kN = kPer * kTopkThreads;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-  // thread t owns bins (kBins-1-2t) and (kBins-2-2t): a descending walk is a prefix scan over t
-  const unsigned int c0 = sm->hist[kBins - 1 - 2 * tid];
-  const unsigned int c1 = sm->hist[kBins - 2 - 2 * tid];
-  const unsigned int s = c0 + c1;
+  // thread t owns bins kN-1-kPer*t down to kN-kPer-kPer*t: a descending walk is a prefix scan over t
+  unsigned int c[kPer];
+  unsigned int s = 0;
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) {
+    c[e] = sm->hist[kN - 1 - kPer * tid - e];
+    s += c[e];
+  }
   unsigned int incl = s;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -201,17 +213,18 @@ __device__ void find_threshold_bin(TopkSmem* sm, unsigned int need) {
       if (lane >= o) wi += n;
     }
     sm->warp_tot[lane] = wi - w;  // exclusive
+    if (lane == 31) sm->hist_total = wi;
   }
   __syncthreads();
-  const unsigned int excl = sm->warp_tot[warp] + incl - s;
-  if (excl < need && need <= excl + c0) {
-    sm->thr_bin = kBins - 1 - 2 * tid;
-    sm->thr_above = excl;
-    sm->thr_count = c0;
-  } else if (excl + c0 < need && need <= excl + s) {
-    sm->thr_bin = kBins - 2 - 2 * tid;
-    sm->thr_above = excl + c0;
-    sm->thr_count = c1;
+  unsigned int run = sm->warp_tot[warp] + incl - s;  // count in the bins above this thread's first
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) {
+    if (run < need && need <= run + c[e]) {
+      sm->thr_bin = kN - 1 - kPer * tid - e;
+      sm->thr_above = run;
+      sm->thr_count = c[e];
+    }
+    run += c[e];
   }
   __syncthreads();
 }
@@ -288,81 +301,102 @@ li_topk_kernel(TopkParams p) {
   const int begin = min(eff, static_cast<int>(rank) * chunk);
   const int end = min(eff, begin + chunk);
 
-  // ---- 1. row min / max -------------------------------------------------------------------
-  float vmin = INFINITY, vmax = -INFINITY;
-  for_each_element(row, begin, end, [&](float v, int) {
-    vmin = fminf(vmin, v);
-    vmax = fmaxf(vmax, v);
-  });
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
-    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-  }
-  if (lane == 0) {
-    sm->red_min[warp] = vmin;
-    sm->red_max[warp] = vmax;
-  }
-  for (int j = tid; j < kBins; j += kTopkThreads) sm->hist[j] = 0;
-  if (tid == 0) {
-    sm->n_sel = 0;
-    sm->n_cand = 0;
-  }
-  __syncthreads();
-  vmin = sm->red_min[lane];
-  vmax = sm->red_max[lane];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
-    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-  }
-  if (csize > 1) {
-    if (tid < csize) {  // thread r tells rank r
-      st_peer_u32(peer_addr(&sm->all_min[rank], tid), __float_as_uint(vmin));
-      st_peer_u32(peer_addr(&sm->all_max[rank], tid), __float_as_uint(vmax));
+  // ---- 0. the score kernel's histogram of the row, when there is one ------------------------------
+  bool coarse = false;
+  float vmin = 0.f, inv = 0.f;
+  if (p.hist != nullptr) {
+    const uint4* h4 = reinterpret_cast<const uint4*>(p.hist + static_cast<int64_t>(row_id) * kLiHistBins);
+    static_assert(kLiHistBins == 4 * kTopkThreads, "one 16-byte load per thread");
+    reinterpret_cast<uint4*>(sm->hist)[tid] = __ldg(h4 + tid);
+    if (tid == 0) {
+      sm->n_sel = 0;
+      sm->n_cand = 0;
     }
-    cluster_barrier();
-    for (unsigned int r = 0; r < csize; ++r) {  // every rank arrives at the same pair
-      vmin = fminf(vmin, sm->all_min[r]);
-      vmax = fmaxf(vmax, sm->all_max[r]);
-    }
-  }
-  // monotone bucket map: floor((v - vmin) * inv), clamped. Non-finite range -> everything in bin 0
-  // and the radix fallback resolves it.
-  float inv = 0.f;
-  {
-    const float range = vmax - vmin;
-    if (range > 0.f && range < INFINITY) inv = static_cast<float>(kBins - 1) / range;
-    if (!(inv < INFINITY)) inv = 0.f;
+    __syncthreads();
+    find_threshold_bin<kLiHistBins / kTopkThreads>(sm, static_cast<unsigned int>(k));
+    // usable if it counted exactly this row's positions and its threshold bin fits the candidate buffer; the
+    // same answer in every rank of the cluster (all read the same histogram)
+    coarse = sm->hist_total == static_cast<unsigned int>(eff) && sm->thr_count <= static_cast<unsigned int>(kCandCap);
+    __syncthreads();  // every thread has read the outcome before the histogram area is reused
   }
   auto bucket = [&](float v) -> int {
+    if (coarse) return static_cast<int>(float_order(v) >> kLiHistShift);
     const float x = (v - vmin) * inv;
     int bkt = static_cast<int>(x);
     bkt = max(0, min(kBins - 1, bkt));
     return bkt;
   };
-
-  // ---- 2. histogram -----------------------------------------------------------------------
-  for_each_element(row, begin, end, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
-  __syncthreads();
-  if (csize > 1) {
-    // every rank adds its counts into every other rank's histogram; a rank must not receive additions
-    // before its own pass is over (they would be indistinguishable from its own counts only after it)
-    unsigned int mine[kBins / kTopkThreads];
+  if (!coarse) {
+    // ---- 1. row min / max -------------------------------------------------------------------
+    vmin = INFINITY;
+    float vmax = -INFINITY;
+    for_each_element(row, begin, end, [&](float v, int) {
+      vmin = fminf(vmin, v);
+      vmax = fmaxf(vmax, v);
+    });
 #pragma unroll
-    for (int u = 0; u < kBins / kTopkThreads; ++u) mine[u] = sm->hist[tid + u * kTopkThreads];
-    cluster_barrier();  // all local histograms complete and read into registers
+    for (int o = 16; o > 0; o >>= 1) {
+      vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    }
+    if (lane == 0) {
+      sm->red_min[warp] = vmin;
+      sm->red_max[warp] = vmax;
+    }
+    for (int j = tid; j < kBins; j += kTopkThreads) sm->hist[j] = 0;
+    if (tid == 0) {
+      sm->n_sel = 0;
+      sm->n_cand = 0;
+    }
+    __syncthreads();
+    vmin = sm->red_min[lane];
+    vmax = sm->red_max[lane];
 #pragma unroll
-    for (int u = 0; u < kBins / kTopkThreads; ++u) {
-      if (mine[u] != 0) {
-        for (unsigned int r = 0; r < csize; ++r) {
-          if (r != rank) red_peer_add_u32(peer_addr(&sm->hist[tid + u * kTopkThreads], r), mine[u]);
-        }
+    for (int o = 16; o > 0; o >>= 1) {
+      vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+      vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    }
+    if (csize > 1) {
+      if (tid < csize) {  // thread r tells rank r
+        st_peer_u32(peer_addr(&sm->all_min[rank], tid), __float_as_uint(vmin));
+        st_peer_u32(peer_addr(&sm->all_max[rank], tid), __float_as_uint(vmax));
+      }
+      cluster_barrier();
+      for (unsigned int r = 0; r < csize; ++r) {  // every rank arrives at the same pair
+        vmin = fminf(vmin, sm->all_min[r]);
+        vmax = fmaxf(vmax, sm->all_max[r]);
       }
     }
-    cluster_barrier();  // every rank holds the row's histogram
+    // monotone bucket map: floor((v - vmin) * inv), clamped. Non-finite range -> everything in bin 0
+    // and the radix fallback resolves it.
+    {
+      const float range = vmax - vmin;
+      if (range > 0.f && range < INFINITY) inv = static_cast<float>(kBins - 1) / range;
+      if (!(inv < INFINITY)) inv = 0.f;
+    }
+
+    // ---- 2. histogram -----------------------------------------------------------------------
+    for_each_element(row, begin, end, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
+    __syncthreads();
+    if (csize > 1) {
+      // every rank adds its counts into every other rank's histogram; a rank must not receive additions
+      // before its own pass is over (they would be indistinguishable from its own counts only after it)
+      unsigned int mine[kBins / kTopkThreads];
+#pragma unroll
+      for (int u = 0; u < kBins / kTopkThreads; ++u) mine[u] = sm->hist[tid + u * kTopkThreads];
+      cluster_barrier();  // all local histograms complete and read into registers
+#pragma unroll
+      for (int u = 0; u < kBins / kTopkThreads; ++u) {
+        if (mine[u] != 0) {
+          for (unsigned int r = 0; r < csize; ++r) {
+            if (r != rank) red_peer_add_u32(peer_addr(&sm->hist[tid + u * kTopkThreads], r), mine[u]);
+          }
+        }
+      }
+      cluster_barrier();  // every rank holds the row's histogram
+    }
+    find_threshold_bin<kBins / kTopkThreads>(sm, static_cast<unsigned int>(k));  // the same answer in every rank
   }
-  find_threshold_bin(sm, static_cast<unsigned int>(k));  // the same answer in every rank
   const int thr_bin = sm->thr_bin;
   const unsigned int above = sm->thr_above;
   const unsigned int thr_count = sm->thr_count;
@@ -447,7 +481,7 @@ li_topk_kernel(TopkParams p) {
         atomicAdd(&sm->hist[static_cast<unsigned int>(key >> new_shift) & ((1u << w) - 1u)], 1u);
       });
       __syncthreads();
-      find_threshold_bin(sm, remaining);
+      find_threshold_bin<kBins / kTopkThreads>(sm, remaining);
       remaining -= sm->thr_above;
       exact = (sm->thr_count == remaining);
       prefix = (prefix << w) | static_cast<unsigned long long>(sm->thr_bin);

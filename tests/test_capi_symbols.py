@@ -44,12 +44,14 @@ def test_host_only_calls(lib):
     assert lib.pto_abi_version() == 1
     assert lib.pto_strerror(0) == b"ok"
     assert lib.pto_strerror(-2).startswith(b"workspace")
-    assert lib.pto_li_workspace_bytes(8, 256, 128) == 256 + 8 * 256 * 128 * 4
+    # status words, fp32 score rows, one 4096-bin histogram row per query token
+    assert lib.pto_li_workspace_bytes(8, 256, 128) == 256 + 8 * 256 * 128 * 4 + 8 * 4096 * 4
     assert lib.pto_li_workspace_bytes(0, 256, 128) == 0
     # 64 tokens x 2 head blocks fill the device: unsplit, status words only
     assert lib.pto_sfa_workspace_bytes(80, 128) == 256
     assert lib.pto_sfa_workspace_bytes(2, 128) > 2 * 16 * 128 * 512 * 4
-    assert lib.pto_decode_workspace_bytes(64, 512, 128, 128) == 256 + 64 * 512 * 128 * 4 + lib.pto_sfa_workspace_bytes(64, 128) - 256
+    assert lib.pto_decode_workspace_bytes(64, 512, 128, 128) == (256 + 64 * 512 * 128 * 4 + lib.pto_sfa_workspace_bytes(64, 128)
+                                                                 - 256 + 64 * 4096 * 4)
 
 
 def test_argument_errors_are_reported_before_any_cuda_call(lib):
