@@ -57,6 +57,13 @@ typedef struct CUstream_st* pto_stream_t; /* cudaStream_t */
                                * (framework/src/operator/models/deepseek_v3.2_exp/lightning_indexer.cpp:150-196):
                                * fp16(dot * 2^-11), x q_scale, x k_scale, relu, x weight all in fp16, head sum in
                                * fp32; scales and weights must be fp16 */
+#define PTO_LI_EPILOGUE_HIST 0x8 /* decode / fused entries with at most two query tokens per sequence: the score
+                               * kernel also leaves a 4096-bin histogram of every row (top 12 bits of the
+                               * order-preserving image of the score) and the selection starts from it instead
+                               * of scanning the row for min/max and its own histogram. Same results. Measured
+                               * 1.3 us slower per step on the benchmark configuration (the scans it saves read
+                               * L2-resident rows; the histogram costs a memset, shared-memory atomics in the score
+                               * epilogue and a flush), so it is off unless asked for. */
 
 /* device status area at the start of every workspace */
 #define PTO_STATUS_WORDS 8

@@ -11,7 +11,7 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "libpypto_b200.so"
 
 PTO_DT_F16, PTO_DT_F32 = 0, 1
-PTO_LI_SCORE_SIMT, PTO_LI_UNSORTED, PTO_LI_FP16_CHAIN = 0x1, 0x2, 0x4
+PTO_LI_SCORE_SIMT, PTO_LI_UNSORTED, PTO_LI_FP16_CHAIN, PTO_LI_EPILOGUE_HIST = 0x1, 0x2, 0x4, 0x8
 PTO_STATUS_WORDS = 8
 PTO_LI_STATIC_SCRATCH_BYTES = (8 << 20) + 256
 PTO_ST_BAD_PAGE, PTO_ST_WAIT_EXPIRED = 0x1, 0x2

@@ -5,6 +5,7 @@
 #include <dlfcn.h>
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <atomic>
 #include <cstring>
@@ -249,7 +250,9 @@ int run_li_scores(const int8_t* q, const void* qs, const int8_t* kc, const void*
 
 // Whether the score stage of this call leaves a histogram for the top-k stage: tensor-core kernel, one launch
 // that takes every query token of a sequence.
-bool li_hist_usable(int s1, int flags) { return (flags & PTO_LI_SCORE_SIMT) == 0 && s1 <= pto::kLiHistMaxS1; }
+bool li_hist_usable(int s1, int flags) {
+  return (flags & PTO_LI_EPILOGUE_HIST) != 0 && (flags & PTO_LI_SCORE_SIMT) == 0 && s1 <= pto::kLiHistMaxS1;
+}
 
 int run_li_topk(const float* scores, int64_t row_stride, const int32_t* act, int32_t* out, int b, int s1, int k,
                 int flags, int32_t* status, cudaStream_t stream, const unsigned int* hist = nullptr) {

@@ -192,6 +192,11 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
 
   tc_fence_before();
   __syncthreads();
+  if (ctl->abort) {
+    // give copies still in flight time to land before the CTA's shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 128);

@@ -410,33 +410,57 @@ sfa_mma_kernel(SfaParams p) {
 }
 
 // Merge of the split partials: O = sum_i O_i 2^(m_i - m) / sum_i l_i 2^(m_i - m), rounded once to bf16.
+// One CTA per (token, head). The splits' maxima and sums are fetched by one lane each and reduced by shuffles,
+// the output rows of up to eight splits are requested together: two trips to memory instead of one per split.
+constexpr int kMaxSplit = 32;
 __global__ void __launch_bounds__(128)
 sfa_combine_kernel(SfaParams p) {
+  __shared__ float wgt[kMaxSplit];
+  __shared__ float inv_l;
+  pdl_wait();  // launched with programmatic serialization behind the kernel that writes the partials
   const int64_t th = blockIdx.x;  // token * nq + head
   const int ti = static_cast<int>(th / p.nq);
   const int head = static_cast<int>(th % p.nq);
   const int tid = threadIdx.x;
-  float m = -INFINITY;
-  for (int sp = 0; sp < p.n_split; ++sp) {
-    m = fmaxf(m, p.part_ml[((static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + head) * 2]);
+  const int64_t prow0 = static_cast<int64_t>(ti) * p.n_split * p.nq + head;  // row of split 0; splits are nq rows apart
+  if (tid < 32) {
+    float mi = -INFINITY, li = 0.f;
+    if (tid < p.n_split) {
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (prow0 + static_cast<int64_t>(tid) * p.nq) * 2);
+      mi = ml.x;
+      li = ml.y;
+    }
+    float m = mi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float w = (li > 0.f && m != -INFINITY) ? ex2(mi - m) : 0.f;
+    float l = li * w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    wgt[tid] = w;
+    if (tid == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
   }
+  __syncthreads();
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  float l = 0.f;
-  if (m != -INFINITY) {
-    for (int sp = 0; sp < p.n_split; ++sp) {
-      const int64_t prow = (static_cast<int64_t>(ti) * p.n_split + sp) * p.nq + head;
-      const float li = p.part_ml[prow * 2 + 1];
-      if (li <= 0.f) continue;
-      const float w = ex2(p.part_ml[prow * 2] - m);
-      l += li * w;
-      const float4 v = *reinterpret_cast<const float4*>(p.part_o + prow * kDV + tid * 4);
-      acc.x += v.x * w;
-      acc.y += v.y * w;
-      acc.z += v.z * w;
-      acc.w += v.w * w;
+  for (int s0 = 0; s0 < p.n_split; s0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int sp = s0 + u;
+      v[u] = (sp < p.n_split && wgt[sp] != 0.f)
+                 ? *reinterpret_cast<const float4*>(p.part_o + (prow0 + static_cast<int64_t>(sp) * p.nq) * kDV + tid * 4)
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float w = s0 + u < p.n_split ? wgt[s0 + u] : 0.f;
+      acc.x += v[u].x * w;
+      acc.y += v[u].y * w;
+      acc.z += v[u].z * w;
+      acc.w += v[u].w * w;
     }
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const float inv = inv_l;
   __nv_bfloat16* dst = p.out + (static_cast<int64_t>(ti) * p.nq_total + p.head_begin + head) * kDV + tid * 4;
   uint2 pk;
   pk.x = pack_bf16x2(acc.x * inv, acc.y * inv);
@@ -468,9 +492,10 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
   }
   if (e != cudaSuccess) return e;
   if (p.n_split > 1) {
+    if (p.n_split > kMaxSplit) return cudaErrorInvalidValue;
     count_launch();
-    sfa_combine_kernel<<<t * p.nq, 128, 0, stream>>>(p);
-    e = cudaGetLastError();
+    // may be scheduled while the attention kernel drains; its first instruction waits for that grid
+    e = launch_maybe_pdl(sfa_combine_kernel, dim3(static_cast<unsigned>(t * p.nq)), dim3(128), 0, stream, true, p);
   }
   return e;
 }

@@ -91,11 +91,6 @@ __device__ __forceinline__ uint32_t pair_ctarank() {
 __device__ __forceinline__ void pair_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ uint32_t pair_map(uint32_t local_smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
-  return r;
-}
 // Notice from CTA 1 to CTA 0: a tcgen05.commit of no outstanding operation arrives at once on the mbarrier at this
 // offset in CTA 0 (mask 1). It travels on the tensor pipe's own path: measured one way 390 cycles, as fast as an
 // asynchronous remote store, but unlike that store it does not queue behind the SM's gathers in the load/store
@@ -213,6 +208,9 @@ __device__ __forceinline__ uint32_t pair_setup_sync(PairCtl* ctl) {
   __syncthreads();
   pair_cluster_sync();
   tc_fence_after();
+  // the kernel behind this one (the merge of the split partials) may be scheduled from here on; it waits for
+  // this grid to complete before it reads anything
+  if (threadIdx.x == 0) pdl_trigger();
   if (threadIdx.x == 0) TLP(1, 20);  // roles start
   return ctl->tmem_base;
 }

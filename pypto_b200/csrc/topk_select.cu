@@ -29,6 +29,15 @@ namespace pto {
 
 namespace {
 
+// -DPTO_TOPK_TIMELINE: clock64 stamps of thread 0 of CTA 0 at the phase boundaries (development aid, read back
+// through pto_debug_topk_timeline; not part of the ABI)
+#ifdef PTO_TOPK_TIMELINE
+__device__ long long g_topk_tl[16];
+#define TKT(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_topk_tl[i] = clock64(); } while (0)
+#else
+#define TKT(i) do { } while (0)
+#endif
+
 constexpr int kTopkThreads = 1024;
 constexpr int kBins = 2048;
 constexpr int kHistSlots = kLiHistBins > kBins ? kLiHistBins : kBins;
@@ -45,6 +54,7 @@ struct TopkSmem {
   float red_max[32];
   unsigned int n_sel;
   unsigned int n_cand;
+  unsigned int n_sel2, n_cand2;  // second radix step over the candidates of a coarse bin
   // values every rank of the cluster publishes into every other rank's copy (remote stores, made visible
   // by the next cluster barrier), so that nobody waits for a chain of remote loads
   float all_min[8], all_max[8];
@@ -263,8 +273,10 @@ li_topk_kernel(TopkParams p) {
   extern __shared__ __align__(16) uint8_t topk_smem_raw[];
   TopkSmem* sm = reinterpret_cast<TopkSmem*>(topk_smem_raw);
   // launched with programmatic serialization: the score kernel before it may still be running
+  TKT(0);
   pdl_wait();
   pdl_trigger();
+  TKT(1);
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const unsigned int csize = cluster_size();
@@ -326,6 +338,7 @@ li_topk_kernel(TopkParams p) {
     bkt = max(0, min(kBins - 1, bkt));
     return bkt;
   };
+  TKT(2);
   if (!coarse) {
     // ---- 1. row min / max -------------------------------------------------------------------
     vmin = INFINITY;
@@ -375,6 +388,7 @@ li_topk_kernel(TopkParams p) {
       if (!(inv < INFINITY)) inv = 0.f;
     }
 
+    TKT(3);
     // ---- 2. histogram -----------------------------------------------------------------------
     for_each_element(row, begin, end, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
     __syncthreads();
@@ -395,8 +409,10 @@ li_topk_kernel(TopkParams p) {
       }
       cluster_barrier();  // every rank holds the row's histogram
     }
+    TKT(4);
     find_threshold_bin<kBins / kTopkThreads>(sm, static_cast<unsigned int>(k));  // the same answer in every rank
   }
+  TKT(5);
   const int thr_bin = sm->thr_bin;
   const unsigned int above = sm->thr_above;
   const unsigned int thr_count = sm->thr_count;
@@ -413,6 +429,7 @@ li_topk_kernel(TopkParams p) {
       }
     });
     __syncthreads();
+    TKT(6);
     if (csize > 1) {
       if (tid < csize) {
         st_peer_u32(peer_addr(&sm->all_sel[rank], tid), sm->n_sel);
@@ -442,18 +459,64 @@ li_topk_kernel(TopkParams p) {
       if (rank != 0) return;
       __syncthreads();
     }
+    TKT(7);
     // ---- 4. best `need` of the candidates (rank 0) --------------------------------------------
-    if (need != thr_count) {
-      int cpow2 = 1;
-      while (cpow2 < static_cast<int>(thr_count)) cpow2 <<= 1;
-      for (int j = thr_count + tid; j < cpow2; j += kTopkThreads) sm->cand[j] = 0ull;
-      bitonic_sort_desc(sm->cand, cpow2);
+    // a chosen key goes to its place among the selected ones: straight to the output when every rank wrote its own
+    // part there (unordered, cluster), else behind the `above` keys already in `sel`
+    const bool direct = unsorted && csize > 1;
+    auto emit = [&](unsigned int j, unsigned long long key) {
+      if (direct) out[above + j] = key_pos(key); else sm->sel[above + j] = key;
+    };
+    bool refined = false;
+    if (coarse && need != thr_count && thr_count > 256u) {
+      // The candidates of a coarse bin share the top 12 bits of their value word and are many (the bin is wide):
+      // one more radix step inside shared memory instead of sorting them all. Digit: the next 11 bits of the value.
+      constexpr int kFineShift = 32 + kLiHistShift - 11;
+      for (int j = tid; j < kBins; j += kTopkThreads) sm->hist[j] = 0;
+      if (tid == 0) {
+        sm->n_sel2 = 0;
+        sm->n_cand2 = 0;
+      }
+      __syncthreads();
+      for (unsigned int j = tid; j < thr_count; j += kTopkThreads) {
+        atomicAdd(&sm->hist[static_cast<unsigned int>(sm->cand[j] >> kFineShift) & (kBins - 1)], 1u);
+      }
+      __syncthreads();
+      find_threshold_bin<kBins / kTopkThreads>(sm, need);
+      const unsigned int fine_bin = static_cast<unsigned int>(sm->thr_bin), fine_above = sm->thr_above, fine_count = sm->thr_count;
+      __syncthreads();  // the histogram area becomes the list of the keys in the fine threshold bin
+      unsigned long long* tmp = reinterpret_cast<unsigned long long*>(sm->hist);
+      constexpr unsigned int kTmpCap = kHistSlots * sizeof(unsigned int) / sizeof(unsigned long long);
+      if (fine_count <= kTmpCap) {
+        for (unsigned int j = tid; j < thr_count; j += kTopkThreads) {
+          const unsigned long long key = sm->cand[j];
+          const unsigned int f = static_cast<unsigned int>(key >> kFineShift) & (kBins - 1);
+          if (f > fine_bin) emit(atomicAdd(&sm->n_sel2, 1u), key);
+          else if (f == fine_bin) tmp[atomicAdd(&sm->n_cand2, 1u)] = key;
+        }
+        __syncthreads();
+        const unsigned int need2 = need - fine_above;
+        if (need2 != fine_count) {
+          int cpow2 = 2;
+          while (cpow2 < static_cast<int>(fine_count)) cpow2 <<= 1;
+          for (int j = fine_count + tid; j < cpow2; j += kTopkThreads) tmp[j] = 0ull;
+          bitonic_sort_desc(tmp, cpow2);
+        }
+        for (unsigned int j = tid; j < need2; j += kTopkThreads) emit(fine_above + j, tmp[j]);
+        refined = true;
+      }
     }
-    if (unsorted && csize > 1) {
-      for (unsigned int j = tid; j < need; j += kTopkThreads) out[above + j] = key_pos(sm->cand[j]);
-      return;
+    if (!refined) {
+      if (need != thr_count) {
+        int cpow2 = 1;
+        while (cpow2 < static_cast<int>(thr_count)) cpow2 <<= 1;
+        for (int j = thr_count + tid; j < cpow2; j += kTopkThreads) sm->cand[j] = 0ull;
+        bitonic_sort_desc(sm->cand, cpow2);
+      }
+      for (unsigned int j = tid; j < need; j += kTopkThreads) emit(j, sm->cand[j]);
     }
-    for (unsigned int j = tid; j < need; j += kTopkThreads) sm->sel[above + j] = sm->cand[j];
+    TKT(8);
+    if (direct) return;
     __syncthreads();
   } else {
     // ---- 4'. massive ties: MSB-first radix select on the 64-bit keys of the threshold bucket ----
@@ -542,5 +605,11 @@ cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream
 }
 
 int topk_max_k() { return kMaxK; }
+
+#ifdef PTO_TOPK_TIMELINE
+extern "C" int pto_debug_topk_timeline(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_topk_tl, sizeof(long long) * n));
+}
+#endif
 
 }  // namespace pto

@@ -173,12 +173,13 @@ def lightning_indexer_topk_nonquant(idx_query, idx_key_cache, idx_weight, act_se
 
 def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, act_seq_key,
                              block_table, topk_res, unroll_list=None, configs=None, selected_count=2048, *,
-                             sort=True, _simt_scores=False, fp16_chain=False):
+                             sort=True, _simt_scores=False, fp16_chain=False, histogram=False):
     """Top-`selected_count` key positions per query token (value-descending, -1 padded).
     `fp16_chain=True` (not in the reference's Python signature) scores with the older formulation of
     LightningIndexerTopkImpl, lightning_indexer.cpp:150-196 (fp16 scales and weights only).
     A bfloat16 `idx_query` selects the non-quantised formulation (`lightning_indexer_topk_nonquant`; the two scale
-    arguments must then be None)."""
+    arguments must then be None). `histogram=True` (s1 <= 2): the score kernel leaves a histogram of every row for
+    the selection to start from (same results; measured slightly slower, hence off by default)."""
     if unwrap(idx_query, "idx_query").dtype == torch.bfloat16:
         _need(idx_query_scale is None and idx_key_scale is None, "bfloat16 idx_query: the scale tensors must be None")
         _need(not (_simt_scores or fp16_chain), "bfloat16 idx_query: one formulation, tensor cores only")
@@ -195,6 +196,7 @@ def lightning_indexer_decode(idx_query, idx_query_scale, idx_key_cache, idx_key_
     nbytes = lib.pto_li_workspace_bytes(m["t"], m["max_blocks"], m["block_size"])
     flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_SCORE_SIMT if _simt_scores else 0)
     flags |= _lib.PTO_LI_FP16_CHAIN if fp16_chain else 0
+    flags |= _lib.PTO_LI_EPILOGUE_HIST if histogram else 0
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         _lib.check(lib.pto_li_decode(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),
@@ -529,7 +531,7 @@ def pack_kv_cache(key_nope_2d, key_rope_2d, k_nope_scales, nope_cache):
 def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, idx_key_scale, idx_weight, query_nope,
                                    query_rope, key_nope_2d, key_rope_2d, k_nope_scales, act_seq, block_table,
                                    topk_res, attention_out, nq=128, softmax_scale=576 ** -0.5, selected_count=2048, *,
-                                   sort=False, fp16_chain=False):
+                                   sort=False, fp16_chain=False, histogram=False):
     """Fused chain: indexer score -> top-k -> sparse attention with the kernel's own indices.
     Both caches share `block_table` / `act_seq`. Writes `topk_res` and `attention_out`."""
     dev, (q, qs, kc, ks, w, act, bt), m = _li_args(idx_query, idx_query_scale, idx_key_cache, idx_key_scale,
@@ -550,6 +552,7 @@ def decode_indexer_attention_quant(idx_query, idx_query_scale, idx_key_cache, id
     lib = _lib.load()
     nbytes = lib.pto_decode_workspace_bytes(t, m["max_blocks"], 128, int(nq))
     flags = (0 if sort else _lib.PTO_LI_UNSORTED) | (_lib.PTO_LI_FP16_CHAIN if fp16_chain else 0)
+    flags |= _lib.PTO_LI_EPILOGUE_HIST if histogram else 0
     with torch.cuda.device(dev):
         ws = _workspace(dev, nbytes)
         _lib.check(lib.pto_decode_fused(q.data_ptr(), qs.data_ptr(), kc.data_ptr(), ks.data_ptr(), w.data_ptr(),

@@ -10,16 +10,25 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _fused(d, sort=False, fill=0):
+def _fused(d, sort=False, fill=0, **kw):
     g = d.to(DEV)
     idx = torch.full((d.t, 1, 2048), fill, dtype=torch.int32, device=DEV)
     out = torch.full((d.b, d.s1, 128, 512), float(fill), dtype=torch.bfloat16, device=DEV)
     pto.decode_indexer_attention_quant(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
                                        g.query_nope, g.query_rope, g.key_nope_2d, g.key_rope_2d, g.k_nope_scales,
-                                       g.act_seq_key, g.block_table, idx, out, sort=sort)
+                                       g.act_seq_key, g.block_table, idx, out, sort=sort, **kw)
     torch.cuda.synchronize()
     assert pto.workspace_status()[0] == 0
     return idx.cpu(), out.cpu()
+
+
+def test_fused_chain_with_the_score_kernels_histogram_gives_the_same_result():
+    """`histogram=True`: the selection starts from the histogram the score kernel leaves (behind the attention
+    partials in the workspace); ordered indices and outputs are those of the default call, bit for bit."""
+    d = gen.make_inputs([4096, 9000, 300, 2047, 2048, 2049, 15, 30000], s1=2, seed=77)
+    idx, out = _fused(d, sort=True)
+    idx_h, out_h = _fused(d, sort=True, histogram=True)
+    assert torch.equal(idx_h, idx) and torch.equal(out_h, out)
 
 
 @pytest.mark.parametrize("s1,act", [(1, [4096, 9000, 300, 2047, 2048, 2049, 15]), (2, [6000, 1, 2500, 130])])

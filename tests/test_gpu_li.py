@@ -242,8 +242,9 @@ def test_prefill_chunk_groups_share_a_launch():
 
 @pytest.mark.parametrize("s1", [1, 2, 3])
 def test_chained_selection_from_the_score_kernels_histogram_equals_the_two_stages(s1):
-    """With at most two query tokens per sequence the score kernel leaves a 4096-bin histogram per row and the
-    selection starts from it (one scan of the row); with three it scans the row for min/max and its own histogram.
+    """Asked to (`histogram=True`), with at most two query tokens per sequence, the score kernel leaves a 4096-bin
+    histogram per row and the selection starts from it (one scan of the row, a radix step over the candidates in
+    shared memory); with three tokens it scans the row for min/max and its own histogram as it does by default.
     Either way the ordered result must equal the selection run alone over the same score rows. Cases: ragged
     lengths, sequences whose causal end cuts a page, a row shorter than k, and rows whose scores all tie (zero
     weights: one bin holds the whole row, which sends the selection back to its own passes and the radix path)."""
@@ -251,7 +252,8 @@ def test_chained_selection_from_the_score_kernels_histogram_equals_the_two_stage
     act = torch.randint(2049, 30000, (6,), generator=g0).tolist() + [2048 + s1, 300, 9000, 4097]
     d = gen.make_inputs(act, s1=s1, seed=91 + s1, with_attention=False)
     d.idx_weight[8 * s1:9 * s1] = 0  # sequence 8: every score is +0
-    got = _decode(d)
+    got = _decode(d, histogram=True)
+    assert torch.equal(got, _decode(d))
     g = d.to(DEV)
     sc = torch.zeros((d.t, d.max_blocks * 128), dtype=torch.float32, device=DEV)
     pto.lightning_indexer_scores(g.idx_query, g.idx_query_scale, g.idx_key_cache, g.idx_key_scale, g.idx_weight,
@@ -264,6 +266,6 @@ def test_chained_selection_from_the_score_kernels_histogram_equals_the_two_stage
     for i in range(s1):
         assert got[8 * s1 + i, 0].tolist() == list(range(2048))
     # unordered output: the same sets
-    got_u = _decode(d, sort=False)
+    got_u = _decode(d, sort=False, histogram=True)
     for ti in range(d.t):
         assert set(got_u[ti, 0].tolist()) == set(got[ti, 0].tolist())
