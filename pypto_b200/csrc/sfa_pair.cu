@@ -215,22 +215,39 @@ __device__ __forceinline__ uint32_t pair_setup_sync(PairCtl* ctl) {
   return ctl->tmem_base;
 }
 
-// ================================ MMA issuer (CTA 0) ============================================
-// One thread, an event loop over four actions, each as soon as both CTAs' operands for it are in place:
+// ================================ MMA issuers (CTA 0) ===========================================
+// Two threads on two different schedulers: warp 0 issues the score products, warp 2 the value products.
 //   q.K^T first half  (chunks 0-3: 16 MMAs)  needs K half 0 of the tile and the score buffer it overwrites read
 //   q.K^T second half (chunks 4-8: 20 MMAs)  needs K half 1; completes the tile's scores
 //   P.V first half    (keys 0-63:   8 MMAs)  needs P of the tile and V key half 0
 //   P.V second half   (keys 64-127: 8 MMAs)  needs V key half 1; completes the tile's P.V
 // After each action a commit hands the half it read back to its producers, so that the refill for the next tile
-// runs behind the MMAs that read the other half. An operation in progress is finished before another starts.
-__device__ __forceinline__ void pair_role_mma(const SfaParams& p, PairCtx c) {
+// runs behind the MMAs that read the other half. One thread issuing everything (an event loop over the four
+// actions) was what a tile waited for: 36 + 16 MMAs kept it busy for 8.7 k cycles per tile; side by side the two
+// threads take 3.2-4.0 k and 1.5-2.7 k (80.1 -> 77.7 us on 64 tokens x 2048 rows). The products of the two threads
+// are independent (different accumulators), every dependency between them goes through the mbarriers, and a
+// commit covers the MMAs of the thread that executes it.
+// (No cluster-scope fence before the MMAs: measured, `fence.acq_rel.cluster` holds a thread for 2000-3700 cycles
+// per use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive on their
+// own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA issued here
+// after the notice reads CTA 1's shared memory from CTA 1's side.)
+__device__ __forceinline__ bool pair_poll(uint32_t bar, uint32_t parity) {  // one thread, bounded
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    __nanosleep(20);
+    if (mbar_test_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+}
+
+__device__ __forceinline__ void pair_role_issue_qk(const SfaParams& p, PairCtx c) {
   PairCtl* ctl = c.ctl;
   const int ntiles = c.ntiles;
   c.tmem_base = pair_setup_sync(ctl);
   if ((threadIdx.x & 31) == 0) {
     const uint32_t idesc_qk = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 0, 128, kPT);
-    const uint32_t idesc_pv = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 1, 128, 256);
-    const uint32_t q_base = c.base + kSmemQ, k_base = c.base + kSmemK, v_base = c.base + kSmemV, p_base = c.base + kSmemP;
+    const uint32_t q_base = c.base + kSmemQ, k_base = c.base + kSmemK;
     auto issue_qk_chunks = [&](int j, int ch0, int ch1) {
       const uint32_t d = c.tmem_base + kPairColS + 64 * (j & 1);
 #pragma unroll 1
@@ -241,10 +258,46 @@ __device__ __forceinline__ void pair_role_mma(const SfaParams& p, PairCtx c) {
         for (int k = 0; k < 4; ++k) mma2_f16_ss(d, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, (ch | k) != 0 ? 1u : 0u);
       }
     };
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const uint32_t ph = j & 1;
+      ok = pair_poll(smem_u32(&ctl->kfull[0]), ph) && pair_poll(smem_u32(&ctl->kpeer[0]), ph);
+      if (ok && j >= 2) {  // the score buffer it overwrites has been read in both CTAs
+        const uint32_t sp = ((j - 2) >> 1) & 1;
+        ok = pair_poll(smem_u32(&ctl->sread[j & 1]), sp) && pair_poll(smem_u32(&ctl->speer[j & 1]), sp);
+      }
+      if (!ok) break;
+      tc_fence_after();
+      TLP(6, j);
+      issue_qk_chunks(j, 0, 4);
+      tc2_commit(smem_u32(&ctl->kfree[0]));
+      ok = pair_poll(smem_u32(&ctl->kfull[1]), ph) && pair_poll(smem_u32(&ctl->kpeer[1]), ph);
+      if (!ok) break;
+      tc_fence_after();
+      issue_qk_chunks(j, 4, kQChunks);
+      tc2_commit(smem_u32(&ctl->kfree[1]));
+      tc2_commit(smem_u32(&ctl->sfull[j & 1]));
+      TLP(7, j);
+    }
+    if (!ok) {
+      ctl->abort = 1;
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 50);
+    }
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void pair_role_issue_pv(const SfaParams& p, PairCtx c) {
+  PairCtl* ctl = c.ctl;
+  const int ntiles = c.ntiles;
+  c.tmem_base = pair_setup_sync(ctl);
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t idesc_pv = umma_idesc(kCFmtF32, kABFmtBF16, kABFmtBF16, 0, 1, 128, 256);
+    const uint32_t v_base = c.base + kSmemV, p_base = c.base + kSmemP;
     auto issue_pv_half = [&](int j, int kh) {  // keys 64 kh .. +63 into both pairs of value columns
       const uint64_t a_desc = umma_desc_kmajor_sw128(p_base + kh * kChunk);
 #pragma unroll 1
-      for (int dp = 0; dp < 2; ++dp) {  // value columns: 128 per CTA and MMA, two chunks of 64
+      for (int dp = 0; dp < 2; ++dp) {
         const uint64_t b_desc = desc_mnmajor_sw128(v_base + kh * kVHalfBytes + dp * 2 * kChunk, kChunk, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -253,73 +306,27 @@ __device__ __forceinline__ void pair_role_mma(const SfaParams& p, PairCtx c) {
         }
       }
     };
-    auto done = [&](uint64_t* bar, uint32_t parity) -> bool { return mbar_test_wait(smem_u32(bar), parity); };
     bool ok = true;
-    int qk_i = 0, qk_h = 0, pv_i = 0, pv_h = 0;  // next tile and half of each operation
-    long long t_last = clock64();
-#ifdef PTO_PAIR_TIMELINE
-    int seen_s = 0, seen_p = 0;
-#endif
-    // (No cluster-scope fence before the MMAs: measured, `fence.acq_rel.cluster` holds this thread for 2000-3700
-    // cycles per use. The order is kept by the chain itself: CTA 1's writers fence for the async proxy and arrive
-    // on their own barrier, its forwarding thread observes that barrier before it sends the notice, and the MMA
-    // issued here after the notice reads CTA 1's shared memory from CTA 1's side.)
-    while (pv_i < ntiles) {
-      bool progressed = false;
-#ifdef PTO_PAIR_TIMELINE
-      if (seen_s < qk_i && done(&ctl->sfull[seen_s & 1], (seen_s >> 1) & 1)) { TLP(2, seen_s); ++seen_s; }  // q.K^T complete
-      if (seen_p < ntiles && seen_p <= pv_i && done(&ctl->ppeer, seen_p & 1)) { TLP(15, seen_p); ++seen_p; }
-#endif
-      const uint32_t qph = qk_i & 1, pph = pv_i & 1;
-      if (qk_i < ntiles && qk_h == 1 && done(&ctl->kfull[1], qph) && done(&ctl->kpeer[1], qph)) {
-        tc_fence_after();
-        issue_qk_chunks(qk_i, 4, kQChunks);
-        tc2_commit(smem_u32(&ctl->kfree[1]));
-        tc2_commit(smem_u32(&ctl->sfull[qk_i & 1]));
-        TLP(7, qk_i);
-        qk_h = 0;
-        ++qk_i;
-        progressed = true;
-      } else if (pv_h == 1 && done(&ctl->vfull[1], pph) && done(&ctl->vpeer[1], pph)) {
-        tc_fence_after();
-        issue_pv_half(pv_i, 1);
-        tc2_commit(smem_u32(&ctl->vfree[1]));
-        tc2_commit(smem_u32(&ctl->pvdone));
-        TLP(9, pv_i);
-        pv_h = 0;
-        ++pv_i;
-        progressed = true;
-      } else if (pv_h == 0 && pv_i < qk_i && done(&ctl->pfull, pph) && done(&ctl->ppeer, pph) &&
-                 done(&ctl->vfull[0], pph) && done(&ctl->vpeer[0], pph)) {
-        tc_fence_after();
-        TLP(8, pv_i);
-        issue_pv_half(pv_i, 0);
-        tc2_commit(smem_u32(&ctl->vfree[0]));
-        pv_h = 1;
-        progressed = true;
-      } else if (qk_i < ntiles && qk_h == 0 && done(&ctl->kfull[0], qph) && done(&ctl->kpeer[0], qph) &&
-                 (qk_i < 2 || (done(&ctl->sread[qk_i & 1], ((qk_i - 2) >> 1) & 1) &&
-                               done(&ctl->speer[qk_i & 1], ((qk_i - 2) >> 1) & 1)))) {
-        tc_fence_after();
-        TLP(6, qk_i);
-        issue_qk_chunks(qk_i, 0, 4);
-        tc2_commit(smem_u32(&ctl->kfree[0]));
-        qk_h = 1;
-        progressed = true;
-      }
-      if (progressed) {
-        t_last = clock64();
-      } else {
-        __nanosleep(20);
-        if (clock64() - t_last > kWaitBudgetCycles) {
-          ok = false;
-          break;
-        }
-      }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const uint32_t ph = j & 1;
+      ok = pair_poll(smem_u32(&ctl->pfull), ph) && pair_poll(smem_u32(&ctl->ppeer), ph) &&
+           pair_poll(smem_u32(&ctl->vfull[0]), ph) && pair_poll(smem_u32(&ctl->vpeer[0]), ph);
+      if (!ok) break;
+      tc_fence_after();
+      TLP(8, j);
+      issue_pv_half(j, 0);
+      tc2_commit(smem_u32(&ctl->vfree[0]));
+      ok = pair_poll(smem_u32(&ctl->vfull[1]), ph) && pair_poll(smem_u32(&ctl->vpeer[1]), ph);
+      if (!ok) break;
+      tc_fence_after();
+      issue_pv_half(j, 1);
+      tc2_commit(smem_u32(&ctl->vfree[1]));
+      tc2_commit(smem_u32(&ctl->pvdone));
+      TLP(9, j);
     }
     if (!ok) {
       ctl->abort = 1;
-      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 50);
+      set_status(p.status, PTO_ST_WAIT_EXPIRED, blockIdx.x, 55);
     }
   }
   __syncwarp();
@@ -630,6 +637,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   uint32_t nwait = 0;
   RowRegs ra;
   pdl_wait();          // the selected indices come from the kernel before this one, which may still be running
+  if (ptid == 0) TLP(3, 21);
   int row_n;           // this lane's row of tile j+1
   int idx_a, entry_a;  // tile j+2
   int idx_b;           // tile j+3
@@ -637,13 +645,17 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
     const int idx0 = load_idx(0), idx1 = load_idx(1);
     idx_a = load_idx(2);
     idx_b = load_idx(3);
+    if (ptid == 0 && idx0 + idx1 + idx_a + idx_b != -12345) TLP(4, 21);
     const int e0 = tc_table_entry(p, bi, idx0);
     const int e1 = tc_table_entry(p, bi, idx1);
     entry_a = tc_table_entry(p, bi, idx_a);
+    if (ptid == 0 && e0 + e1 + entry_a != -12345) TLP(5, 21);
     issue_loads(ra, pair_row(p, idx0, e0));
     row_n = pair_row(p, idx1, e1);
     prefetch_row(row_n);
+    if (ptid == 0) TLP(6, 21);
   }
+  if (ptid == 0 && ra.d[0][0].x != 0x7fffffffu) TLP(7, 21);  // first rows arrived
   pair_setup_sync(ctl);
   for (int j = 0; j < ntiles && ok; ++j) {
 #pragma unroll
@@ -851,12 +863,14 @@ sfa_pair_kernel(const __grid_constant__ SfaParams p) {
     }
     ctl->abort = 0;
     fence_mbar_init();
+    TLP(0, 21);
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                  "r"(kPairTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    if (tid == 0) TLP(1, 21);
   }
   // this CTA's 64 query rows into shared memory, nine swizzled chunks of 64 dims (A operand of q.K^T): 64 x 72
   // 16-byte units, twelve per thread of the twelve warps that are not producers, all loads in flight before the
@@ -879,13 +893,15 @@ sfa_pair_kernel(const __grid_constant__ SfaParams p) {
       sts_v4u(base + kSmemQ + (u >> 3) * kChunk + r * 128 + (((u & 7) ^ (r & 7)) << 4), w[i]);
     }
     fence_proxy_async();
+    if (tid == 0) TLP(2, 21);
   }
   static_assert(12 * 32 * kPairKWarp0 == 64 * 72, "Q units per loader thread");
 
 #define PAIR_SETREG(x) asm volatile(x)
   if (warp < kPairSoftmaxWarp0) {
     PAIR_SETREG("setmaxnreg.dec.sync.aligned.u32 24;");
-    if (warp == 0 && crank == 0) pair_role_mma(p, c);
+    if (warp == 0 && crank == 0) pair_role_issue_qk(p, c);
+    else if (warp == 2 && crank == 0) pair_role_issue_pv(p, c);
     else if (warp == 1 && crank == 1) pair_role_relay(p, c);
     else pair_setup_sync(ctl);
   } else if (warp < kPairKWarp0) {
