@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
   }
 }
 
-// Warp-wide form (all 32 lanes call it, converged): every lane polls and the verdict is made uniform.
+// Warp-wide form (all 32 lanes call it, converged): every lane polls and the outcome is made uniform.
 // Polling from one lane while the others wait at a shuffle was measured slower (the divergent
 // section costs more than the 31 extra probes).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {

@@ -512,45 +512,74 @@ __device__ __forceinline__ void pair_role_softmax(const SfaParams& p, PairCtx c)
     const int b = ntiles & 1;
     l_tot = (ctl->mt[b][0][head] + ctl->mt[b][1][head]) + (ctl->mt[b][2][head] + ctl->mt[b][3][head]);
   }
-  if (ok) {
-    tc_fence_after();
-    const int head_g = 64 * static_cast<int>(c.crank) + head;  // head of the token
-    const int dv0 = 256 * kh + 128 * ch;                         // this thread's 128 output values
-    if (p.n_split == 1) {
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      __nv_bfloat16* dst = p.out + (c.q_row0 + head_g) * 512 + dv0;
+  // The rows go out through shared memory: a thread holds 128 values of ONE row, so direct stores put every lane of
+  // a warp on its own 128-byte line (4096 lines per CTA, about 4 k cycles); staged, a warp writes 512 contiguous
+  // bytes. Staging area: the K chunks (all q.K^T of this cluster are complete once the last P.V is), rows of
+  // 1 KB + 16 B (the pad keeps the lanes of a warp, which write different rows, on different banks); a row holds
+  // the 256-byte pieces of the head's four threads. bf16 rows take one pass, fp32 partial rows two.
+  {
+    const uint32_t stage = c.base + kSmemK;
+    constexpr uint32_t kStageRow = 1024 + 16;
+    static_assert(64 * kStageRow <= kQChunks * kChunk, "output staging exceeds the K chunks");
+    const int stid = threadIdx.x - 32 * kPairSoftmaxWarp0;       // 0..255
+    const uint32_t my_piece = stage + head * kStageRow + slot * 256;
+    const bool direct = p.n_split == 1;
+    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+    const int npass = direct ? 1 : 2;
+    if (ok) tc_fence_after();
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(lane_addr + kPairColO + ch * 128 + cc * 32, o);
-        tc_wait_ld();
+    for (int ps = 0; ps < npass; ++ps) {
+      if (ok) {
+#pragma unroll 1
+        for (int cc = 0; cc < (direct ? 4 : 2); ++cc) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_addr + kPairColO + ch * 128 + (direct ? cc : 2 * ps + cc) * 32, o);
+          tc_wait_ld();
+          if (direct) {  // 32 values -> 64 bytes
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-          w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-          w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-          w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = w;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              sts_v4u(my_piece + cc * 64 + i * 2, w);
+            }
+          } else {       // 32 values -> 128 bytes
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) sts_v4u(my_piece + cc * 128 + i * 4, make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]));
+          }
         }
       }
-    } else {
-      const int64_t prow = (static_cast<int64_t>(c.ti) * p.n_split + c.sp) * p.nq + head_g;
-      float* dst = p.part_o + prow * 512 + dv0;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(lane_addr + kPairColO + ch * 128 + cc * 32, o);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // (every softmax thread reaches it, also after an expired wait)
+      if (ok) {
+        // 64 rows x 64 units of 16 bytes; consecutive threads take consecutive units of a row
+        uint8_t* gbase;
+        int64_t grow_bytes;  // bytes between rows in global memory
+        if (direct) {
+          gbase = reinterpret_cast<uint8_t*>(p.out + (c.q_row0 + 64 * static_cast<int>(c.crank)) * 512);
+          grow_bytes = 1024;
+        } else {
+          const int64_t prow0 = (static_cast<int64_t>(c.ti) * p.n_split + c.sp) * p.nq + 64 * static_cast<int>(c.crank);
+          gbase = reinterpret_cast<uint8_t*>(p.part_o + prow0 * 512);
+          grow_bytes = 2048;
+        }
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int e = it * 256 + stid;
+          const int r = e >> 6, unit = e & 63;        // unit: 16 bytes of the staged row; piece = unit / 16
+          const uint4 w = lds_v4u(stage + r * kStageRow + unit * 16);
+          // bf16: the row's bytes in order. fp32: piece q of pass ps holds floats 128 q + 64 ps .. + 63 of the row
+          const int64_t off = direct ? unit * 16 : ((unit >> 4) * 512 + ps * 256 + (unit & 15) * 16);
+          *reinterpret_cast<uint4*>(gbase + r * grow_bytes + off) = w;
         }
       }
-      if (slot == 0) {
-        p.part_ml[prow * 2] = m_seen;
-        p.part_ml[prow * 2 + 1] = l_tot;
-      }
+      if (ps + 1 < npass) asm volatile("bar.sync 1, 256;" ::: "memory");  // staging area reused by the next pass
+    }
+    if (ok && !direct && slot == 0) {
+      const int64_t prow = (static_cast<int64_t>(c.ti) * p.n_split + c.sp) * p.nq + 64 * static_cast<int>(c.crank) + head;
+      p.part_ml[prow * 2] = m_seen;
+      p.part_ml[prow * 2 + 1] = l_tot;
     }
   }
   if (!ok && lane == 0) {
