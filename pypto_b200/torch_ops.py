@@ -67,6 +67,25 @@ def decode_indexer_attention_quant(idx_query: Tensor, idx_query_scale: Tensor, i
                                        sort=sort, fp16_chain=fp16_chain)
 
 
+@torch.library.custom_op(f"{_NS}::lightning_indexer_topk_nonquant", mutates_args=("topk_res",))
+def lightning_indexer_topk_nonquant(idx_query: Tensor, idx_key_cache: Tensor, idx_weight: Tensor, act_seq_key: Tensor,
+                                    block_table: Tensor, topk_res: Tensor, selected_count: int = 2048,
+                                    sort: bool = True) -> None:
+    ops.lightning_indexer_topk_nonquant(idx_query, idx_key_cache, idx_weight, act_seq_key, block_table, topk_res,
+                                        selected_count, sort=sort)
+
+
+@torch.library.custom_op(f"{_NS}::decode_indexer_attention", mutates_args=("topk_res", "attention_out"))
+def decode_indexer_attention(idx_query: Tensor, idx_key_cache: Tensor, idx_weight: Tensor, query_nope: Tensor,
+                             query_rope: Tensor, key_nope_2d: Tensor, key_rope_2d: Tensor, act_seq: Tensor,
+                             block_table: Tensor, topk_res: Tensor, attention_out: Tensor, nq: int = 128,
+                             softmax_scale: float = 576 ** -0.5, selected_count: int = 2048,
+                             sort: bool = False) -> None:
+    ops.decode_indexer_attention(idx_query, idx_key_cache, idx_weight, query_nope, query_rope, key_nope_2d, key_rope_2d,
+                                 act_seq, block_table, topk_res, attention_out, nq, softmax_scale, selected_count,
+                                 sort=sort)
+
+
 _PROLOG_OUT = ("mla_kv_cache", "mla_kr_cache", "mla_k_scale_cache", "ip_k_cache", "ip_k_cache_scale",
                "mla_query_nope_out", "mla_query_rope_out", "ip_q_int8_out", "ip_q_scale_out", "ip_weights_out")
 
@@ -96,6 +115,7 @@ def _no_result(*args, **kwargs) -> None:
 
 
 OPS = (lightning_indexer_decode, sparse_flash_attention_quant, sparse_attention_antiquant,
-       decode_indexer_attention_quant, mla_indexer_prolog_quant)
+       decode_indexer_attention_quant, lightning_indexer_topk_nonquant, decode_indexer_attention,
+       mla_indexer_prolog_quant)
 for _op in OPS:
     _op.register_fake(_no_result)

@@ -14,6 +14,8 @@ def test_schemas_name_the_buffers_each_op_writes():
         "sparse_flash_attention_quant": {"attention_out"},
         "sparse_attention_antiquant": {"attention_out"},
         "decode_indexer_attention_quant": {"topk_res", "attention_out"},
+        "lightning_indexer_topk_nonquant": {"topk_res"},
+        "decode_indexer_attention": {"topk_res", "attention_out"},
         "mla_indexer_prolog_quant": set(top._PROLOG_OUT),
     }
     for name, written in want.items():
