@@ -299,6 +299,7 @@ def run_stage(args, dev):
         "li_score_chain": lambda: pto.lightning_indexer_scores(*li, sc, fp16_chain=True),  # needs --scale-dtype float16
         "li_decode": lambda: pto.lightning_indexer_decode(*li, idx, None, None, 2048),
         "topk": lambda: pto.lightning_indexer_topk(sc, d.act_seq_key, idx, s1=d.s1),
+        "topk_unsorted": lambda: pto.lightning_indexer_topk(sc, d.act_seq_key, idx, s1=d.s1, sort=False),
         "sfa": lambda: pto.sparse_flash_attention_quant_d(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d,
                                                           d.k_nope_scales, d.topk_indices, d.block_table,
                                                           d.act_seq_key, out, args.nq, 1, SCALE, 2048, 128, d.max_blocks),
@@ -538,7 +539,7 @@ def main():
     ap.add_argument("--partition", default="heads", choices=["heads", "tokens"], help="configuration 4 on N > 1 GPUs")
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
     ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer", "li_score_chain",
-                             "kv_pack", "li_score_nonquant"],
+                             "kv_pack", "li_score_nonquant", "topk_unsorted"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)

@@ -23,6 +23,8 @@
 // image of the float, counted over the positions below the row's causal end), passes 1 and 2 are skipped: the
 // threshold bin comes from that histogram and pass 3 is the only scan of the row. The histogram is used only if
 // its total equals the row's length and its threshold bin fits the candidate buffer; otherwise passes 1-2 run.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace pto {
@@ -585,6 +587,12 @@ cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream
   // ordered output ends in a 2048-key sort on rank 0 that dwarfs the scans of short rows: measured, a
   // cluster only pays there for rows beyond ~40 K positions
   if ((p.flags & PTO_LI_UNSORTED) == 0 && p.row_stride <= 40960) csize = 1;
+  static const int forced = [] {  // PTO_TOPK_CLUSTER=1|2|4|8 in the environment: CTAs per row (A/B timing aid)
+    const char* v = getenv("PTO_TOPK_CLUSTER");
+    const int want = v != nullptr ? atoi(v) : 0;
+    return (want == 1 || want == 2 || want == 4 || want == 8) ? want : 0;
+  }();
+  if (forced != 0) csize = forced;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(rows * csize), 1, 1);
   cfg.blockDim = dim3(kTopkThreads, 1, 1);
