@@ -465,7 +465,7 @@ def measure_e2e_layer(d, dev, steps, barrier):
     def views(arena):
         return {n: arena[off:off + nb].view(dt).reshape(shape) for n, (off, nb, dt, shape) in layout.items()}
 
-    host_arena = torch.empty(total, dtype=torch.uint8).pin_memory()
+    host_arena = gen.pinned_staging(total)  # write-combined: the host writes it, the GPU reads it
     hv = views(host_arena)
     for n, v in step_in.items():
         hv[n].copy_(v.cpu())
@@ -748,7 +748,7 @@ def main():
     def views(arena):
         return {n: arena[off:off + nb].view(dt).reshape(shape) for n, (off, nb, dt, shape) in layout.items()}
 
-    host_arena = torch.empty(total, dtype=torch.uint8).pin_memory()
+    host_arena = gen.pinned_staging(total)  # write-combined: the host writes it, the GPU reads it
     host = views(host_arena)
     for n in host_names:
         host[n].copy_(getattr(d, n).cpu())
@@ -903,8 +903,8 @@ def main():
                                   "launch includes its combine kernel when the rows are split over CTAs"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "h2d_copy_ms": h2d_ms, "ms_per_step": 1e3 * e2e_s / args.steps,
-                    "note": "per-step inputs (queries, scales, weights, lengths, block table) from one pinned host "
-                            "arena in one copy, output copied back, steps double-buffered over H2D/compute/D2H streams; "
+                    "note": "per-step inputs (queries, scales, weights, lengths, block table) from one pinned (write-combined) "
+                            "host arena in one copy, output copied back, steps double-buffered over H2D/compute/D2H streams; "
                             "KV caches are resident device state; h2d_copy_ms = that copy alone (per rank, max over ranks)"},
             "gpu_launches": launches_per_step * args.steps,
             "gpu_launches_per_step": launches_per_step,

