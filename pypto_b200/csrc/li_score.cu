@@ -85,10 +85,11 @@ __device__ __forceinline__ float load_ws(const void* qs, const void* w, int dtyp
 // relu(d) * 2^-11 rounded to fp16, for two dots at once; exact for |d| < 2^21:
 // adding d to the bit pattern of 6144.0f (ulp 2^-11) and subtracting 6144 gives d * 2^-11.
 __device__ __forceinline__ float2 relu_scale_round(int d0, int d1) {
-  const float f0 = __int_as_float(0x45C00000 + d0) - 6144.0f;
-  const float f1 = __int_as_float(0x45C00000 + d1) - 6144.0f;
-  uint32_t packed;  // round to fp16 and clamp negatives to zero in one conversion (f0 in the low half)
-  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(f1), "f"(f0));
+  // the two subtractions as one packed fp32 instruction (each half is an ordinary IEEE subtraction)
+  const float2 f = __fadd2_rn(make_float2(__int_as_float(0x45C00000 + d0), __int_as_float(0x45C00000 + d1)),
+                              make_float2(-6144.0f, -6144.0f));
+  uint32_t packed;  // round to fp16 and clamp negatives to zero in one conversion (f.x in the low half)
+  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(f.y), "f"(f.x));
   return __half22float2(*reinterpret_cast<const __half2*>(&packed));
 }
 
@@ -113,32 +114,31 @@ __device__ __forceinline__ float chain_sum_32(const uint32_t (&v)[32], const flo
 }
 
 __device__ __forceinline__ float weighted_sum_32(const uint32_t (&v)[32], const float* ws) {
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  // four running sums as two packed pairs: one packed FMA per two heads (the same four chains of ordinary FMAs)
+  float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int c = 0; c < 32; c += 4) {
     const float4 w = *reinterpret_cast<const float4*>(ws + c);
     const float2 x = relu_scale_round(static_cast<int>(v[c]), static_cast<int>(v[c + 1]));
     const float2 y = relu_scale_round(static_cast<int>(v[c + 2]), static_cast<int>(v[c + 3]));
-    a0 = fmaf(w.x, x.x, a0);
-    a1 = fmaf(w.y, x.y, a1);
-    a2 = fmaf(w.z, y.x, a2);
-    a3 = fmaf(w.w, y.y, a3);
+    a01 = __ffma2_rn(make_float2(w.x, w.y), x, a01);
+    a23 = __ffma2_rn(make_float2(w.z, w.w), y, a23);
   }
-  return (a0 + a1) + (a2 + a3);
+  return (a01.x + a01.y) + (a23.x + a23.y);
 }
 
 // Non-quantised formulation, 32 heads of one key: the accumulators are fp32 dots.
 __device__ __forceinline__ float weighted_relu_sum_32(const uint32_t (&v)[32], const float* ws) {
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int c = 0; c < 32; c += 4) {
     const float4 w = *reinterpret_cast<const float4*>(ws + c);
-    a0 = fmaf(w.x, fmaxf(__uint_as_float(v[c]), 0.f), a0);
-    a1 = fmaf(w.y, fmaxf(__uint_as_float(v[c + 1]), 0.f), a1);
-    a2 = fmaf(w.z, fmaxf(__uint_as_float(v[c + 2]), 0.f), a2);
-    a3 = fmaf(w.w, fmaxf(__uint_as_float(v[c + 3]), 0.f), a3);
+    a01 = __ffma2_rn(make_float2(w.x, w.y),
+                     make_float2(fmaxf(__uint_as_float(v[c]), 0.f), fmaxf(__uint_as_float(v[c + 1]), 0.f)), a01);
+    a23 = __ffma2_rn(make_float2(w.z, w.w),
+                     make_float2(fmaxf(__uint_as_float(v[c + 2]), 0.f), fmaxf(__uint_as_float(v[c + 3]), 0.f)), a23);
   }
-  return (a0 + a1) + (a2 + a3);
+  return (a01.x + a01.y) + (a23.x + a23.y);
 }
 
 template <int kMode>
