@@ -45,6 +45,7 @@ constexpr int kBins = 2048;
 constexpr int kHistSlots = kLiHistBins > kBins ? kLiHistBins : kBins;
 constexpr int kMaxK = 2048;
 constexpr int kCandCap = 4096;
+constexpr int kRowCap = 32768;  // positions of a rank's share that stay in shared memory between the scans
 
 struct TopkSmem {
   unsigned long long sel[kMaxK];
@@ -64,6 +65,8 @@ struct TopkSmem {
   int thr_bin;
   unsigned int thr_above;
   unsigned int thr_count;
+  // this rank's share of the row, kept from the first scan for the other two (when it fits)
+  __align__(16) float row[kRowCap];
 };
 
 __device__ __forceinline__ unsigned int cluster_rank() {
@@ -244,7 +247,7 @@ __device__ void find_threshold_bin(TopkSmem* sm, unsigned int need) {
 // Applies f(value, position) to every element of row[0, eff). Loads go through the read-only path
 // and are issued four 16-byte loads at a time before the bodies run, so the latency of one batch is
 // paid once (the bodies contain shared-memory atomics the compiler will not move loads across).
-template <typename F>
+template <bool kGlobal, typename F>
 __device__ __forceinline__ void for_each_element(const float* row, int begin, int end, F&& f) {
   const int tid = threadIdx.x;
   const int n4 = begin + ((end - begin) & ~3);  // begin is a multiple of 4
@@ -254,7 +257,7 @@ __device__ __forceinline__ void for_each_element(const float* row, int begin, in
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int j = j0 + u * kStep;
-      if (j < n4) v[u] = __ldg(reinterpret_cast<const float4*>(row + j));
+      if (j < n4) v[u] = kGlobal ? __ldg(reinterpret_cast<const float4*>(row + j)) : *reinterpret_cast<const float4*>(row + j);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -267,7 +270,7 @@ __device__ __forceinline__ void for_each_element(const float* row, int begin, in
       }
     }
   }
-  for (int j = n4 + tid; j < end; j += kTopkThreads) f(__ldg(row + j), j);
+  for (int j = n4 + tid; j < end; j += kTopkThreads) f(kGlobal ? __ldg(row + j) : row[j], j);
 }
 
 __global__ void __launch_bounds__(kTopkThreads, 1)
@@ -340,15 +343,42 @@ li_topk_kernel(TopkParams p) {
     bkt = max(0, min(kBins - 1, bkt));
     return bkt;
   };
+  // the share stays in shared memory between the scans when it fits (not when the first scan is skipped)
+  const bool resident = !coarse && (end - begin) <= kRowCap;
   TKT(2);
   if (!coarse) {
     // ---- 1. row min / max -------------------------------------------------------------------
     vmin = INFINITY;
     float vmax = -INFINITY;
-    for_each_element(row, begin, end, [&](float v, int) {
-      vmin = fminf(vmin, v);
-      vmax = fmaxf(vmax, v);
-    });
+    {
+      // the one scan that reads the row from global memory (L2): this rank's share also goes into shared memory,
+      // where the other two scans read it (three trips to L2 were three of the latencies this kernel consists of)
+      const int n4 = begin + ((end - begin) & ~3);
+      constexpr int kStep = kTopkThreads * 4;
+      for (int j0 = begin + tid * 4; j0 < n4; j0 += 4 * kStep) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * kStep;
+          if (j < n4) v[u] = __ldg(reinterpret_cast<const float4*>(row + j));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * kStep;
+          if (j < n4) {
+            vmin = fminf(fminf(vmin, fminf(v[u].x, v[u].y)), fminf(v[u].z, v[u].w));
+            vmax = fmaxf(fmaxf(vmax, fmaxf(v[u].x, v[u].y)), fmaxf(v[u].z, v[u].w));
+            if (resident) *reinterpret_cast<float4*>(sm->row + (j - begin)) = v[u];
+          }
+        }
+      }
+      for (int j = n4 + tid; j < end; j += kTopkThreads) {
+        const float v = __ldg(row + j);
+        vmin = fminf(vmin, v);
+        vmax = fmaxf(vmax, v);
+        if (resident) sm->row[j - begin] = v;
+      }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
@@ -392,7 +422,11 @@ li_topk_kernel(TopkParams p) {
 
     TKT(3);
     // ---- 2. histogram -----------------------------------------------------------------------
-    for_each_element(row, begin, end, [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); });
+    {
+      auto count = [&](float v, int) { atomicAdd(&sm->hist[bucket(v)], 1u); };
+      if (resident) for_each_element<false>(sm->row - begin, begin, end, count);
+      else for_each_element<true>(row, begin, end, count);
+    }
     __syncthreads();
     if (csize > 1) {
       // every rank adds its counts into every other rank's histogram; a rank must not receive additions
@@ -422,14 +456,18 @@ li_topk_kernel(TopkParams p) {
 
   if (thr_count <= static_cast<unsigned int>(kCandCap)) {
     // ---- 3. collect (this rank's positions) ---------------------------------------------------
-    for_each_element(row, begin, end, [&](float v, int pos) {
-      const int bkt = bucket(v);
-      if (bkt > thr_bin) {
-        sm->sel[atomicAdd(&sm->n_sel, 1u)] = make_key(v, pos);
-      } else if (bkt == thr_bin) {
-        sm->cand[atomicAdd(&sm->n_cand, 1u)] = make_key(v, pos);
-      }
-    });
+    {
+      auto collect = [&](float v, int pos) {
+        const int bkt = bucket(v);
+        if (bkt > thr_bin) {
+          sm->sel[atomicAdd(&sm->n_sel, 1u)] = make_key(v, pos);
+        } else if (bkt == thr_bin) {
+          sm->cand[atomicAdd(&sm->n_cand, 1u)] = make_key(v, pos);
+        }
+      };
+      if (resident) for_each_element<false>(sm->row - begin, begin, end, collect);
+      else for_each_element<true>(row, begin, end, collect);
+    }
     __syncthreads();
     TKT(6);
     if (csize > 1) {
@@ -539,7 +577,7 @@ li_topk_kernel(TopkParams p) {
       const int new_shift = shift - w;
       for (int j = tid; j < kBins; j += kTopkThreads) sm->hist[j] = 0;
       __syncthreads();
-      for_each_element(row, 0, eff, [&](float v, int pos) {
+      for_each_element<true>(row, 0, eff, [&](float v, int pos) {
         if (bucket(v) != thr_bin) return;
         const unsigned long long key = make_key(v, pos);
         if (shift < 64 && (key >> shift) != prefix) return;
@@ -554,7 +592,7 @@ li_topk_kernel(TopkParams p) {
       __syncthreads();
     }
     // every key with (key >> shift) >= prefix inside the bucket, plus all higher buckets
-    for_each_element(row, 0, eff, [&](float v, int pos) {
+    for_each_element<true>(row, 0, eff, [&](float v, int pos) {
       const int bkt = bucket(v);
       if (bkt < thr_bin) return;
       const unsigned long long key = make_key(v, pos);
