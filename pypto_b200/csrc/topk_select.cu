@@ -547,13 +547,27 @@ li_topk_kernel(TopkParams p) {
       }
     }
     if (!refined) {
-      if (need != thr_count) {
-        int cpow2 = 1;
-        while (cpow2 < static_cast<int>(thr_count)) cpow2 <<= 1;
-        for (int j = thr_count + tid; j < cpow2; j += kTopkThreads) sm->cand[j] = 0ull;
-        bitonic_sort_desc(sm->cand, cpow2);
+      if (need != thr_count && thr_count <= 512u) {
+        // few candidates (the usual case: a fine bucket holds a few dozen): every candidate counts the candidates
+        // above it (keys are unique, so the counts are the ranks) and the first `need` ranks go out. All threads
+        // read the same candidate at a time (a broadcast); no barrier inside, where a bitonic sort of 1024 threads
+        // spends its time.
+        __syncthreads();
+        if (static_cast<unsigned int>(tid) < thr_count) {
+          const unsigned long long mine = sm->cand[tid];
+          unsigned int rank_of = 0;
+          for (unsigned int j = 0; j < thr_count; ++j) rank_of += sm->cand[j] > mine ? 1u : 0u;
+          if (rank_of < need) emit(rank_of, mine);
+        }
+      } else {
+        if (need != thr_count) {
+          int cpow2 = 1;
+          while (cpow2 < static_cast<int>(thr_count)) cpow2 <<= 1;
+          for (int j = thr_count + tid; j < cpow2; j += kTopkThreads) sm->cand[j] = 0ull;
+          bitonic_sort_desc(sm->cand, cpow2);
+        }
+        for (unsigned int j = tid; j < need; j += kTopkThreads) emit(j, sm->cand[j]);
       }
-      for (unsigned int j = tid; j < need; j += kTopkThreads) emit(j, sm->cand[j]);
     }
     TKT(8);
     if (direct) return;
