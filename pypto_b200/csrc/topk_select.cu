@@ -279,9 +279,6 @@ li_topk_kernel(TopkParams p) {
   TopkSmem* sm = reinterpret_cast<TopkSmem*>(topk_smem_raw);
   // launched with programmatic serialization: the score kernel before it may still be running
   TKT(0);
-  pdl_wait();
-  pdl_trigger();
-  TKT(1);
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const unsigned int csize = cluster_size();
@@ -292,9 +289,14 @@ li_topk_kernel(TopkParams p) {
   const int k = p.k;
   int32_t* out = p.out + static_cast<int64_t>(row_id) * k;
   const float* row = p.scores + static_cast<int64_t>(row_id) * p.row_stride;
+  // the row's length is an input of the call, not a result of the score kernel: its trip to memory runs while
+  // this grid still waits for that kernel
   int eff = p.act_seq[bi] - (p.s1 - 1 - i);
   if (eff > p.row_stride) eff = static_cast<int>(p.row_stride);
   const bool unsorted = (p.flags & PTO_LI_UNSORTED) != 0;
+  pdl_wait();
+  pdl_trigger();
+  TKT(1);
 
   // short rows: rank 0 alone, no cluster barrier on this path (every CTA of the cluster takes it)
   if (eff <= k) {
@@ -470,7 +472,40 @@ li_topk_kernel(TopkParams p) {
     }
     __syncthreads();
     TKT(6);
-    if (csize > 1) {
+    unsigned int direct_base = above;  // first output slot of the keys chosen among the candidates (direct mode)
+    if (csize == 2 && unsorted) {
+      // Two ranks, unordered output: ONE cluster barrier. Rank 1 writes its selected positions from the END of
+      // the output row and pushes its candidates to the END of rank 0's candidate buffer (neither needs rank 0's
+      // counts), with its count; after the barrier rank 0 moves them behind its own and fills the slots between
+      // its selected positions and rank 1's with the chosen candidates.
+      const unsigned int my_sel = sm->n_sel, my_cand = sm->n_cand;
+      if (rank == 1) {
+        for (unsigned int j = tid; j < my_sel; j += kTopkThreads) out[k - 1 - static_cast<int>(j)] = key_pos(sm->sel[j]);
+        for (unsigned int j = tid; j < my_cand; j += kTopkThreads) st_peer_u64(peer_addr(&sm->cand[kCandCap - 1 - j], 0), sm->cand[j]);
+        if (tid == 0) st_peer_u32(peer_addr(&sm->all_cand[1], 0), my_cand);
+      } else {
+        for (unsigned int j = tid; j < my_sel; j += kTopkThreads) out[j] = key_pos(sm->sel[j]);
+      }
+      cluster_barrier();  // rank 0 holds every candidate and rank 1's count
+      if (rank != 0) return;
+      const unsigned int c1 = sm->all_cand[1];
+      // (thr_count = my_cand + c1 <= kCandCap, so the two segments cannot overlap)
+      // (the two regions can overlap when there are many candidates: all reads, a barrier, then the writes)
+      unsigned long long moved[kCandCap / kTopkThreads];
+#pragma unroll
+      for (int u = 0; u < kCandCap / kTopkThreads; ++u) {
+        const unsigned int j = tid + u * kTopkThreads;
+        moved[u] = j < c1 ? sm->cand[kCandCap - 1 - j] : 0ull;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int u = 0; u < kCandCap / kTopkThreads; ++u) {
+        const unsigned int j = tid + u * kTopkThreads;
+        if (j < c1) sm->cand[my_cand + j] = moved[u];
+      }
+      direct_base = my_sel;
+      __syncthreads();
+    } else if (csize > 1) {
       if (tid < csize) {
         st_peer_u32(peer_addr(&sm->all_sel[rank], tid), sm->n_sel);
         st_peer_u32(peer_addr(&sm->all_cand[rank], tid), sm->n_cand);
@@ -505,7 +540,7 @@ li_topk_kernel(TopkParams p) {
     // part there (unordered, cluster), else behind the `above` keys already in `sel`
     const bool direct = unsorted && csize > 1;
     auto emit = [&](unsigned int j, unsigned long long key) {
-      if (direct) out[above + j] = key_pos(key); else sm->sel[above + j] = key;
+      if (direct) out[direct_base + j] = key_pos(key); else sm->sel[above + j] = key;
     };
     bool refined = false;
     if (coarse && need != thr_count && thr_count > 256u) {

@@ -269,3 +269,26 @@ def test_chained_selection_from_the_score_kernels_histogram_equals_the_two_stage
     got_u = _decode(d, sort=False, histogram=True)
     for ti in range(d.t):
         assert set(got_u[ti, 0].tolist()) == set(got[ti, 0].tolist())
+
+
+def test_two_ctas_per_row_with_thousands_of_tied_candidates():
+    """24 rows: two CTAs per row. Unordered output with a single exchange between them: rank 1 writes its selected
+    positions from the end of the row and pushes its candidates to the end of rank 0's buffer. Rows of eight
+    distinct values put ~3700 keys into the threshold bucket, half in each rank, so that the two candidate segments
+    overlap when rank 0 joins them; rows of 300 distinct values are the ordinary case."""
+    g = torch.Generator().manual_seed(11)
+    n, rows = 30000, 24
+    sc = torch.empty((rows, 32768))
+    sc[:12, :n] = torch.randint(0, 8, (12, n), generator=g).float()
+    sc[12:, :n] = torch.randint(0, 300, (12, n), generator=g).float()
+    act = torch.full((rows,), n, dtype=torch.int32)
+    out = torch.zeros((rows, 1, 2048), dtype=torch.int32, device=DEV)
+    pto.lightning_indexer_topk(sc.to(DEV), act.to(DEV), out, s1=1, selected_count=2048, sort=False)
+    torch.cuda.synchronize()
+    assert pto.workspace_status()[0] == 0
+    out = out.cpu()
+    for r in range(rows):
+        key = sc[r, :n].double() * 1e6 - torch.arange(n).double() * 1e-3  # ties toward the smaller position
+        want = set(torch.topk(key, 2048).indices.tolist())
+        got = out[r, 0].tolist()
+        assert len(set(got)) == 2048 and set(got) == want, f"row {r}"
