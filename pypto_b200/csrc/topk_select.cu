@@ -430,7 +430,23 @@ li_topk_kernel(TopkParams p) {
       else for_each_element<true>(row, begin, end, count);
     }
     __syncthreads();
-    if (csize > 1) {
+    if (csize == 2) {
+      // two ranks: each stores its counts into the free upper half of the other's histogram area (plain remote
+      // stores, all bins), one cluster barrier, and adds what it received to its own
+      static_assert(kHistSlots >= 2 * kBins, "no room for the peer's counts");
+#pragma unroll
+      for (int u = 0; u < kBins / kTopkThreads; ++u) {
+        const int bin = tid + u * kTopkThreads;
+        st_peer_u32(peer_addr(&sm->hist[kBins + bin], rank ^ 1u), sm->hist[bin]);
+      }
+      cluster_barrier();
+#pragma unroll
+      for (int u = 0; u < kBins / kTopkThreads; ++u) {
+        const int bin = tid + u * kTopkThreads;
+        sm->hist[bin] += sm->hist[kBins + bin];
+      }
+      __syncthreads();
+    } else if (csize > 1) {
       // every rank adds its counts into every other rank's histogram; a rank must not receive additions
       // before its own pass is over (they would be indistinguishable from its own counts only after it)
       unsigned int mine[kBins / kTopkThreads];
