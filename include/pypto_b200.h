@@ -281,6 +281,34 @@ int pto_mla_indexer_prolog_quant(
     int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
     void* workspace, size_t workspace_bytes, pto_stream_t stream);
 
+/* The two prologs in front of the non-quantised chain, in one call: `MlaPrologComputeV32` without
+ * quantisation (framework/src/operator/models/deepseek_v3.2_exp/dynamic_mla_v32.cpp:187-345) and
+ * `LightningIndexerPrologCompute` (.../lightning_indexer_prolog.cpp:129-227) on its normalised query, as
+ * `DecodeIndexerAttention` runs them (.../decode_indexer_attention.cpp:85-106). Arithmetic of the system tests'
+ * goldens (framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_mla_prolog_golden_v32.py:176-303,
+ * gen_lightning_indexer_prolog.py:253-293): every product is rounded to bf16 once, all ropes de-interleave,
+ * the indexer key is LayerNorm(fp32 product) -> bf16 -> rope, the weights are bf16(x . w_idx_proj).
+ *
+ *   as pto_mla_indexer_prolog_quant, except:
+ *   w_uqqr bf16 [q_lora, 128*192]    w_idx_qb bf16 [q_lora, 64*128]    no scales, no Hadamard matrices
+ *   kv_cache bf16 [cache_rows, 512]  kr_cache bf16 [cache_rows, 64]    idx_k_cache bf16 [cache_rows, 128]
+ *   idx_query_out bf16 [t, 64, 128]  weights_out bf16 [t, 64]
+ *   q_norm_out bf16 [t, q_lora] or NULL: the normalised query (the reference's `rmsRes`)
+ *
+ * The outputs are what pto_li_decode_bf16 / pto_sfa_bf16 / pto_decode_fused_bf16 take. Same workspace rules as
+ * the quantised prolog; size from pto_prolog_nonquant_workspace_bytes. */
+size_t pto_prolog_nonquant_workspace_bytes(int t, int hidden, int q_lora);
+
+int pto_mla_indexer_prolog(
+    const void* token_x, const void* w_dq, const void* w_uqqr, const void* w_uk, const void* w_dkvkr,
+    const void* gamma_cq, const void* gamma_ckv, const void* cos, const void* sin, const int64_t* cache_index,
+    void* kv_cache, void* kr_cache, const void* w_idx_qb, const void* w_idx_k, const void* w_idx_proj,
+    const void* ln_gamma, const void* ln_beta, void* idx_k_cache, void* query_nope_out, void* query_rope_out,
+    void* idx_query_out, void* weights_out, void* q_norm_out,
+    const void* w_x_packed /* from pto_prolog_pack_weights, or NULL */,
+    int t, int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
+    void* workspace, size_t workspace_bytes, pto_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Fused decode chain: indexer -> top-k -> sparse attention on one stream, the order of
  * `DeepSeekIndexerAttentionQuant`

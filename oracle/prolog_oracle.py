@@ -13,6 +13,16 @@ Every intermediate rounding of the goldens is kept: projections are rounded to b
 casts, the int8 quantisation is round-half-even of x*127/max followed by the fp16 -> trunc chain, and
 the dequantisation scale is 1/(127/max) in fp32. `eps` arguments default to 0, which is the golden's
 arithmetic (its RMSNorm has no epsilon); the operator passes the caller's value.
+
+The two prologs in front of the non-quantised chain (`DecodeIndexerAttention`,
+framework/src/operator/models/deepseek_v3.2_exp/decode_indexer_attention.cpp:85-106) follow the system
+tests' goldens:
+
+  mla_prolog_nonquant      `mla_prolog_compute` with is_quant_a = is_quant_b = False
+                           (framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_mla_prolog_golden_v32.py:176-303)
+  indexer_prolog_nonquant  `indexer_prolog` (.../gen_lightning_indexer_prolog.py:253-293)
+  chained as `mla_prolog_golden` + `gen_deepseek_dsa_golden` chain them (.../gen_decode_indexer_attention.py:195-262):
+  the normalised query (`q_a_layernorm`) is the indexer prolog's `qr`.
 """
 from __future__ import annotations
 
@@ -147,5 +157,64 @@ def mla_indexer_prolog(p: dict, eps_cq: float = 0.0, eps_ckv: float = 0.0, ln_ep
     i = indexer_prolog(p["token_x"], m["q_norm"], m["q_norm_scale"], p["w_idx_qb"], p["w_idx_qb_scale"], p["w_idx_k"],
                        p["w_idx_proj"], p["ln_gamma"], p["ln_beta"], p["cos"], p["sin"], p["hadamard_q"],
                        p["hadamard_k"], p["idx_k_cache"], p["idx_k_scale_cache"], p["cache_index"], ln_eps)
+    m.update(i)
+    return m
+
+
+def mla_prolog_nonquant(x, w_dq, w_uqqr, w_uk, w_dkvkr, gamma_cq, gamma_ckv, cos, sin, cache_index, kv_cache, kr_cache,
+                        eps_cq: float = 0.0, eps_ckv: float = 0.0):
+    """`mla_prolog_compute` without quantisation (gen_mla_prolog_golden_v32.py:176-303): every product is an fp32
+    matmul rounded to bf16, both caches are bf16. w_uqqr bf16 [q_lora, n*192], kv_cache bf16 [rows, 512],
+    kr_cache bf16 [rows, 64]; the rest as `mla_prolog`."""
+    t = x.shape[0]
+    n, d_nope, lora = w_uk.shape
+    d_rope = cos.shape[-1]
+    xf = x.to(torch.float32)
+    q_a = (xf @ w_dq.to(torch.float32)).to(x.dtype)
+    q_norm = rms_norm(q_a, gamma_cq, eps_cq)  # bf16 [t, q_lora]: also the indexer prolog's `qr`
+    q_b = (q_norm.to(torch.float32) @ w_uqqr.to(torch.float32)).to(x.dtype).reshape(t, n, d_nope + d_rope)
+    q_nope = torch.matmul(q_b[:, :, :d_nope].permute(1, 0, 2).to(torch.float32), w_uk.to(torch.float32))
+    q_nope = q_nope.to(x.dtype).permute(1, 0, 2).contiguous()
+    kv_a = (xf @ w_dkvkr.to(torch.float32)).to(x.dtype)
+    latent = rms_norm(kv_a[:, :lora], gamma_ckv, eps_ckv)
+    q_rope = rope_interleaved(q_b[:, :, d_nope:], cos, sin)
+    k_rope = rope_interleaved(kv_a[:, lora:].reshape(t, 1, d_rope), cos, sin).reshape(t, d_rope)
+    kv_out, kr_out = kv_cache.clone(), kr_cache.clone()
+    idx = cache_index.reshape(-1).long()
+    for i in range(t):
+        kv_out[idx[i]] = latent[i]
+        kr_out[idx[i]] = k_rope[i]
+    return dict(q_nope=q_nope, q_rope=q_rope, q_norm=q_norm, kv_cache=kv_out, kr_cache=kr_out)
+
+
+def indexer_prolog_nonquant(x, qr, w_idx_qb, w_idx_k, w_idx_proj, ln_gamma, ln_beta, cos, sin, idx_k_cache, cache_index,
+                            ln_eps: float = 1e-6):
+    """`indexer_prolog` of the non-quantised indexer (gen_lightning_indexer_prolog.py:253-293): query = bf16(qr @ wq_b)
+    with the de-interleaving rope on the first 64 dims of every head; key = bf16(LayerNorm(fp32(x @ wk))) with the
+    same rope, scattered into the bf16 key cache; weights = bf16(x @ weights_proj), unscaled. w_idx_qb bf16
+    [q_lora, 64*128], idx_k_cache bf16 [rows, 128]."""
+    t = x.shape[0]
+    d = w_idx_k.shape[1]
+    n = w_idx_qb.shape[1] // d
+    rope = cos.shape[-1]
+    xf = x.to(torch.float32)
+    q = (qr.to(torch.float32) @ w_idx_qb.to(torch.float32)).to(qr.dtype).reshape(t, n, d)
+    q = torch.cat([rope_interleaved(q[..., :rope], cos, sin), q[..., rope:]], dim=-1)
+    k = layer_norm(xf @ w_idx_k.to(torch.float32), ln_gamma, ln_beta, ln_eps).to(x.dtype)
+    k = torch.cat([rope_interleaved(k[:, None, :rope], cos, sin)[:, 0], k[:, rope:]], dim=-1)
+    kc = idx_k_cache.clone()
+    idx = cache_index.reshape(-1).long()
+    for i in range(t):
+        kc[idx[i]] = k[i]
+    w = (xf @ w_idx_proj.to(torch.float32)).to(x.dtype)
+    return dict(idx_query=q, idx_k_cache=kc, weights=w)
+
+
+def mla_indexer_prolog_nonquant(p: dict, eps_cq: float = 0.0, eps_ckv: float = 0.0, ln_eps: float = 1e-6) -> dict:
+    """Both prologs of the non-quantised chain over a dict named as `make_prolog_nonquant_inputs` names it."""
+    m = mla_prolog_nonquant(p["token_x"], p["w_dq"], p["w_uqqr"], p["w_uk"], p["w_dkvkr"], p["gamma_cq"], p["gamma_ckv"],
+                            p["cos"], p["sin"], p["cache_index"], p["kv_cache"], p["kr_cache"], eps_cq, eps_ckv)
+    i = indexer_prolog_nonquant(p["token_x"], m["q_norm"], p["w_idx_qb"], p["w_idx_k"], p["w_idx_proj"], p["ln_gamma"],
+                                p["ln_beta"], p["cos"], p["sin"], p["idx_k_cache"], p["cache_index"], ln_eps)
     m.update(i)
     return m

@@ -10,6 +10,7 @@ _OPS = (
     "sparse_flash_attention_quant_d", "sparse_flash_attention_quant_p",
     "sparse_attention_antiquant_d", "sparse_attention_antiquant_p",
     "mla_indexer_prolog_quant_d", "mla_indexer_prolog_quant_p", "pack_kv_cache",
+    "mla_indexer_prolog", "decode_indexer_attention_layer",
     "decode_indexer_attention_quant", "workspace_status", "reset_workspace_status", "launch_count",
 )
 

@@ -42,6 +42,8 @@ SIGNATURES = {
     "pto_prolog_pack_weights": (_i, [_vp] * 4 + [_i, _i, _vp, _vp]),
     "pto_kv_pack_rows": (_i, [_vp] * 3 + [_i64, _vp, _vp]),
     "pto_mla_indexer_prolog_quant": (_i, [_vp] * 31 + [_i, _i, _i, _i64, _f, _f, _f, _vp, _sz, _vp]),
+    "pto_prolog_nonquant_workspace_bytes": (_sz, [_i, _i, _i]),
+    "pto_mla_indexer_prolog": (_i, [_vp] * 24 + [_i, _i, _i, _i64, _f, _f, _f, _vp, _sz, _vp]),
     "pto_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pto_decode_fused": (_i, [_vp] * 5 + [_i] + [_vp] * 9 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]),
     "pto_decode_fused_bf16": (_i, [_vp] * 11 + [_i] * 6 + [_f, _i, _vp, _sz, _vp]),

@@ -442,6 +442,29 @@ PrologWs prolog_ws(int t, int hidden, int q_lora) {
   return w;
 }
 
+struct PrologNqWs {
+  size_t status, xproj, q_norm, q_b, total;
+  int splits;
+};
+
+PrologNqWs prolog_nq_ws(int t, int hidden, int q_lora) {
+  PrologNqWs w{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += align_up(bytes, 256);
+    return at;
+  };
+  const size_t tt = static_cast<size_t>(t);
+  w.status = take(kStatusBytes);
+  w.splits = pto::prolog_sgemm_splits(t, q_lora + kXProjExtra, hidden, kPlanSms);
+  w.xproj = take(w.splits * tt * (q_lora + kXProjExtra) * 4);
+  w.q_norm = take(tt * q_lora * 2);      // bf16 [t, q_lora]
+  w.q_b = take(tt * 128 * 192 * 2);      // bf16 [t, 128, 192]
+  w.total = off;
+  return w;
+}
+
 int check_workspace(void* ws, size_t have, size_t need) {
   if (ws == nullptr) return fail(PTO_ERR_WORKSPACE, "workspace is null");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return fail(PTO_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -829,6 +852,101 @@ int pto_mla_indexer_prolog_quant(const void* token_x, const void* w_dq, const in
                  128 * 512, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
   if (rc != PTO_OK) return rc;
   PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));  // join: everything is ordered before what the caller enqueues next
+  return PTO_OK;
+}
+
+size_t pto_prolog_nonquant_workspace_bytes(int t, int hidden, int q_lora) {
+  if (t < 1 || hidden < 1 || q_lora < 1) return 0;
+  return prolog_nq_ws(t, hidden, q_lora).total;
+}
+
+int pto_mla_indexer_prolog(const void* token_x, const void* w_dq, const void* w_uqqr, const void* w_uk,
+                           const void* w_dkvkr, const void* gamma_cq, const void* gamma_ckv, const void* cos,
+                           const void* sin, const int64_t* cache_index, void* kv_cache, void* kr_cache,
+                           const void* w_idx_qb, const void* w_idx_k, const void* w_idx_proj, const void* ln_gamma,
+                           const void* ln_beta, void* idx_k_cache, void* query_nope_out, void* query_rope_out,
+                           void* idx_query_out, void* weights_out, void* q_norm_out, const void* w_x_packed, int t,
+                           int hidden, int q_lora, int64_t cache_rows, float eps_cq, float eps_ckv, float ln_eps,
+                           void* workspace, size_t workspace_bytes, pto_stream_t stream) {
+  PTO_REQUIRE(token_x && w_dq && w_uqqr && w_uk && w_dkvkr && gamma_cq && gamma_ckv && cos && sin && cache_index &&
+                  kv_cache && kr_cache && w_idx_qb && w_idx_k && w_idx_proj && ln_gamma && ln_beta && idx_k_cache &&
+                  query_nope_out && query_rope_out && idx_query_out && weights_out,
+              "null tensor pointer");
+  PTO_REQUIRE(t >= 1 && t <= 65535, "t %d: 1..65535 tokens per call", t);
+  PTO_REQUIRE(hidden >= 8 && hidden % 8 == 0, "hidden %d must be a positive multiple of 8", hidden);
+  PTO_REQUIRE(q_lora >= 16 && q_lora % 16 == 0 && q_lora <= 12288, "q_lora %d must be a multiple of 16, at most 12288",
+              q_lora);
+  PTO_REQUIRE(cache_rows >= 1, "cache_rows");
+  PTO_REQUIRE(eps_cq >= 0.f && eps_ckv >= 0.f && ln_eps >= 0.f, "negative epsilon");
+  PTO_REQUIRE(aligned16(token_x) && aligned16(w_dq) && aligned16(w_uqqr) && aligned16(w_uk) && aligned16(w_dkvkr) &&
+                  aligned16(w_idx_qb) && aligned16(w_idx_k) && aligned16(w_idx_proj) && aligned16(kv_cache) &&
+                  aligned16(gamma_cq) && aligned16(query_nope_out) && aligned16(idx_query_out) &&
+                  (q_norm_out == nullptr || aligned16(q_norm_out)),
+              "prolog tensors must be 16-byte aligned");
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != PTO_OK) return rc;
+  const PrologNqWs w = prolog_nq_ws(t, hidden, q_lora);
+  rc = check_workspace(workspace, workspace_bytes, w.total);
+  if (rc != PTO_OK) return rc;
+  uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(base + w.status);
+  const int ld = q_lora + kXProjExtra;
+  float* qa = reinterpret_cast<float*>(base + w.xproj);
+  float* kv = qa + q_lora;
+  float* ki = kv + 576;
+  float* wp = ki + 128;
+  void* q_norm = q_norm_out != nullptr ? q_norm_out : static_cast<void*>(base + w.q_norm);
+  void* q_b = base + w.q_b;
+
+  int dev = 0;
+  rc = prolog_side_stream(&dev);
+  if (rc != PTO_OK) return rc;
+  std::lock_guard<std::mutex> lock(prolog_side().dev_mu[dev]);
+  cudaStream_t side = prolog_side().side[dev];
+  cudaEvent_t* ev = prolog_side().ev[dev];
+
+  // projections of the token, as in the quantised prolog: fp32 K-split partials [splits][t, q_lora | 576 | 128 | 64]
+  const int splits = w.splits;
+  const long long split_stride = static_cast<long long>(t) * ld;
+  const size_t x_pitch = static_cast<size_t>(hidden) * 2;
+  if (w_x_packed != nullptr) {
+    PTO_REQUIRE(aligned16(w_x_packed), "w_x_packed must be 16-byte aligned");
+    rc = run_sgemm(0, token_x, x_pitch, w_x_packed, static_cast<size_t>(ld) * 2, hidden, qa, t, ld, hidden, 1, 0, 0, 0, ld,
+                   splits, split_stride, di.num_sms, status, stream);
+    if (rc != PTO_OK) return rc;
+  } else {
+    const void* ws[4] = {w_dq, w_dkvkr, w_idx_k, w_idx_proj};
+    float* outs[4] = {qa, kv, ki, wp};
+    const int ns[4] = {q_lora, 576, 128, 64};
+    for (int i = 0; i < 4; ++i) {
+      rc = run_sgemm(0, token_x, x_pitch, ws[i], static_cast<size_t>(ns[i]) * 2, hidden, outs[i], t, ns[i], hidden, 1, 0, 0,
+                     0, ld, splits, split_stride, di.num_sms, status, stream);
+      if (rc != PTO_OK) return rc;
+    }
+  }
+  // fork: caches, indexer key and weights need only the projections
+  PTO_CUDA(cudaEventRecord(ev[0], stream));
+  PTO_CUDA(cudaStreamWaitEvent(side, ev[0], 0));
+  PTO_CUDA(pto::launch_prolog_kv_bf16(kv, ki, wp, ld, splits, split_stride, gamma_ckv, cos, sin, ln_gamma, ln_beta,
+                                      cache_index, cache_rows, t, eps_ckv, ln_eps, kv_cache, kr_cache, idx_k_cache,
+                                      weights_out, status, side));
+  PTO_CUDA(cudaEventRecord(ev[2], side));
+  // caller's stream: normalised query -> the two up-projections (bf16 in, bf16 out) -> ropes -> absorbed nope part
+  PTO_CUDA(pto::launch_prolog_qnorm_bf16(qa, ld, splits, split_stride, gamma_cq, t, q_lora, eps_cq, q_norm, stream,
+                                         /*pdl=*/true));
+  const size_t qn_pitch = static_cast<size_t>(q_lora) * 2;
+  rc = run_sgemm(1, q_norm, qn_pitch, w_uqqr, 128 * 192 * 2, q_lora, q_b, t, 128 * 192, q_lora, 1, 0, 0, 0, 128 * 192, 1, 0,
+                 di.num_sms, status, stream, /*pdl=*/true);
+  if (rc != PTO_OK) return rc;
+  rc = run_sgemm(1, q_norm, qn_pitch, w_idx_qb, 64 * 128 * 2, q_lora, idx_query_out, t, 64 * 128, q_lora, 1, 0, 0, 0,
+                 64 * 128, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(pto::launch_prolog_rope_bf16(q_b, cos, sin, t, query_rope_out, idx_query_out, stream, /*pdl=*/true));
+  rc = run_sgemm(1, q_b, 128 * 192 * 2, w_uk, 512 * 2, 128 * 128, query_nope_out, t, 512, 128, 128, 128, 192 * 2, 512,
+                 128 * 512, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
+  if (rc != PTO_OK) return rc;
+  PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));
   return PTO_OK;
 }
 

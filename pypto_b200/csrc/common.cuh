@@ -387,5 +387,15 @@ cudaError_t launch_kv_pack_rows(const int8_t* kv, const void* kr, const float* s
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,
                                const void* sin, const void* hadamard_q, int t, int8_t* q_int8, void* q_scale,
                                cudaStream_t stream);
+// stages of the two non-quantised prologs (bf16 caches, bf16 indexer query and weights)
+cudaError_t launch_prolog_qnorm_bf16(const float* qa, int ld, int n_split, long long split_stride, const void* gamma_cq,
+                                     int t, int q_lora, float eps, void* q_norm, cudaStream_t stream, bool pdl = false);
+cudaError_t launch_prolog_kv_bf16(const float* kv, const float* ki, const float* wp, int ld, int n_split,
+                                  long long split_stride, const void* gamma_ckv, const void* cos, const void* sin,
+                                  const void* ln_gamma, const void* ln_beta, const int64_t* cache_index,
+                                  int64_t cache_rows, int t, float eps_ckv, float ln_eps, void* kv_cache, void* kr_cache,
+                                  void* idx_k_cache, void* weights, int32_t* status, cudaStream_t stream);
+cudaError_t launch_prolog_rope_bf16(const void* q_b, const void* cos, const void* sin, int t, void* q_rope,
+                                    void* idx_query, cudaStream_t stream, bool pdl = false);
 
 }  // namespace pto

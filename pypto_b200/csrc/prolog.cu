@@ -62,12 +62,13 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale_q) {
   return static_cast<int8_t>(__float2int_rn(__fmul_rn(v, scale_q)));
 }
 
-// ---- query down-projection: bf16 rounding, RMSNorm, per-token int8 ------------------------------------
+// ---- query down-projection: bf16 rounding, RMSNorm, then per-token int8 (kQuant) or the bf16 row itself ----
 // grid = tokens, 512 threads, dynamic shared memory = q_lora floats (16-byte aligned rows: ld and q_lora multiples of 4)
+template <bool kQuant>
 __global__ void __launch_bounds__(512)
-prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, int n_split, long long split_stride,
-                          const __nv_bfloat16* __restrict__ gamma, int q_lora, float eps, int8_t* __restrict__ q_norm,
-                          float* __restrict__ q_norm_scale) {
+prolog_qnorm_kernel(const float* __restrict__ qa, int ld, int n_split, long long split_stride,
+                    const __nv_bfloat16* __restrict__ gamma, int q_lora, float eps, int8_t* __restrict__ q_norm,
+                    float* __restrict__ q_norm_scale, __nv_bfloat16* __restrict__ q_norm_bf16) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
   pdl_wait();  // the projection before it may still be running when this grid is scheduled
@@ -113,9 +114,17 @@ prolog_qnorm_quant_kernel(const float* __restrict__ qa, int ld, int n_split, lon
     v.y = bf16_round(__fmul_rn(__fdiv_rn(v.y, rms), __uint_as_float(gm.x & 0xffff0000u)));
     v.z = bf16_round(__fmul_rn(__fdiv_rn(v.z, rms), __uint_as_float(gm.y << 16)));
     v.w = bf16_round(__fmul_rn(__fdiv_rn(v.w, rms), __uint_as_float(gm.y & 0xffff0000u)));
-    row4[g] = v;
-    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    if constexpr (kQuant) {
+      row4[g] = v;
+      amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    } else {
+      uint2 o;  // the values are bf16 already: their upper halves are the row
+      o.x = (__float_as_uint(v.x) >> 16) | (__float_as_uint(v.y) & 0xffff0000u);
+      o.y = (__float_as_uint(v.z) >> 16) | (__float_as_uint(v.w) & 0xffff0000u);
+      reinterpret_cast<uint2*>(q_norm_bf16 + static_cast<int64_t>(ti) * q_lora)[g] = o;
+    }
   }
+  if constexpr (!kQuant) return;
   amax = block_max(amax, red);
   const float scale_q = __fdiv_rn(127.0f, amax);
   char4* dst = reinterpret_cast<char4*>(q_norm + static_cast<int64_t>(ti) * q_lora);
@@ -371,6 +380,130 @@ prolog_idxq_kernel(const int32_t* __restrict__ qi_i32, const float* __restrict__
   }
 }
 
+// ==== the two prologs of the non-quantised chain ===========================================================
+// Arithmetic of the system tests' goldens: `mla_prolog_compute` without quantisation
+// (framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_mla_prolog_golden_v32.py:176-303) and the
+// non-quantised `indexer_prolog` (.../gen_lightning_indexer_prolog.py:253-293); operators
+// `MlaPrologComputeV32` (framework/src/operator/models/deepseek_v3.2_exp/dynamic_mla_v32.cpp:187-345) and
+// `LightningIndexerPrologCompute` (.../lightning_indexer_prolog.cpp:129-227). Every rope here de-interleaves
+// (even dims first), the indexer's too; there is no Hadamard rotation and the weights are not scaled.
+
+// de-interleaving rope of 64 values held in shared memory: output element c
+__device__ __forceinline__ float rope_deinterleaved(const float* pe, int c, float cs, float sn) {
+  const int j = c & 31;
+  const float even = pe[2 * j], odd = pe[2 * j + 1];
+  const float x = c < 32 ? even : odd;
+  const float rot = c < 32 ? -odd : even;
+  return __fadd_rn(__fmul_rn(x, cs), __fmul_rn(rot, sn));
+}
+
+// ---- per token: bf16 latent row, rope key, indexer key, indexer weights; scatter into the bf16 caches -----
+// grid = tokens, block = 128 (thread i owns latent dims 4i..4i+3 and indexer-key dim i)
+__global__ void __launch_bounds__(128)
+prolog_kv_bf16_kernel(const float* __restrict__ kv, const float* __restrict__ ki, const float* __restrict__ wp, int ld,
+                      int n_split, long long split_stride, const __nv_bfloat16* __restrict__ gamma_ckv,
+                      const __nv_bfloat16* __restrict__ cos, const __nv_bfloat16* __restrict__ sin,
+                      const __nv_bfloat16* __restrict__ ln_gamma, const __nv_bfloat16* __restrict__ ln_beta,
+                      const int64_t* __restrict__ cache_index, int64_t cache_rows, float eps_ckv, float ln_eps,
+                      __nv_bfloat16* __restrict__ kv_cache, __nv_bfloat16* __restrict__ kr_cache,
+                      __nv_bfloat16* __restrict__ idx_k_cache, __nv_bfloat16* __restrict__ weights, int32_t* status) {
+  __shared__ float red[32];
+  __shared__ float pe[kRope];
+  __shared__ float kpe[kRope];
+  const int ti = blockIdx.x, i = threadIdx.x;
+  const int64_t row = cache_index[ti];
+  const bool row_ok = row >= 0 && row < cache_rows;
+  if (!row_ok && i == 0) set_status(status, PTO_ST_BAD_PAGE, static_cast<int>(row), 61);
+  auto proj = [&](const float* p) {
+    float part[8];
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) part[sp] = sp < n_split ? __ldg(p + sp * split_stride) : 0.f;
+    float a = part[0];
+#pragma unroll
+    for (int sp = 1; sp < 8; ++sp) {
+      if (sp < n_split) a = __fadd_rn(a, part[sp]);
+    }
+    return a;
+  };
+  // latent part: bf16 rounding, RMSNorm, bf16
+  const float* src = kv + static_cast<int64_t>(ti) * ld;
+  float v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    v[e] = bf16_round(proj(src + 4 * i + e));
+    ss = __fadd_rn(ss, __fmul_rn(__fmul_rn(v[e], v[e]), 1.0f / kLora));
+  }
+  const float rms = sqrtf(block_sum(ss, red) + eps_ckv);
+  if (row_ok) {
+    __nv_bfloat16 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      o[e] = __float2bfloat16_rn(__fmul_rn(__fdiv_rn(v[e], rms), ld_bf16(gamma_ckv + 4 * i + e)));
+    }
+    *reinterpret_cast<uint2*>(kv_cache + row * kLora + 4 * i) = *reinterpret_cast<const uint2*>(o);
+  }
+  // rope key and indexer key: the values to rotate go through shared memory
+  if (i < kRope) pe[i] = bf16_round(proj(src + kLora + i));
+  const float x = proj(ki + static_cast<int64_t>(ti) * ld + i);
+  const float mean = block_sum(x, red) * (1.0f / kIdxDim);
+  const float dx = x - mean;
+  const float var = block_sum(__fmul_rn(dx, dx), red) * (1.0f / kIdxDim);
+  const float y = __fdiv_rn(dx, sqrtf(var + ln_eps));
+  const float k = bf16_round(__fadd_rn(__fmul_rn(y, ld_bf16(ln_gamma + i)), ld_bf16(ln_beta + i)));
+  if (i < kRope) kpe[i] = k;
+  __syncthreads();
+  if (row_ok) {
+    float ko = k;
+    if (i < kRope) {
+      const float cs = ld_bf16(cos + ti * kRope + i), sn = ld_bf16(sin + ti * kRope + i);
+      kr_cache[row * kRope + i] = __float2bfloat16_rn(rope_deinterleaved(pe, i, cs, sn));
+      ko = rope_deinterleaved(kpe, i, cs, sn);
+    }
+    idx_k_cache[row * kIdxDim + i] = __float2bfloat16_rn(ko);
+  }
+  if (i < kIdxHeads) {
+    weights[static_cast<int64_t>(ti) * kIdxHeads + i] = __float2bfloat16_rn(proj(wp + static_cast<int64_t>(ti) * ld + i));
+  }
+}
+
+// ---- ropes of the two up-projections -----------------------------------------------------------------
+// grid = (24 head groups, tokens), block = 256, two values per thread: groups 0..15 take eight attention heads
+// each (q_b[t, head, 128:192] -> q_rope[t, head, :]), groups 16..23 eight indexer heads each
+// (idx_query[t, head, 0:64] rotated in place; the other 64 dims of a head stay as the product wrote them)
+__global__ void __launch_bounds__(256)
+prolog_rope_bf16_kernel(const __nv_bfloat16* __restrict__ q_b, const __nv_bfloat16* __restrict__ cos,
+                        const __nv_bfloat16* __restrict__ sin, __nv_bfloat16* __restrict__ q_rope,
+                        __nv_bfloat16* __restrict__ idx_query) {
+  __shared__ float pe[8][kRope];
+  pdl_wait();
+  if (threadIdx.x == 0) pdl_trigger();
+  const int g = blockIdx.x, ti = blockIdx.y;
+  const bool att = g < kHeads / 8;
+  const int head0 = att ? g * 8 : (g - kHeads / 8) * 8;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int e = u * 256 + threadIdx.x;
+    const int hh = e >> 6, c = e & 63;
+    const __nv_bfloat16* src = att ? q_b + (static_cast<int64_t>(ti) * kHeads + head0 + hh) * kQHead + kNope + c
+                                   : idx_query + (static_cast<int64_t>(ti) * kIdxHeads + head0 + hh) * kIdxDim + c;
+    pe[hh][c] = __bfloat162float(*src);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int e = u * 256 + threadIdx.x;
+    const int hh = e >> 6, c = e & 63;
+    const float cs = ld_bf16(cos + ti * kRope + c), sn = ld_bf16(sin + ti * kRope + c);
+    const __nv_bfloat16 o = __float2bfloat16_rn(rope_deinterleaved(pe[hh], c, cs, sn));
+    if (att) {
+      q_rope[(static_cast<int64_t>(ti) * kHeads + head0 + hh) * kRope + c] = o;
+    } else {
+      idx_query[(static_cast<int64_t>(ti) * kIdxHeads + head0 + hh) * kIdxDim + c] = o;
+    }
+  }
+}
+
 // ---- split caches -> packed 656-byte rows: one warp per row, 41 16-byte pieces ----------------------------
 __global__ void __launch_bounds__(256)
 kv_pack_rows_kernel(const int8_t* __restrict__ kv, const __nv_bfloat16* __restrict__ kr, const float* __restrict__ sc,
@@ -401,13 +534,29 @@ cudaError_t launch_prolog_qnorm_quant(const float* qa, int ld, int n_split, long
                                       cudaStream_t stream, bool pdl) {
   const size_t dyn = static_cast<size_t>(q_lora) * sizeof(float);
   if (dyn > 40 * 1024) {  // beyond what fits the default 48 KB next to the kernel's static shared memory
-    cudaError_t e = cudaFuncSetAttribute(prolog_qnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(prolog_qnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(dyn));
     if (e != cudaSuccess) return e;
   }
   count_launch();
-  return launch_maybe_pdl(prolog_qnorm_quant_kernel, dim3(t), dim3(512), dyn, stream, pdl, qa, ld, n_split, split_stride,
-                          reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale);
+  return launch_maybe_pdl(prolog_qnorm_kernel<true>, dim3(t), dim3(512), dyn, stream, pdl, qa, ld, n_split, split_stride,
+                          reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps, q_norm, q_norm_scale,
+                          static_cast<__nv_bfloat16*>(nullptr));
+}
+
+cudaError_t launch_prolog_qnorm_bf16(const float* qa, int ld, int n_split, long long split_stride, const void* gamma_cq,
+                                     int t, int q_lora, float eps, void* q_norm, cudaStream_t stream, bool pdl) {
+  const size_t dyn = static_cast<size_t>(q_lora) * sizeof(float);
+  if (dyn > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(prolog_qnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dyn));
+    if (e != cudaSuccess) return e;
+  }
+  count_launch();
+  return launch_maybe_pdl(prolog_qnorm_kernel<false>, dim3(t), dim3(512), dyn, stream, pdl, qa, ld, n_split,
+                          split_stride, reinterpret_cast<const __nv_bfloat16*>(gamma_cq), q_lora, eps,
+                          static_cast<int8_t*>(nullptr), static_cast<float*>(nullptr),
+                          reinterpret_cast<__nv_bfloat16*>(q_norm));
 }
 
 cudaError_t launch_prolog_qb_dequant_rope(const int32_t* qb_i32, const float* q_norm_scale, const float* w_scale,
@@ -436,6 +585,30 @@ cudaError_t launch_prolog_kv(const float* kv, const float* ki, const float* wp, 
       cache_rows, eps_ckv, ln_eps, kv_cache, reinterpret_cast<__nv_bfloat16*>(kr_cache), kv_scale_cache, idx_k_cache,
       reinterpret_cast<__half*>(idx_k_scale_cache), reinterpret_cast<__half*>(weights), packed_cache, status);
   return cudaGetLastError();
+}
+
+cudaError_t launch_prolog_kv_bf16(const float* kv, const float* ki, const float* wp, int ld, int n_split,
+                                  long long split_stride, const void* gamma_ckv, const void* cos, const void* sin,
+                                  const void* ln_gamma, const void* ln_beta, const int64_t* cache_index,
+                                  int64_t cache_rows, int t, float eps_ckv, float ln_eps, void* kv_cache, void* kr_cache,
+                                  void* idx_k_cache, void* weights, int32_t* status, cudaStream_t stream) {
+  count_launch();
+  prolog_kv_bf16_kernel<<<t, 128, 0, stream>>>(
+      kv, ki, wp, ld, n_split, split_stride, reinterpret_cast<const __nv_bfloat16*>(gamma_ckv),
+      reinterpret_cast<const __nv_bfloat16*>(cos), reinterpret_cast<const __nv_bfloat16*>(sin),
+      reinterpret_cast<const __nv_bfloat16*>(ln_gamma), reinterpret_cast<const __nv_bfloat16*>(ln_beta), cache_index,
+      cache_rows, eps_ckv, ln_eps, reinterpret_cast<__nv_bfloat16*>(kv_cache), reinterpret_cast<__nv_bfloat16*>(kr_cache),
+      reinterpret_cast<__nv_bfloat16*>(idx_k_cache), reinterpret_cast<__nv_bfloat16*>(weights), status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prolog_rope_bf16(const void* q_b, const void* cos, const void* sin, int t, void* q_rope,
+                                    void* idx_query, cudaStream_t stream, bool pdl) {
+  count_launch();
+  return launch_maybe_pdl(prolog_rope_bf16_kernel, dim3((kHeads + kIdxHeads) / 8, t), dim3(256), 0, stream, pdl,
+                          reinterpret_cast<const __nv_bfloat16*>(q_b), reinterpret_cast<const __nv_bfloat16*>(cos),
+                          reinterpret_cast<const __nv_bfloat16*>(sin), reinterpret_cast<__nv_bfloat16*>(q_rope),
+                          reinterpret_cast<__nv_bfloat16*>(idx_query));
 }
 
 cudaError_t launch_prolog_idxq(const int32_t* qi_i32, const float* q_norm_scale, const float* w_scale, const void* cos,

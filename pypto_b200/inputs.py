@@ -383,6 +383,53 @@ def make_prolog_inputs(act_seq: Sequence[int], s1: int = 1, seed: int = 0, devic
     return p
 
 
+def make_prolog_nonquant_inputs(act_seq: Sequence[int], s1: int = 1, seed: int = 0, device="cpu") -> dict:
+    """Inputs of the two prologs in front of the non-quantised chain (`DecodeIndexerAttention`,
+    framework/src/operator/models/deepseek_v3.2_exp/decode_indexer_attention.cpp:64-106): as `make_prolog_inputs`,
+    with bf16 up-projection weights, bf16 latent / rope / indexer-key caches and no Hadamard matrices or scales."""
+    g = torch.Generator().manual_seed(seed)
+    b = len(act_seq)
+    t = b * s1
+    block_num, _, table = make_block_table(act_seq, g)
+    rows = block_num * BLOCK_SIZE
+    bf = torch.bfloat16
+
+    def uni(shape, lo, hi, dtype=bf):
+        return _uniform(shape, lo, hi, g, "cpu", torch.float32).to(dtype)
+
+    cache_index = torch.empty(t, dtype=torch.int64)
+    for bi, s in enumerate(act_seq):
+        for j in range(s1):
+            pos = s - s1 + j
+            cache_index[bi * s1 + j] = int(table[bi, pos // BLOCK_SIZE]) * BLOCK_SIZE + pos % BLOCK_SIZE
+    p = dict(
+        token_x=uni((t, HIDDEN), -1, 1),
+        w_dq=uni((HIDDEN, Q_LORA), -0.1, 0.1),
+        w_uqqr=uni((Q_LORA, ATT_HEADS * (NOPE_DIM + ROPE_DIM)), -0.1, 0.1),
+        w_uk=uni((ATT_HEADS, NOPE_DIM, KV_LORA), -0.1, 0.1),
+        w_dkvkr=uni((HIDDEN, KV_LORA + ROPE_DIM), -0.1, 0.1),
+        gamma_cq=uni((Q_LORA,), -1, 1),
+        gamma_ckv=uni((KV_LORA,), -1, 1),
+        cos=uni((t, ROPE_DIM), -1, 1),
+        sin=uni((t, ROPE_DIM), -1, 1),
+        cache_index=cache_index,
+        kv_cache=uni((rows, KV_LORA), -1, 1),
+        kr_cache=uni((rows, ROPE_DIM), -1, 1),
+        w_idx_qb=uni((Q_LORA, IDX_HEADS * IDX_DIM), -0.1, 0.1),
+        w_idx_k=uni((HIDDEN, IDX_DIM), -0.1, 0.1),
+        w_idx_proj=uni((HIDDEN, IDX_HEADS), -0.1, 0.1),
+        ln_gamma=uni((IDX_DIM,), 0.5, 1.5),
+        ln_beta=uni((IDX_DIM,), -0.5, 0.5),
+        idx_k_cache=uni((rows, IDX_DIM), -1, 1),
+        block_table=table,
+    )
+    if str(device) != "cpu":
+        p = {k: v.to(device) for k, v in p.items()}
+    p["act_seq"] = list(act_seq)
+    p["s1"] = s1
+    return p
+
+
 # --- host staging ----------------------------------------------------------------------------
 
 _HOST_ARENAS = []  # keeps the cudaHostAlloc'd regions alive for the life of the process

@@ -594,3 +594,112 @@ def decode_indexer_attention(idx_query, idx_key_cache, idx_weight, query_nope, q
                                              0 if sort else _lib.PTO_LI_UNSORTED, ws.data_ptr(), ws.numel(),
                                              torch.cuda.current_stream(dev).cuda_stream))
     return None
+
+
+def mla_indexer_prolog(token_x, w_dq, w_uq_qr, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index, kv_cache,
+                       kr_cache, idx_w_qb, idx_wk, idx_w_proj, idx_ln_gamma, idx_ln_beta, idx_k_cache, query_nope_out,
+                       query_rope_out, idx_query_out, idx_weights_out, epsilon_cq=1e-5, epsilon_ckv=1e-5,
+                       cache_mode="PA_BSND", *, ln_eps=1e-6, q_norm_out=None):
+    """The two prologs in front of the non-quantised chain, in one call: `MlaPrologComputeV32` without quantisation
+    (framework/src/operator/models/deepseek_v3.2_exp/dynamic_mla_v32.cpp:187-345) and
+    `LightningIndexerPrologCompute` on its normalised query (.../lightning_indexer_prolog.cpp:129-227), as
+    `DecodeIndexerAttention` runs them (.../decode_indexer_attention.cpp:85-106).
+
+    token_x bf16 [t, h]; w_dq [h, q_lora]; w_uq_qr [q_lora, 128*192]; w_uk [128, 128, 512]; w_dkv_kr [h, 576];
+    cos, sin [t, 64]; cache_index int64 [t]; idx_w_qb [q_lora, 64*128]; idx_wk [h, 128]; idx_w_proj [h, 64];
+    LayerNorm gamma / beta [128]. Updated in place at row cache_index[i]: kv_cache bf16 [.., 512], kr_cache bf16
+    [.., 64], idx_k_cache bf16 [.., 128]. Written: query_nope_out [t, 128, 512], query_rope_out [t, 128, 64],
+    idx_query_out [t, 64, 128], idx_weights_out [t, 64] (all bf16), and `q_norm_out` [t, q_lora] (the reference's
+    `rmsRes`) when given."""
+    bf = torch.bfloat16
+    x = unwrap(token_x, "token_x")
+    _need(x.dtype == bf and x.dim() == 2, "token_x: bfloat16 [t, h]")
+    t, h = x.shape
+    wdq = unwrap(w_dq, "w_dq")
+    _need(wdq.dtype == bf and wdq.dim() == 2 and wdq.shape[0] == h, "w_dq: bfloat16 [h, q_lora_rank]")
+    q_lora = wdq.shape[1]
+
+    def want(x_, name, numel, what, dtype=bf):
+        v = unwrap(x_, name)
+        _need(v.dtype == dtype and v.numel() == numel and v.is_contiguous(), f"{name}: {what}")
+        return v
+
+    w_uqqr = want(w_uq_qr, "w_uq_qr", q_lora * 128 * 192, "bfloat16 [q_lora_rank, 128*192]")
+    wuk = want(w_uk, "w_uk", 128 * 128 * 512, "bfloat16 [128, 128, 512]")
+    w_dkvkr = want(w_dkv_kr, "w_dkv_kr", h * 576, "bfloat16 [h, 576]")
+    g_cq = want(gamma_cq, "gamma_cq", q_lora, "bfloat16 [q_lora_rank]")
+    g_ckv = want(gamma_ckv, "gamma_ckv", 512, "bfloat16 [512]")
+    cos_t = want(cos, "cos", t * 64, "bfloat16 [t, 64]")
+    sin_t = want(sin, "sin", t * 64, "bfloat16 [t, 64]")
+    ci = want(cache_index, "cache_index", t, "int64 [t]", torch.int64)
+    w_qb = want(idx_w_qb, "idx_w_qb", q_lora * 64 * 128, "bfloat16 [q_lora_rank, 64*128]")
+    w_k = want(idx_wk, "idx_wk", h * 128, "bfloat16 [h, 128]")
+    w_proj = want(idx_w_proj, "idx_w_proj", h * 64, "bfloat16 [h, 64]")
+    ln_g = want(idx_ln_gamma, "idx_ln_gamma", 128, "bfloat16 [128]")
+    ln_b = want(idx_ln_beta, "idx_ln_beta", 128, "bfloat16 [128]")
+    _need(str(cache_mode) == "PA_BSND", "cache_mode: only the paged layout 'PA_BSND'")
+    kv = unwrap(kv_cache, "kv_cache")
+    _need(kv.dtype == bf and kv.numel() % 512 == 0 and kv.is_contiguous(), "kv_cache: bfloat16 [block_num, block_size, 1, 512]")
+    rows = kv.numel() // 512
+    kr = want(kr_cache, "kr_cache", rows * 64, "bfloat16 [block_num, block_size, 1, 64]")
+    ik = want(idx_k_cache, "idx_k_cache", rows * 128, "bfloat16 [block_num, block_size, 1, 128]")
+    q_nope = want(query_nope_out, "query_nope_out", t * 128 * 512, "bfloat16 [t, 128, 512]")
+    q_rope = want(query_rope_out, "query_rope_out", t * 128 * 64, "bfloat16 [t, 128, 64]")
+    iq = want(idx_query_out, "idx_query_out", t * 64 * 128, "bfloat16 [t, 64, 128]")
+    w_out = want(idx_weights_out, "idx_weights_out", t * 64, "bfloat16 [t, 64]")
+    tensors = [x, wdq, w_uqqr, wuk, w_dkvkr, g_cq, g_ckv, cos_t, sin_t, ci, kv, kr, w_qb, w_k, w_proj, ln_g, ln_b, ik,
+               q_nope, q_rope, iq, w_out]
+    qn = None
+    if q_norm_out is not None:
+        qn = want(q_norm_out, "q_norm_out", t * q_lora, "bfloat16 [t, q_lora_rank]")
+    dev = _same_device(tensors + ([qn] if qn is not None else []))
+    lib = _lib.load()
+    nbytes = lib.pto_prolog_nonquant_workspace_bytes(t, h, q_lora)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, nbytes)
+        packed = _packed_x_weights(lib, dev, wdq, w_dkvkr, w_k, w_proj, h, q_lora)
+        _lib.check(lib.pto_mla_indexer_prolog(*[v.data_ptr() for v in tensors],
+                                              qn.data_ptr() if qn is not None else None,
+                                              packed.data_ptr() if packed is not None else None, t, h, q_lora, rows,
+                                              float(epsilon_cq), float(epsilon_ckv), float(ln_eps), ws.data_ptr(),
+                                              ws.numel(), torch.cuda.current_stream(dev).cuda_stream))
+    return None
+
+
+def decode_indexer_attention_layer(x, w_dq, w_uq_qr, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, sin, cos, cache_index,
+                                   kv_cache, kr_cache, block_table, act_seqs, q_w, k_w, proj_w, ln_w, ln_bias,
+                                   index_k_cache, attention_out, *, topk_res=None, scratch=None, eps=1e-5,
+                                   softmax_scale=576 ** -0.5, selected_count=2048, sort=False):
+    """`DecodeIndexerAttention` whole, inputs in the reference's order
+    (framework/src/operator/models/deepseek_v3.2_exp/decode_indexer_attention.cpp:22-131; note sin before cos):
+    the two prologs (`mla_indexer_prolog`), then indexer -> top-k -> sparse attention over the caches they have just
+    updated (`decode_indexer_attention`). x is [b, s1, h] or [t, h]; `act_seqs` int32 [b].
+
+    `scratch`: dict with bf16 tensors query_nope [t,128,512], query_rope [t,128,64], idx_query [t,64,128],
+    idx_weights [t,64] and int32 topk_res [t,1,selected_count]; allocated when absent (pass it to record the call
+    into a CUDA graph). Returns the scratch dict (the selected positions are in scratch["topk_res"])."""
+    xt = unwrap(x, "x")
+    x2 = xt.reshape(-1, xt.shape[-1])
+    t = x2.shape[0]
+    dev = x2.device
+    if scratch is None:
+        bf = torch.bfloat16
+        scratch = dict(query_nope=torch.empty((t, 128, 512), dtype=bf, device=dev),
+                       query_rope=torch.empty((t, 128, 64), dtype=bf, device=dev),
+                       idx_query=torch.empty((t, 64, 128), dtype=bf, device=dev),
+                       idx_weights=torch.empty((t, 64), dtype=bf, device=dev),
+                       topk_res=torch.empty((t, 1, int(selected_count)), dtype=torch.int32, device=dev))
+    if topk_res is not None:
+        scratch["topk_res"] = unwrap(topk_res, "topk_res")
+    kv = unwrap(kv_cache, "kv_cache")
+    kr = unwrap(kr_cache, "kr_cache")
+    ik = unwrap(index_k_cache, "index_k_cache")
+    mla_indexer_prolog(x2, w_dq, w_uq_qr, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, unwrap(cos, "cos").reshape(t, -1),
+                       unwrap(sin, "sin").reshape(t, -1), unwrap(cache_index, "cache_index").reshape(-1), kv, kr, q_w,
+                       k_w, proj_w, ln_w, ln_bias, ik, scratch["query_nope"], scratch["query_rope"],
+                       scratch["idx_query"], scratch["idx_weights"], eps, eps)
+    decode_indexer_attention(scratch["idx_query"], ik.reshape(-1, 128, 1, 128), scratch["idx_weights"],
+                             scratch["query_nope"].reshape(t * 128, 512), scratch["query_rope"].reshape(t * 128, 64),
+                             kv.reshape(-1, 512), kr.reshape(-1, 64), act_seqs, block_table, scratch["topk_res"],
+                             attention_out, 128, softmax_scale, selected_count, sort=sort)
+    return scratch

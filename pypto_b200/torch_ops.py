@@ -110,12 +110,27 @@ def mla_indexer_prolog_quant(token_x: Tensor, mla_w_dq: Tensor, mla_w_uq_qr: Ten
                                    ip_k_cache_scale, ip_weights_out, mla_epsilon_cq, mla_epsilon_ckv)
 
 
+@torch.library.custom_op(f"{_NS}::mla_indexer_prolog",
+                         mutates_args=("kv_cache", "kr_cache", "idx_k_cache", "query_nope_out", "query_rope_out",
+                                       "idx_query_out", "idx_weights_out"))
+def mla_indexer_prolog(token_x: Tensor, w_dq: Tensor, w_uq_qr: Tensor, w_uk: Tensor, w_dkv_kr: Tensor, gamma_cq: Tensor,
+                       gamma_ckv: Tensor, cos: Tensor, sin: Tensor, cache_index: Tensor, kv_cache: Tensor,
+                       kr_cache: Tensor, idx_w_qb: Tensor, idx_wk: Tensor, idx_w_proj: Tensor, idx_ln_gamma: Tensor,
+                       idx_ln_beta: Tensor, idx_k_cache: Tensor, query_nope_out: Tensor, query_rope_out: Tensor,
+                       idx_query_out: Tensor, idx_weights_out: Tensor, epsilon_cq: float = 1e-5,
+                       epsilon_ckv: float = 1e-5) -> None:
+    """The two prologs of the non-quantised chain; the three bf16 caches are updated in place."""
+    ops.mla_indexer_prolog(token_x, w_dq, w_uq_qr, w_uk, w_dkv_kr, gamma_cq, gamma_ckv, cos, sin, cache_index, kv_cache,
+                           kr_cache, idx_w_qb, idx_wk, idx_w_proj, idx_ln_gamma, idx_ln_beta, idx_k_cache,
+                           query_nope_out, query_rope_out, idx_query_out, idx_weights_out, epsilon_cq, epsilon_ckv)
+
+
 def _no_result(*args, **kwargs) -> None:
     return None
 
 
 OPS = (lightning_indexer_decode, sparse_flash_attention_quant, sparse_attention_antiquant,
        decode_indexer_attention_quant, lightning_indexer_topk_nonquant, decode_indexer_attention,
-       mla_indexer_prolog_quant)
+       mla_indexer_prolog_quant, mla_indexer_prolog)
 for _op in OPS:
     _op.register_fake(_no_result)

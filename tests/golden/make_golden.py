@@ -17,6 +17,10 @@ drivers' pure-torch golden functions are called:
   * compute_attention_no_flash / compute_attention
     (examples/models/deepseek_v32_exp/deepseekv32_sparse_flash_attention_quant.py:169-254, :49-166)
   * compute_attention_aq       (examples/models/deepseek_v32_exp/deepseekv32_sparse_attention_antiquant.py:49-136)
+  * mla_prolog_compute without quantisation (numpy + ml_dtypes;
+    framework/tests/st/operator/src/test_deepseek_v3.2_exp/gen_mla_prolog_golden_v32.py:176-303) and the
+    non-quantised indexer_prolog (.../gen_lightning_indexer_prolog.py:253-293), chained as
+    .../gen_decode_indexer_attention.py:195-262 chains them
 
 Inputs come from `pypto_b200.inputs.make_inputs` (seeded); each fixture stores the seed, a sha256
 of every input tensor and the reference's outputs, so the tests regenerate identical inputs
@@ -255,6 +259,67 @@ def make_prolog(pro_mod, name, act_seq, s1):
     print(name, "t", t, "rows", rows)
 
 
+PROLOG_NONQUANT_CASES = {
+    # name: (act_seq, s1)
+    "prolog_nonquant_single": ([300, 129, 1000], 1),
+    "prolog_nonquant_mtp": ([257, 2048], 2),
+}
+
+
+def make_prolog_nonquant(name, act_seq, s1):
+    """Runs the system tests' goldens of the two non-quantised prologs on inputs of
+    `pypto_b200.inputs.make_prolog_nonquant_inputs`: `mla_prolog_compute` (numpy, ml_dtypes bfloat16; is_quant_a =
+    is_quant_b = False, cache mode PA_BSND), then `indexer_prolog` (torch) with the first one's normalised query as
+    `qr`."""
+    import ml_dtypes
+    mla_mod = importlib.import_module("gen_mla_prolog_golden_v32")
+    ip_mod = importlib.import_module("gen_lightning_indexer_prolog")
+    seed = 15000 + sum(act_seq) + s1
+    p = gen.make_prolog_nonquant_inputs(act_seq, s1=s1, seed=seed)
+    b, t = len(act_seq), len(act_seq) * s1
+    rows = p["kv_cache"].shape[0]
+    nb = rows // 128
+    bf = ml_dtypes.bfloat16
+
+    def nbf(x):
+        return x.contiguous().view(torch.int16).numpy().view(bf).copy()
+
+    def tbf(a):
+        return torch.from_numpy(np.ascontiguousarray(a).view(np.int16).copy()).view(torch.bfloat16)
+
+    mla_in = dict(dtype=bf, is_quant_a=False, is_quant_b=False, has_smooth=False, cache_mode="PA_BSND", epsilon=0.0,
+                  gamma_cq=nbf(p["gamma_cq"]).astype(np.float32), gamma_ckv=nbf(p["gamma_ckv"]).astype(np.float32),
+                  x=nbf(p["token_x"]).reshape(b, s1, -1), w_dq=nbf(p["w_dq"]), w_uqqr=nbf(p["w_uqqr"]),
+                  w_uk=nbf(p["w_uk"]), w_dkvkr=nbf(p["w_dkvkr"]), cos=nbf(p["cos"]).reshape(b, s1, -1),
+                  sin=nbf(p["sin"]).reshape(b, s1, -1), kv_cache=nbf(p["kv_cache"]).reshape(nb, 128, 1, 512),
+                  kr_cache=nbf(p["kr_cache"]).reshape(nb, 128, 1, 64),
+                  cache_index=p["cache_index"].reshape(b, s1).numpy())
+    q_out, q_rope, kv_out, kr_out, q_norm = mla_mod.mla_prolog_compute(mla_in)
+    q_nope, q_rope, q_norm = tbf(q_out).reshape(t, 128, 512), tbf(q_rope).reshape(t, 128, 64), tbf(q_norm).reshape(t, -1)
+    kv_out, kr_out = tbf(kv_out).reshape(rows, 512), tbf(kr_out).reshape(rows, 64)
+    ip_in = dict(token_x=p["token_x"].reshape(b, s1, -1), qr=q_norm.reshape(b, s1, -1), wq_b=p["w_idx_qb"],
+                 wk=p["w_idx_k"], cos_idx_rope=p["cos"].reshape(b, s1, -1), sin_idx_rope=p["sin"].reshape(b, s1, -1),
+                 weight_layer_norm=p["ln_gamma"], bias_layer_norm=p["ln_beta"],
+                 idx_k_cache=p["idx_k_cache"].reshape(nb, 128, 1, 128),
+                 idx_k_cache_index=p["cache_index"].reshape(b, s1), weights_proj=p["w_idx_proj"])
+    ip = ip_mod.indexer_prolog(ip_in, dict(b=b, seq=s1, idx_n_heads=64, idx_head_dim=128, rope_head_dim=64))
+    idx = p["cache_index"]
+    tensors = {k: v for k, v in p.items() if isinstance(v, torch.Tensor)}
+    np.savez_compressed(
+        HERE / f"{name}.npz",
+        act_seq=np.array(act_seq, dtype=np.int32), s1=np.int32(s1), seed=np.int64(seed),
+        hashes=np.array([f"{k}={sha(v)}" for k, v in sorted(tensors.items())]),
+        q_nope_sha=sha(q_nope), q_nope_heads=as_np(q_nope[:, list(PROLOG_HEADS), :]),
+        q_rope=as_np(q_rope), q_norm=as_np(q_norm),
+        kv_rows=as_np(kv_out[idx]), kv_cache_sha=sha(kv_out),
+        kr_rows=as_np(kr_out[idx]), kr_cache_sha=sha(kr_out),
+        idx_query=as_np(ip["query"].reshape(t, 64, 128)),
+        idx_k_rows=as_np(ip["idx_k_cache_out"].reshape(rows, 128)[idx]), idx_k_cache_sha=sha(ip["idx_k_cache_out"]),
+        weights=as_np(ip["weights"].reshape(t, 64)),
+    )
+    print(name, "t", t, "rows", rows)
+
+
 def make_gather_kat():
     """The paged-gather known answer printed in the reference docstring
     (python/pypto/experimental.py:62-87) and the `10*token + h` buffer pattern of
@@ -278,6 +343,8 @@ def main():
     pro_mod = importlib.import_module("deepseekv32_mla_indexer_prolog_quant")
     for name, (act, s1) in PROLOG_CASES.items():
         make_prolog(pro_mod, name, act, s1)
+    for name, (act, s1) in PROLOG_NONQUANT_CASES.items():
+        make_prolog_nonquant(name, act, s1)
 
 
 if __name__ == "__main__":

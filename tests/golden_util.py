@@ -49,6 +49,18 @@ def load_prolog_case(name: str):
     return p, z
 
 
+PROLOG_NONQUANT_CASES = ["prolog_nonquant_single", "prolog_nonquant_mtp"]
+
+
+def load_prolog_nonquant_case(name: str):
+    z = np.load(GOLDEN / f"{name}.npz")
+    p = gen.make_prolog_nonquant_inputs([int(x) for x in z["act_seq"]], s1=int(z["s1"]), seed=int(z["seed"]))
+    want = dict(h.split("=") for h in z["hashes"])
+    got = {k: sha(v) for k, v in p.items() if isinstance(v, torch.Tensor)}
+    assert got == want, f"regenerated inputs of {name} differ from the ones the fixture was made with"
+    return p, z
+
+
 LI_CASES = ["li_ragged_f32", "li_mtp_f16", "li_short_f16"]
 NONQUANT_CASES = ["li_nonquant_mtp", "li_nonquant_ragged"]
 SFA_CASES = ["sfa_ragged_mtp", "sfa_single"]

@@ -5,7 +5,8 @@ import pytest
 import torch
 
 from oracle import prolog_oracle as po
-from golden_util import PROLOG_CASES, PROLOG_HEADS, from_np_bf16, load_prolog_case, sha
+from golden_util import (PROLOG_CASES, PROLOG_HEADS, PROLOG_NONQUANT_CASES, from_np_bf16, load_prolog_case,
+                         load_prolog_nonquant_case, sha)
 
 
 def _same_or_close(got, want, name, rel=1e-3):
@@ -46,6 +47,29 @@ def test_prolog_oracle_matches_reference_goldens(name):
     # on this host the restatement is expected to be bit-identical; report when it is
     same = {k: sha(o[k]) == str(z[f"{k}_sha"]) for k in ("q_nope", "kv_cache", "kr_cache", "kv_scale_cache",
                                                           "idx_k_cache", "idx_k_scale_cache")}
+    print(name, "digests equal:", same)
+
+
+@pytest.mark.parametrize("name", PROLOG_NONQUANT_CASES)
+def test_nonquant_prolog_oracle_matches_reference_goldens(name):
+    """`mla_prolog_compute` without quantisation (numpy, ml_dtypes) and the non-quantised `indexer_prolog` (torch) of
+    the reference's system tests, chained; the fixture keeps their outputs."""
+    p, z = load_prolog_nonquant_case(name)
+    o = po.mla_indexer_prolog_nonquant(p)
+    idx = p["cache_index"]
+    _same_or_close(o["q_norm"], from_np_bf16(z["q_norm"]), "q_norm")
+    _same_or_close(o["q_nope"][:, list(PROLOG_HEADS), :], from_np_bf16(z["q_nope_heads"]), "q_nope")
+    _same_or_close(o["q_rope"], from_np_bf16(z["q_rope"]), "q_rope")
+    _same_or_close(o["kv_cache"][idx], from_np_bf16(z["kv_rows"]), "kv rows")
+    _same_or_close(o["kr_cache"][idx], from_np_bf16(z["kr_rows"]), "kr rows")
+    _same_or_close(o["idx_query"], from_np_bf16(z["idx_query"]), "idx_query")
+    _same_or_close(o["idx_k_cache"][idx], from_np_bf16(z["idx_k_rows"]), "idx k rows")
+    _same_or_close(o["weights"], from_np_bf16(z["weights"]), "weights")
+    keep = torch.ones(p["kv_cache"].shape[0], dtype=torch.bool)
+    keep[idx] = False
+    for key in ("kv_cache", "kr_cache", "idx_k_cache"):
+        assert torch.equal(o[key][keep], p[key][keep]), key
+    same = {k: sha(o[k]) == str(z[f"{k}_sha"]) for k in ("q_nope", "kv_cache", "kr_cache", "idx_k_cache")}
     print(name, "digests equal:", same)
 
 

@@ -17,6 +17,8 @@ def test_schemas_name_the_buffers_each_op_writes():
         "lightning_indexer_topk_nonquant": {"topk_res"},
         "decode_indexer_attention": {"topk_res", "attention_out"},
         "mla_indexer_prolog_quant": set(top._PROLOG_OUT),
+        "mla_indexer_prolog": {"kv_cache", "kr_cache", "idx_k_cache", "query_nope_out", "query_rope_out",
+                               "idx_query_out", "idx_weights_out"},
     }
     for name, written in want.items():
         schema = getattr(ns, name).default._schema
