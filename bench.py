@@ -214,8 +214,47 @@ def measure_prolog(dev, batch, ctx, s1, steps, warmup):
             "l2": "256 MB written between timed calls", "status": pto.workspace_status(dev)[0]}
 
 
+def measure_prolog_nonquant(dev, batch, ctx, s1, steps, warmup):
+    """The two prologs of the non-quantised chain (`pto.mla_indexer_prolog`) for `batch` x `s1` tokens, eager and
+    replayed from a CUDA graph. Algorithmic bytes = every (bf16) weight once + the token's rows."""
+    import pypto_b200 as pto
+
+    p = gen.make_prolog_nonquant_inputs([ctx] * batch, s1=s1, seed=4321, device=dev)
+    t = batch * s1
+    bf = torch.bfloat16
+    out = [torch.zeros(t, 128, 512, dtype=bf, device=dev), torch.zeros(t, 128, 64, dtype=bf, device=dev),
+           torch.zeros(t, 64, 128, dtype=bf, device=dev), torch.zeros(t, 64, dtype=bf, device=dev)]
+    names = ["token_x", "w_dq", "w_uqqr", "w_uk", "w_dkvkr", "gamma_cq", "gamma_ckv", "cos", "sin", "cache_index",
+             "kv_cache", "kr_cache", "w_idx_qb", "w_idx_k", "w_idx_proj", "ln_gamma", "ln_beta", "idx_k_cache"]
+    call_args = [p[n] for n in names] + out + [1e-5, 1e-5]
+    weights = ["w_dq", "w_uqqr", "w_uk", "w_dkvkr", "w_idx_qb", "w_idx_k", "w_idx_proj"]
+    by = sum(p[n].numel() * p[n].element_size() for n in weights)
+    by += t * (7168 * 2 + 128 * 576 * 2 + 64 * 128 * 2 + 64 * 2 + (512 + 64 + 128) * 2)
+    captured = pto.CapturedCall(pto.mla_indexer_prolog, *call_args)
+    res = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for tag, fn in (("eager", lambda: pto.mla_indexer_prolog(*call_args)), ("graph", captured.replay)):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        res[tag + "_ms"] = statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+    peak, src = load_peaks()
+    return {"stage": "prolog_nonquant", "tokens": t, **res, "algorithmic_bytes": by,
+            "achieved_gbs": by / res["graph_ms"] / 1e6, "peak_gbs": peak, "peak_source": src,
+            "frac": by / res["graph_ms"] / 1e6 / peak, "gpu_launches_per_call": 7,
+            "l2": "256 MB written between timed calls", "status": pto.workspace_status(dev)[0]}
+
+
 def run_prolog_stage(args, dev):
-    print(json.dumps(measure_prolog(dev, args.batch, args.ctx, args.s1, args.steps, args.warmup)), flush=True)
+    fn = measure_prolog_nonquant if args.stage == "prolog_nonquant" else measure_prolog
+    print(json.dumps(fn(dev, args.batch, args.ctx, args.s1, args.steps, args.warmup)), flush=True)
 
 
 def run_layer_stage(args, dev):
@@ -273,7 +312,7 @@ def run_stage(args, dev):
     """Profiling aid: one stage alone on a uniform synthetic case, timed with CUDA events."""
     import pypto_b200 as pto
 
-    if args.stage == "prolog":
+    if args.stage in ("prolog", "prolog_nonquant"):
         return run_prolog_stage(args, dev)
     if args.stage == "layer":
         return run_layer_stage(args, dev)
@@ -539,7 +578,7 @@ def main():
     ap.add_argument("--partition", default="heads", choices=["heads", "tokens"], help="configuration 4 on N > 1 GPUs")
     ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
     ap.add_argument("--stage", default=None, choices=["li_score", "li_decode", "topk", "sfa", "sfa_bf16", "fused", "prolog", "layer", "li_score_chain",
-                             "kv_pack", "li_score_nonquant", "topk_unsorted"],
+                             "kv_pack", "li_score_nonquant", "topk_unsorted", "prolog_nonquant"],
                     help="profiling aid: run only this stage --steps times on a uniform case (--batch x --ctx) and exit")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--ctx", type=int, default=65536)
