@@ -239,7 +239,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
   int64_t prev_tok0 = 0;
   // adds this CTA's counts of the tokens tok_first .. tok_first + s1 - 1 into the global histogram and clears them
   auto flush_hist = [&](int64_t tok_first) {
-    for (int j = tid; j < s1 * kLiHistBins; j += kLiThreads) {
+    // (not the producer warp: it does not take part in the barrier that orders the flush before new counts)
+    for (int j = tid - 32; j >= 0 && j < s1 * kLiHistBins; j += kLiThreads - 32) {
       const unsigned int c = hist_sm[j];
       if (c != 0u) {
         atomicAdd(p.hist + tok_first * kLiHistBins + j, c);
@@ -257,12 +258,15 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     // (grid y: further groups of s1 tokens of the same sequences, prefill chunks)
     const int64_t tok0 = static_cast<int64_t>(bi) * p.s1_total + p.tok_offset + static_cast<int>(blockIdx.y) * p.s1;
 
-    __syncthreads();  // previous segment fully drained: Q tile and ws may be overwritten
+    // The producer warp takes no part in the two barriers of a segment: the ring's own barriers order its loads, so
+    // the next segment's first pages are on their way while this one drains and the scale products are fetched.
+    // previous segment fully drained: Q tile and ws may be overwritten
+    if (warp != 0) asm volatile("bar.sync 1, %0;" ::"n"(kLiThreads - 32) : "memory");
     if (with_hist && seg > 0) flush_hist(prev_tok0);  // (the barrier below orders it before the next segment's counts)
     prev_tok0 = tok0;
     const bool aborted = ctl->abort != 0;
     if (!aborted) {
-      if (warp == 0 && lane == 0) {
+      if (warp == 1 && lane == 0) {
         if (kBf16) {
           mbar_arrive_expect_tx(smem_u32(&ctl->qfull), 2 * q_half_bytes);
           tma_load_2d(q_base, &tmap_q, 0, static_cast<int>(tok0) * kHeads, smem_u32(&ctl->qfull));
@@ -286,7 +290,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         }
       }
     }
-    __syncthreads();
+    // the scale products are visible to the MMA and epilogue warps
+    if (warp != 0) asm volatile("bar.sync 1, %0;" ::"n"(kLiThreads - 32) : "memory");
 
     if (!aborted) {
       if (warp == 0) {
