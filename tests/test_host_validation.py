@@ -134,3 +134,28 @@ def test_prolog_rejects_bad_arguments_before_any_launch():
         call(cache_index=p["cache_index"].to(torch.int32))
     with pytest.raises(ValueError, match="PA_BSND"):
         pto.mla_indexer_prolog_quant_d(*[p[n] for n in names], *outs, 1e-5, 1e-5, "BSND", None, None, None, None)
+
+
+def test_nonquant_prolog_rejects_bad_arguments_before_any_launch():
+    p = gen.make_prolog_nonquant_inputs([200], s1=1, seed=1)
+    bf = torch.bfloat16
+    outs = [torch.zeros(1, 128, 512, dtype=bf), torch.zeros(1, 128, 64, dtype=bf), torch.zeros(1, 64, 128, dtype=bf),
+            torch.zeros(1, 64, dtype=bf)]
+    names = ["token_x", "w_dq", "w_uqqr", "w_uk", "w_dkvkr", "gamma_cq", "gamma_ckv", "cos", "sin", "cache_index",
+             "kv_cache", "kr_cache", "w_idx_qb", "w_idx_k", "w_idx_proj", "ln_gamma", "ln_beta", "idx_k_cache"]
+
+    def call(*tail, **over):
+        return pto.mla_indexer_prolog(*[over.get(n, p[n]) for n in names], *outs, *tail)
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        call()
+    with pytest.raises(ValueError, match="w_uq_qr"):
+        call(w_uqqr=p["w_uqqr"].to(torch.int8))
+    with pytest.raises(ValueError, match="kv_cache"):
+        call(kv_cache=p["kv_cache"].to(torch.int8))
+    with pytest.raises(ValueError, match="idx_k_cache"):
+        call(idx_k_cache=p["idx_k_cache"][:-1].contiguous())
+    with pytest.raises(ValueError, match="cache_index"):
+        call(cache_index=p["cache_index"].to(torch.int32))
+    with pytest.raises(ValueError, match="PA_BSND"):
+        call(1e-5, 1e-5, "BSND")
