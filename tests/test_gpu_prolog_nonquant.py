@@ -162,3 +162,67 @@ def test_arguments_are_checked():
     torch.cuda.synchronize()
     assert pto.workspace_status()[0] != 0
     pto.reset_workspace_status()
+
+
+def test_layer_recorded_into_a_cuda_graph_and_prolog_through_the_registration():
+    """The whole layer (prologs + chain, scratch passed in) captured once and replayed after the token's hidden
+    states are refreshed in place gives the eager result of the new input; the prolog alone through
+    `torch.ops.pypto_b200.mla_indexer_prolog` equals the direct call."""
+    import pypto_b200.torch_ops  # noqa: F401  (registers the namespace)
+
+    act, s1 = [3000, 700, 129], 1
+    p = gen.make_prolog_nonquant_inputs(act, s1=s1, seed=91)
+    p2 = gen.make_prolog_nonquant_inputs(act, s1=s1, seed=92)
+    g = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in p.items()}
+    b = t = len(act)
+    bf = torch.bfloat16
+    act_t = torch.tensor(act, dtype=torch.int32, device=DEV)
+
+    def fresh_scratch():
+        return dict(query_nope=torch.zeros(t, 128, 512, dtype=bf, device=DEV), query_rope=torch.zeros(t, 128, 64, dtype=bf, device=DEV),
+                    idx_query=torch.zeros(t, 64, 128, dtype=bf, device=DEV), idx_weights=torch.zeros(t, 64, dtype=bf, device=DEV),
+                    topk_res=torch.zeros(t, 1, 2048, dtype=torch.int32, device=DEV))
+
+    def layer_args(x, caches, out):
+        return [x, g["w_dq"], g["w_uqqr"], g["w_uk"], g["w_dkvkr"], g["gamma_cq"], g["gamma_ckv"], g["sin"], g["cos"],
+                g["cache_index"], caches["kv_cache"], caches["kr_cache"], g["block_table"], act_t, g["w_idx_qb"],
+                g["w_idx_k"], g["w_idx_proj"], g["ln_gamma"], g["ln_beta"], caches["idx_k_cache"], out]
+
+    # captured: static input buffer x, own copies of the caches
+    x = g["token_x"].clone()
+    caches_c = {k: g[k].clone() for k in ("kv_cache", "kr_cache", "idx_k_cache")}
+    out_c = torch.zeros((b, s1, 128, 512), dtype=bf, device=DEV)
+    sc_c = fresh_scratch()
+    step = pto.CapturedCall(pto.decode_indexer_attention_layer, *layer_args(x, caches_c, out_c), scratch=sc_c, sort=True)
+    x.copy_(p2["token_x"].to(DEV))
+    step.replay()
+    torch.cuda.synchronize()
+    assert step.workspace_status()[0] == 0
+    # eager on the same new input
+    caches_e = {k: g[k].clone() for k in ("kv_cache", "kr_cache", "idx_k_cache")}
+    out_e = torch.zeros_like(out_c)
+    sc_e = pto.decode_indexer_attention_layer(*layer_args(p2["token_x"].to(DEV), caches_e, out_e), scratch=fresh_scratch(),
+                                              sort=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out_c, out_e) and torch.equal(sc_c["topk_res"], sc_e["topk_res"])
+    for k in caches_c:
+        assert torch.equal(caches_c[k], caches_e[k]), k
+
+    # the prolog through the registered op
+    o1 = fresh_scratch()
+    o2 = fresh_scratch()
+    c1 = {k: g[k].clone() for k in ("kv_cache", "kr_cache", "idx_k_cache")}
+    c2 = {k: g[k].clone() for k in ("kv_cache", "kr_cache", "idx_k_cache")}
+    common = [g["token_x"], g["w_dq"], g["w_uqqr"], g["w_uk"], g["w_dkvkr"], g["gamma_cq"], g["gamma_ckv"], g["cos"], g["sin"],
+              g["cache_index"]]
+    tail = [g["w_idx_qb"], g["w_idx_k"], g["w_idx_proj"], g["ln_gamma"], g["ln_beta"]]
+    pto.mla_indexer_prolog(*common, c1["kv_cache"], c1["kr_cache"], *tail, c1["idx_k_cache"], o1["query_nope"],
+                           o1["query_rope"], o1["idx_query"], o1["idx_weights"], 1e-5, 1e-5)
+    torch.ops.pypto_b200.mla_indexer_prolog(*common, c2["kv_cache"], c2["kr_cache"], *tail, c2["idx_k_cache"],
+                                            o2["query_nope"], o2["query_rope"], o2["idx_query"], o2["idx_weights"], 1e-5,
+                                            1e-5)
+    torch.cuda.synchronize()
+    for k in ("query_nope", "query_rope", "idx_query", "idx_weights"):
+        assert torch.equal(o1[k], o2[k]), k
+    for k in c1:
+        assert torch.equal(c1[k], c2[k]), k
