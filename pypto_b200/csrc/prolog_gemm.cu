@@ -23,13 +23,20 @@ namespace {
 constexpr int kGTileN = 128;              // weight columns per tile (MMA M)
 constexpr int kGTileK = 128;              // k rows per stage
 constexpr int kGStageBytes = kGTileN * kGTileK;  // 16 KB
-constexpr int kGStages = 6;
+constexpr int kGMaxStages = 10;           // ring stages: as many as fit beside the activations, see kGDataBudget
 constexpr int kGXBytesMax = 96 * 1024;    // resident activations: (K / 128) * t_pad * 128 bytes
+// Ring + activations: at most kGDataMax. With more than 32 token rows they stay within kGDataBudget, so that a
+// block of the prolog's per-token kernel (33 KB of shared memory, launched on a second stream just before this
+// kernel) fits on the same SM: with all of shared memory taken here, those blocks (one per token) kept their SMs to
+// themselves and this kernel's CTAs there started 5 us late (64 tokens: 63.3 -> 60.5 us per prolog call; with 8 or
+// 32 tokens sharing costs about 1 us more than it returns, so fewer tokens keep the larger ring).
+constexpr int kGDataBudget = 176 * 1024;
+constexpr int kGDataMax = 192 * 1024;
 constexpr int kGThreads = 192;
 
 struct GemmCtl {
-  uint64_t full[kGStages];
-  uint64_t empty[kGStages];
+  uint64_t full[kGMaxStages];
+  uint64_t empty[kGMaxStages];
   uint64_t x_full;
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
@@ -37,7 +44,8 @@ struct GemmCtl {
   int abort;
 };
 
-constexpr int kGSmemBytes = kGStages * kGStageBytes + kGXBytesMax + sizeof(GemmCtl) + 1024;
+constexpr int kGSmemBytes = kGDataMax + sizeof(GemmCtl) + 1024;
+static_assert(kGXBytesMax + 2 * kGStageBytes <= kGDataBudget, "no room for a ring beside the activations");
 
 struct GemmParams {
   int32_t* out[2];   // [t, ld] row-major
@@ -46,6 +54,8 @@ struct GemmParams {
   int k;             // contraction length, multiple of 128
   int t;             // token rows that are stored
   int t_pad;         // MMA N: t rounded up to 16, <= 64
+  int n_stages;      // ring stages of this launch
+  int data_bytes;    // ring + activations area of this launch (the control block follows it)
   int32_t* status;
 };
 
@@ -57,8 +67,9 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = gemm_smem_raw + (base - raw);
   const uint32_t a_base = base;
-  const uint32_t x_base = base + kGStages * kGStageBytes;
-  GemmCtl* ctl = reinterpret_cast<GemmCtl*>(smem + kGStages * kGStageBytes + kGXBytesMax);
+  const uint32_t n_stages = static_cast<uint32_t>(p.n_stages);
+  const uint32_t x_base = base + n_stages * kGStageBytes;
+  GemmCtl* ctl = reinterpret_cast<GemmCtl*>(smem + p.data_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunks = p.k / kGTileK;
@@ -66,7 +77,7 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
   const uint32_t x_slab = static_cast<uint32_t>(p.t_pad) * 128u;
 
   if (tid == 0) {
-    for (int i = 0; i < kGStages; ++i) {
+    for (int i = 0; i < kGMaxStages; ++i) {
       mbar_init(smem_u32(&ctl->full[i]), 1);
       mbar_init(smem_u32(&ctl->empty[i]), 1);
     }
@@ -106,9 +117,9 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
         const CUtensorMap* tm = second ? &tmap_w1 : &tmap_w0;
         const int n0 = (second ? tile - p.tiles[0] : tile) * kGTileN;
         for (int c = 0; c < chunks; ++c, ++it) {
-          const uint32_t s = it % kGStages;
-          if (it >= kGStages) {
-            ok = mbar_wait(smem_u32(&ctl->empty[s]), ((it / kGStages) - 1) & 1);
+          const uint32_t s = it % n_stages;
+          if (it >= n_stages) {
+            ok = mbar_wait(smem_u32(&ctl->empty[s]), ((it / n_stages) - 1) & 1);
             if (!ok) break;
           }
           mbar_arrive_expect_tx(smem_u32(&ctl->full[s]), kGStageBytes);
@@ -135,8 +146,8 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
         tc_fence_after();
         const uint32_t d = tmem_base + acc * 64u;
         for (int c = 0; c < chunks; ++c, ++it) {
-          const uint32_t s = it % kGStages;
-          ok = mbar_wait(smem_u32(&ctl->full[s]), (it / kGStages) & 1);
+          const uint32_t s = it % n_stages;
+          ok = mbar_wait(smem_u32(&ctl->full[s]), (it / n_stages) & 1);
           if (!ok) break;
           tc_fence_after();
           const uint64_t b_desc = umma_desc_kmajor_sw128(x_base + c * x_slab);
@@ -226,11 +237,16 @@ cudaError_t launch_prolog_i8_gemm(const void* tmap_w0, const void* tmap_w1, cons
   p.k = k;
   p.t = t;
   p.t_pad = (t + 15) / 16 * 16;
+  const int x_bytes = (k / kGTileK) * p.t_pad * 128;
+  p.data_bytes = p.t_pad > 32 ? kGDataBudget : kGDataMax;
+  p.n_stages = (p.data_bytes - x_bytes) / kGStageBytes;
+  if (p.n_stages > kGMaxStages) p.n_stages = kGMaxStages;
+  const int smem_bytes = p.data_bytes + static_cast<int>(sizeof(GemmCtl)) + 1024;
   p.status = status;
   const int n_tiles = p.tiles[0] + p.tiles[1];
   const int grid = n_tiles < num_sms ? n_tiles : num_sms;
   count_launch();
-  return launch_maybe_pdl(prolog_i8_gemm_kernel, dim3(grid), dim3(kGThreads), kGSmemBytes, stream, pdl,
+  return launch_maybe_pdl(prolog_i8_gemm_kernel, dim3(grid), dim3(kGThreads), smem_bytes, stream, pdl,
                           *reinterpret_cast<const CUtensorMap*>(tmap_w0), *reinterpret_cast<const CUtensorMap*>(tmap_w1),
                           *reinterpret_cast<const CUtensorMap*>(tmap_x), p);
 }
