@@ -173,3 +173,45 @@ def test_back_to_back_fused_calls_equal_the_stages_run_one_by_one(b, s1):
                                            576 ** -0.5, 2048, 128, d.max_blocks)
         torch.cuda.synchronize()
         assert torch.equal(out2, outs[r])
+
+
+def test_random_shapes_against_oracle_chain():
+    """Forty seeded random cases: batch 1-8, one to four query tokens per sequence, lengths drawn around the page and
+    selection boundaries (1, 127-129, 2047-2050, 4095-4097) and up to 40000 keys, both scale dtypes, ordered and
+    unordered output. Selected sets against the oracle indexer (exact on untied scores, -1 padding, no duplicates,
+    positions inside the causal prefix), attention against the oracle on the kernel's own selection."""
+    import random
+
+    rng = random.Random(2024)
+    special = [1, 2, 3, 127, 128, 129, 2047, 2048, 2049, 2050, 4095, 4096, 4097, 2048 + 127, 2048 + 128]
+    for case in range(40):
+        b = rng.choice([1, 1, 2, 3, 5, 8])
+        s1 = rng.choice([1, 1, 2, 3, 4])
+        act = []
+        for _ in range(b):
+            r = rng.random()
+            act.append(rng.choice(special) if r < 0.4 else rng.randint(1, 9000) if r < 0.8 else rng.randint(9000, 40000))
+        dt = rng.choice([torch.float32, torch.float16])
+        sort = rng.random() < 0.5
+        d = gen.make_inputs(act, s1=s1, seed=1000 + case, scale_dtype=dt)
+        idx, out = _fused(d, sort=sort, fill=5)
+        want_idx, _, rows = oracle.lightning_indexer(d.idx_query, d.idx_query_scale, d.idx_key_cache, d.idx_key_scale,
+                                                     d.idx_weight, d.act_seq, d.block_table, d.s1)
+        for ti in range(d.t):
+            bi, i = divmod(ti, s1)
+            eff = act[bi] - (s1 - 1 - i)
+            nvalid = max(0, min(eff, 2048))
+            untied, _ = oracle.topk_set_diff(idx[ti], want_idx[ti], rows[ti])
+            assert untied == 0, (case, act, s1, ti, untied)
+            assert int((idx[ti] >= 0).sum()) == nvalid and torch.all(idx[ti, 0, nvalid:] == -1), (case, ti)
+            v = idx[ti, 0, :nvalid]
+            assert nvalid == 0 or (int(v.max()) < eff and len(set(v.tolist())) == nvalid), (case, ti)
+        want = oracle.sparse_attention(d.query_nope, d.query_rope, d.key_nope_2d, d.key_rope_2d, d.k_nope_scales,
+                                       idx.reshape(d.t, 2048), d.block_table, d.act_seq, d.s1)
+        for bi in range(d.b):
+            for i in range(s1):
+                if act[bi] - s1 + 1 + i > 0:
+                    e = oracle.attention_errors(out[bi, i], want[bi, i])
+                    assert e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3, (case, act, s1, bi, i, e)
+                else:
+                    assert torch.all(out[bi, i] == 0), (case, bi, i)
