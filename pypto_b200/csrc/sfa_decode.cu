@@ -484,7 +484,7 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
       const char* v = getenv("PTO_SFA_IMPL");
       return v != nullptr && strcmp(v, "cluster") == 0;
     }();
-    e = (p.kn_bf16 || force_cluster) ? launch_sfa_cluster(p, stream) : launch_sfa_pair(p, stream);
+    e = force_cluster ? launch_sfa_cluster(p, stream) : launch_sfa_pair(p, stream);
   } else {
     count_launch();
     sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);

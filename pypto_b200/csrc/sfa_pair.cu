@@ -602,8 +602,13 @@ __device__ __forceinline__ void pair_role_softmax(const SfaParams& p, PairCtx c)
 // Lane r % 8 also walks the look-ahead chain of row 8w + r % 8: the selected index four tiles ahead, its
 // block-table entry three tiles ahead, an L2 prefetch of the row two tiles ahead, the row itself (by all lanes)
 // one tile ahead.
-template <bool kPacked>
+// kFmt: 0 = int8 latent, bf16 rope and fp32 scales in three arrays, 1 = packed 656-byte rows, 2 = bf16 latent and
+// rope arrays (the non-quantised cache). With a bf16 cache nothing passes through registers: when a half of the
+// buffer is free every lane issues its 16-byte `cp.async` copies from L2 (the rows were prefetched there two tiles
+// ago) straight to the swizzled places the dequantised units would go, waits for them, fences and arrives.
+template <int kFmt>
 __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const PairCtx c) {
+  constexpr bool kPacked = kFmt == 1, kBf = kFmt == 2;
   PairCtl* ctl = c.ctl;
   const int ntiles = c.ntiles, bi = c.bi;
   const int lane = threadIdx.x & 31;
@@ -613,7 +618,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   const int my_row = 64 * static_cast<int>(c.crank) + 8 * w + (lane & 7);  // key of the tile this lane looks ahead for
   const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
   const int n_mine = c.end - (c.begin + my_row);  // entry j * 128 of idx_ptr is valid iff j * 128 < n_mine
-  constexpr int stride_n = kPacked ? 656 : 512, stride_r = kPacked ? 656 : 128, stride_s = kPacked ? 656 : 16;
+  constexpr int stride_n = kPacked ? 656 : (kBf ? 1024 : 512), stride_r = kPacked ? 656 : 128, stride_s = kPacked ? 656 : 16;
   // (the base pointers are read from the parameter block where they are used: they would otherwise occupy six
   // registers across the whole tile loop)
 #define PAIR_KN reinterpret_cast<const uint8_t*>(p.kn)
@@ -627,6 +632,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
   // `phys`: this lane's look-ahead row of the tile (-1: padding or rejected -> zeros with scale 0)
   auto issue_loads = [&](RowRegs& r, int phys) {
+    if (kBf) return;  // (copied from L2 when the buffer is free)
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int pm = __shfl_sync(0xffffffffu, phys, 2 * m + s2);
@@ -650,7 +656,12 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   };
   auto prefetch_row = [&](int phys) {  // lanes r, r+8, r+16, r+24 share a row: one of its four latent lines each, two of them the rest
     if (phys < 0) return;
-    if (kPacked) {
+    if (kBf) {  // eight latent lines and the rope line of the row
+      const uint8_t* a = PAIR_KN + static_cast<int64_t>(phys) * 1024;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a + (lane >> 3) * 128));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 512 + (lane >> 3) * 128));
+      if (lane < 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(PAIR_ROPE + static_cast<int64_t>(phys) * 128));
+    } else if (kPacked) {
       const uint8_t* a = PAIR_KN + static_cast<int64_t>(phys) * 656;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(a + (lane >> 3) * 128));
       if (lane < 16) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + 512 + (lane >> 3) * 128));
@@ -667,6 +678,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
   RowRegs ra;
   pdl_wait();          // the selected indices come from the kernel before this one, which may still be running
   if (ptid == 0) TLP(3, 21);
+  int row_cur;         // this lane's row of tile j (bf16 cache: the copies are issued when the buffer is free)
   int row_n;           // this lane's row of tile j+1
   int idx_a, entry_a;  // tile j+2
   int idx_b;           // tile j+3
@@ -679,12 +691,14 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
     const int e1 = tc_table_entry(p, bi, idx1);
     entry_a = tc_table_entry(p, bi, idx_a);
     if (ptid == 0 && e0 + e1 + entry_a != -12345) TLP(5, 21);
-    issue_loads(ra, pair_row(p, idx0, e0));
+    row_cur = pair_row(p, idx0, e0);
+    issue_loads(ra, row_cur);
+    if (kBf) prefetch_row(row_cur);
     row_n = pair_row(p, idx1, e1);
     prefetch_row(row_n);
     if (ptid == 0) TLP(6, 21);
   }
-  if (ptid == 0 && ra.d[0][0].x != 0x7fffffffu) TLP(7, 21);  // first rows arrived
+  if (!kBf && ptid == 0 && ra.d[0][0].x != 0x7fffffffu) TLP(7, 21);  // first rows arrived
   pair_setup_sync(ctl);
   for (int j = 0; j < ntiles && ok; ++j) {
 #pragma unroll
@@ -697,21 +711,35 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
 #pragma unroll
       for (int m = 0; m < 4; ++m) {  // row 8w + 2m + s2 (its swizzle term is 2m + s2); scale 2 half + u / 8 of that row
         const int x = 2 * m + s2;
-        const float scale = __shfl_sync(0xffffffffu, ra.sc, 4 * x + 2 * half + (u >> 3));
         const uint32_t row_addr = k_rows + half * 4 * kChunk + x * 128;
         const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
-        const uint4 v = ra.d[half][m];
-        // first half of the unit (bytes 0-7) belongs at `a`, second half at `b`; odd chunks store the second first
-        sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
-        sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+        if (kBf) {  // the unit's 16 values are 32 bytes of the bf16 row: two copies
+          const int pm = __shfl_sync(0xffffffffu, row_cur, x);
+          const uint8_t* src = PAIR_KN + (pm >= 0 ? static_cast<int64_t>(pm) * 1024 + half * 512 + u * 32 : 0);
+          cp_async_16(row_addr + a, src, pm >= 0 ? 16u : 0u);
+          cp_async_16(row_addr + b, src + (pm >= 0 ? 16 : 0), pm >= 0 ? 16u : 0u);
+        } else {
+          const float scale = __shfl_sync(0xffffffffu, ra.sc, 4 * x + 2 * half + (u >> 3));
+          const uint4 v = ra.d[half][m];
+          // first half of the unit (bytes 0-7) belongs at `a`, second half at `b`; odd chunks store the second first
+          sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
+          sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+        }
       }
       if (half == 1) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {  // rope of row 8w + 4i + lane / 8
           const int r8 = 4 * i + (lane >> 3);
-          sts_v4u(c.base + kSmemK + 8 * kChunk + (8 * w + r8) * 128 + (((lane & 7) ^ r8) << 4), ra.r[i]);
+          const uint32_t dst = c.base + kSmemK + 8 * kChunk + (8 * w + r8) * 128 + (((lane & 7) ^ r8) << 4);
+          if (kBf) {
+            const int pr = __shfl_sync(0xffffffffu, row_cur, r8);
+            cp_async_16(dst, PAIR_ROPE + (pr >= 0 ? static_cast<int64_t>(pr) * 128 + (lane & 7) * 16 : 0), pr >= 0 ? 16u : 0u);
+          } else {
+            sts_v4u(dst, ra.r[i]);
+          }
         }
       }
+      if (kBf) asm volatile("cp.async.wait_all;" ::: "memory");
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->kfull[half]));
@@ -719,6 +747,7 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
     }
     if (!ok) break;
     if (j + 1 < ntiles) issue_loads(ra, row_n);  // rows of tile j+1 (in L2: prefetched a tile ago)
+    row_cur = row_n;
     row_n = pair_row(p, idx_a, entry_a);         // tile j+2: into L2
     prefetch_row(row_n);
     idx_a = idx_b;
@@ -739,8 +768,9 @@ __device__ __forceinline__ void pair_role_kproducer(const SfaParams& p, const Pa
 // second half first in odd chunks as in the K producers. Key half 0 is stored when the P.V of the previous tile
 // has read keys 0-63, key half 1 when it has read the rest. Lane r % 16 walks the look-ahead chain of row
 // 64 (r / 8) + 8w + r % 8 (no L2 prefetch: the row's owner issues it).
-template <bool kPacked>
+template <int kFmt>
 __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const PairCtx c) {
+  constexpr bool kPacked = kFmt == 1, kBf = kFmt == 2;
   PairCtl* ctl = c.ctl;
   const int ntiles = c.ntiles;
   const int lane = threadIdx.x & 31;
@@ -751,13 +781,14 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
   const int32_t* idx_ptr = c.idx_row + c.begin + my_row;
   const int n_mine = c.end - (c.begin + my_row);
   const int col0 = 256 * static_cast<int>(c.crank);  // first latent byte of this CTA's value columns
-  constexpr int stride_n = kPacked ? 656 : 512, stride_s = kPacked ? 656 : 16;
+  constexpr int stride_n = kPacked ? 656 : (kBf ? 1024 : 512), stride_s = kPacked ? 656 : 16;
   struct RowRegs {
     uint4 d[2][4];  // [key half][m]: unit u of row 64 half + 8w + 2m + s2
     float sc;       // scale lane % 2 (of this CTA's two) of the row lane / 2 (chain order: half * 8 + r)
   };
   auto load_idx = [&](int j) -> int { return (j < ntiles && j * kPT < n_mine) ? ldg_pinned_i32(idx_ptr + j * kPT) : -1; };
   auto issue_loads = [&](RowRegs& r, int phys) {
+    if (kBf) return;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -778,14 +809,15 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
   uint32_t nwait = 0;
   RowRegs ra;
   pdl_wait();
-  int row_n, idx_a, entry_a;  // this lane's row of tile j+1; index and block-table entry of tile j+2
+  int row_cur, row_n, idx_a, entry_a;  // this lane's row of tiles j and j+1; index and block-table entry of tile j+2
   {
     const int idx0 = load_idx(0), idx1 = load_idx(1);
     idx_a = load_idx(2);
     const int e0 = tc_table_entry(p, c.bi, idx0);
     const int e1 = tc_table_entry(p, c.bi, idx1);
     entry_a = tc_table_entry(p, c.bi, idx_a);
-    issue_loads(ra, pair_row(p, idx0, e0));
+    row_cur = pair_row(p, idx0, e0);
+    issue_loads(ra, row_cur);
     row_n = pair_row(p, idx1, e1);
   }
   pair_setup_sync(ctl);
@@ -800,13 +832,21 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
 #pragma unroll
       for (int m = 0; m < 4; ++m) {  // row 64 half + 8w + 2m + s2: swizzle term 2m + s2, scale held by lane 2 (8 half + 2m + s2) + u / 8
         const int x = 2 * m + s2;
-        const float scale = __shfl_sync(0xffffffffu, ra.sc, 2 * (8 * half + x) + (u >> 3));
         const uint32_t row_addr = v_rows + half * kVHalfBytes + x * 128;
         const uint32_t a = ((2 * (u & 3)) ^ x) << 4, b = ((2 * (u & 3) + 1) ^ x) << 4;
-        const uint4 v = ra.d[half][m];
-        sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
-        sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+        if (kBf) {
+          const int pm = __shfl_sync(0xffffffffu, row_cur, 8 * half + x);
+          const uint8_t* src = PAIR_KN + (pm >= 0 ? static_cast<int64_t>(pm) * 1024 + 2 * col0 + u * 32 : 0);
+          cp_async_16(row_addr + a, src, pm >= 0 ? 16u : 0u);
+          cp_async_16(row_addr + b, src + (pm >= 0 ? 16 : 0), pm >= 0 ? 16u : 0u);
+        } else {
+          const float scale = __shfl_sync(0xffffffffu, ra.sc, 2 * (8 * half + x) + (u >> 3));
+          const uint4 v = ra.d[half][m];
+          sts_v4u(row_addr + (odd ? b : a), pair_dequant8(odd ? v.z : v.x, odd ? v.w : v.y, scale));
+          sts_v4u(row_addr + (odd ? a : b), pair_dequant8(odd ? v.x : v.z, odd ? v.y : v.w, scale));
+        }
       }
+      if (kBf) asm volatile("cp.async.wait_all;" ::: "memory");
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->vfull[half]));
@@ -814,6 +854,7 @@ __device__ __forceinline__ void pair_role_vproducer(const SfaParams& p, const Pa
     }
     if (!ok) break;
     if (j + 1 < ntiles) issue_loads(ra, row_n);
+    row_cur = row_n;
     row_n = pair_row(p, idx_a, entry_a);
     idx_a = load_idx(j + 3);
     entry_a = tc_table_entry(p, c.bi, idx_a);  // (the index was requested this iteration: one trip to L2 here, after the
@@ -938,12 +979,14 @@ sfa_pair_kernel(const __grid_constant__ SfaParams p) {
     pair_role_softmax(p, c);
   } else if (warp < kPairVWarp0) {
     PAIR_SETREG("setmaxnreg.inc.sync.aligned.u32 72;");  // (no change of the count; without it ptxas spills in this role)
-    if (p.packed) pair_role_kproducer<true>(p, c);
-    else pair_role_kproducer<false>(p, c);
+    if (p.kn_bf16) pair_role_kproducer<2>(p, c);
+    else if (p.packed) pair_role_kproducer<1>(p, c);
+    else pair_role_kproducer<0>(p, c);
   } else {
     PAIR_SETREG("setmaxnreg.dec.sync.aligned.u32 64;");
-    if (p.packed) pair_role_vproducer<true>(p, c);
-    else pair_role_vproducer<false>(p, c);
+    if (p.kn_bf16) pair_role_vproducer<2>(p, c);
+    else if (p.packed) pair_role_vproducer<1>(p, c);
+    else pair_role_vproducer<0>(p, c);
   }
 
   // ---- teardown: neither CTA may leave while the peer's MMAs can still read its shared memory --------
