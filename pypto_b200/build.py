@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libpypto_b200.so"
-SOURCES = ["capi.cu", "li_score.cu", "topk_select.cu", "sfa_decode.cu", "sfa_cluster.cu", "sfa_pair.cu", "prolog.cu", "prolog_gemm.cu",
+SOURCES = ["capi.cu", "li_score.cu", "topk_select.cu", "sfa_decode.cu", "sfa_pair.cu", "prolog.cu", "prolog_gemm.cu",
            "prolog_sgemm.cu"]
 HEADERS = [CSRC / "common.cuh", CSRC / "sfa_common.cuh", PKG.parent / "include" / "pypto_b200.h"]
 

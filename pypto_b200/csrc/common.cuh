@@ -333,8 +333,7 @@ cudaError_t launch_li_score_tc(const LiParams& p, const void* tmap_k, const void
 cudaError_t launch_li_score_simt(const LiParams& p, cudaStream_t stream);
 cudaError_t launch_li_topk(const TopkParams& p, int num_sms, cudaStream_t stream);
 cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream);
-cudaError_t launch_sfa_cluster(const SfaParams& p, cudaStream_t stream);  // nq == 128 only, 2-CTA cluster (bf16 latent cache)
-cudaError_t launch_sfa_pair(const SfaParams& p, cudaStream_t stream);     // nq == 128, int8 cache: 2-SM MMAs, heads split over the pair
+cudaError_t launch_sfa_pair(const SfaParams& p, cudaStream_t stream);     // nq == 128, any cache format: 2-SM MMAs, heads split over the pair
 int sfa_pair_split(int t, int num_sms);
 
 // Launch with the programmatic-serialization attribute when `pdl`: the grid may be scheduled while the kernel

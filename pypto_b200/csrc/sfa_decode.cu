@@ -14,8 +14,6 @@
 // consumed by bf16 mma.sync (m16n8k16, fp32 accumulate) for both q.K^T and P.V with an online
 // softmax: P = bf16(exp(s - running max)) un-normalised, (m, l, O) in fp32, one rounding of P and
 // one of the output. Splits are merged by `sfa_combine_kernel`.
-#include <cstdlib>
-#include <cstring>
 
 #include "common.cuh"
 
@@ -477,14 +475,9 @@ cudaError_t launch_sfa(const SfaParams& p, cudaStream_t stream) {
   const int t = p.b * p.s1;
   const int n_hb = (p.nq + kHB - 1) / kHB;
   if (p.nq == 128) {
-    // all 128 heads of a token: tcgen05 kernels on a pair of SMs; narrower head slices use mma.sync below.
-    // int8 cache: the pair shares every MMA (heads split, sfa_pair.cu); bf16 cache: the pair splits the
-    // contraction (sfa_cluster.cu), which PTO_SFA_IMPL=cluster also selects for the int8 cache (A/B timing aid)
-    static const bool force_cluster = [] {
-      const char* v = getenv("PTO_SFA_IMPL");
-      return v != nullptr && strcmp(v, "cluster") == 0;
-    }();
-    e = force_cluster ? launch_sfa_cluster(p, stream) : launch_sfa_pair(p, stream);
+    // all 128 heads of a token: the tcgen05 kernel on a pair of SMs that shares every MMA (sfa_pair.cu; int8, packed
+    // and bf16 caches); narrower head slices use mma.sync below
+    e = launch_sfa_pair(p, stream);
   } else {
     count_launch();
     sfa_mma_kernel<<<t * n_hb * p.n_split, kSfaThreads, sizeof(SfaSmem), stream>>>(p);

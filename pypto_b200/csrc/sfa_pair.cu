@@ -20,11 +20,17 @@
 // Tensor memory of a 2-SM MMA with 64 rows per CTA: lanes 0-63 hold the first half of the N columns, lanes
 // 64-127 the second half (row = lane % 64). So of a score tile lane l holds (head l % 64, keys 64 (l / 64) ..+63),
 // and of O lane l holds (head l % 64, values 256 (l / 64) ..+255).
-//   warp 0          CTA 0: issues every MMA (event loop over "keys ready", "scores read", "P written", "V ready")
-//   warp 1          CTA 1: forwards those four events of its own to CTA 0 (tcgen05.commit arrivals on CTA 0's barriers)
+//   warp 0          CTA 0: issues the q.K^T MMAs of a tile as soon as its keys are ready and a score buffer is free
+//   warp 2          CTA 0: issues the P.V MMAs of a tile as soon as P is written and the values are ready
+//                   (two issuing threads on two schedulers: neither queue waits behind the other's barrier)
+//   warp 1          CTA 1: forwards the "ready" events of its own CTA to CTA 0 (tcgen05.commit arrivals on CTA 0's barriers)
 //   warps 4..11     softmax: four threads per head (two TMEM lanes x two column halves), P goes to shared memory
 //   warps 12..19    K producers: 16-byte gathers of the CTA's 64 rows, int8 -> bf16 in registers, swizzled stores
 //   warps 20..27    V producers: this CTA's half of the value columns of all 128 rows
+// Cache formats: int8 latent + bf16 rope + fp32 scales in three arrays, the same as packed 656-byte rows, or bf16
+// latent + rope arrays (the non-quantised cache): there the producers dequantise nothing, they copy the rows' bytes
+// from L2 to the same swizzled places with cp.async once a buffer half is free. The MMAs, the softmax and the
+// output are the same code, so the bf16 cache of dequantised values gives the int8 cache's output bit for bit.
 // Roles are uniform within each group of four warps so that registers can be moved between them (setmaxnreg):
 // 72 per thread at launch (seven warps share one scheduler's file of 512 x 32), then 24 / 104 / 72 / 64:
 // nothing spills (a spilled register costs a trip to L2: beside 227 KB of shared memory there is no L1 to speak of).
