@@ -931,23 +931,27 @@ int pto_mla_indexer_prolog(const void* token_x, const void* w_dq, const void* w_
   PTO_CUDA(pto::launch_prolog_kv_bf16(kv, ki, wp, ld, splits, split_stride, gamma_ckv, cos, sin, ln_gamma, ln_beta,
                                       cache_index, cache_rows, t, eps_ckv, ln_eps, kv_cache, kr_cache, idx_k_cache,
                                       weights_out, status, side));
-  PTO_CUDA(cudaEventRecord(ev[2], side));
-  // caller's stream: normalised query -> the two up-projections (bf16 in, bf16 out) -> ropes -> absorbed nope part
+  // caller's stream: normalised query -> attention up-projection (bf16 in, bf16 out) -> ropes -> absorbed nope part.
+  // The indexer's up-projection (64 column tiles) runs on the side stream beside the attention one (192 tiles on
+  // 148 CTAs: its second wave leaves two thirds of the SMs free), behind the per-token kernel.
   PTO_CUDA(pto::launch_prolog_qnorm_bf16(qa, ld, splits, split_stride, gamma_cq, t, q_lora, eps_cq, q_norm, stream,
                                          /*pdl=*/true));
+  PTO_CUDA(cudaEventRecord(ev[1], stream));
   const size_t qn_pitch = static_cast<size_t>(q_lora) * 2;
   rc = run_sgemm(1, q_norm, qn_pitch, w_uqqr, 128 * 192 * 2, q_lora, q_b, t, 128 * 192, q_lora, 1, 0, 0, 0, 128 * 192, 1, 0,
-                 di.num_sms, status, stream, /*pdl=*/true);
+                 di.num_sms, status, stream);
   if (rc != PTO_OK) return rc;
+  PTO_CUDA(cudaStreamWaitEvent(side, ev[1], 0));
   rc = run_sgemm(1, q_norm, qn_pitch, w_idx_qb, 64 * 128 * 2, q_lora, idx_query_out, t, 64 * 128, q_lora, 1, 0, 0, 0,
-                 64 * 128, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
+                 64 * 128, 1, 0, di.num_sms, status, side);
   if (rc != PTO_OK) return rc;
-  PTO_CUDA(pto::launch_prolog_rope_bf16(q_b, cos, sin, t, query_rope_out, idx_query_out, stream, /*pdl=*/true));
+  PTO_CUDA(cudaEventRecord(ev[2], side));
+  PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));  // the rope kernel reads both products
+  PTO_CUDA(pto::launch_prolog_rope_bf16(q_b, cos, sin, t, query_rope_out, idx_query_out, stream));
   rc = run_sgemm(1, q_b, 128 * 192 * 2, w_uk, 512 * 2, 128 * 128, query_nope_out, t, 512, 128, 128, 128, 192 * 2, 512,
                  128 * 512, 1, 0, di.num_sms, status, stream, /*pdl=*/true);
   if (rc != PTO_OK) return rc;
-  PTO_CUDA(cudaStreamWaitEvent(stream, ev[2], 0));
-  return PTO_OK;
+  return PTO_OK;  // (the side stream was joined in front of the rope kernel)
 }
 
 size_t pto_decode_workspace_bytes(int t, int max_blocks, int block_size, int nq) {
