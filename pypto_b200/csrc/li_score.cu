@@ -297,6 +297,8 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
       if (warp == 0) {
         // ---------------- TMA producer ----------------
         const int32_t* bt = p.block_table + static_cast<int64_t>(bi) * p.max_blocks + page0;
+        // key pages are read once: first to leave L2, so that the score rows written for the selection stay there
+        const uint64_t stream_policy = l2_policy_evict_first();
         bool ok = true;
         for (int j0 = 0; j0 < npages && ok; j0 += 32) {
           const int mine = (j0 + lane < npages) ? bt[j0 + lane] : 0;
@@ -322,11 +324,11 @@ li_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
                 const uint32_t dst = stage_base + slot * kStage;
                 if (kBf16) {
                   mbar_arrive_expect_tx(bar, kBf16PageBytes);
-                  tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
-                  tma_load_2d(dst + kPageBytes, &tmap_k, 128, phys * kPageKeys, bar);
+                  tma_load_2d_hint(dst, &tmap_k, 0, phys * kPageKeys, bar, stream_policy);
+                  tma_load_2d_hint(dst + kPageBytes, &tmap_k, 128, phys * kPageKeys, bar, stream_policy);
                 } else {
                   mbar_arrive_expect_tx(bar, kPageBytes + scale_bytes);
-                  tma_load_2d(dst, &tmap_k, 0, phys * kPageKeys, bar);
+                  tma_load_2d_hint(dst, &tmap_k, 0, phys * kPageKeys, bar, stream_policy);
                   bulk_load_1d(dst + kPageBytes,
                                reinterpret_cast<const uint8_t*>(p.k_scale) + static_cast<int64_t>(scale_page) * scale_bytes,
                                scale_bytes, bar);
