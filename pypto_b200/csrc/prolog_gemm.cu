@@ -112,6 +112,7 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
       mbar_arrive_expect_tx(smem_u32(&ctl->x_full), static_cast<uint32_t>(chunks) * x_slab);
       for (int c = 0; c < chunks; ++c) tma_load_2d(x_base + c * x_slab, &tmap_x, c * kGTileK, 0, smem_u32(&ctl->x_full));
       uint32_t it = 0;
+      const uint64_t w_policy = l2_policy_evict_first();  // weights are read once per call
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const bool second = tile >= p.tiles[0];
         const CUtensorMap* tm = second ? &tmap_w1 : &tmap_w0;
@@ -123,7 +124,7 @@ prolog_i8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_
             if (!ok) break;
           }
           mbar_arrive_expect_tx(smem_u32(&ctl->full[s]), kGStageBytes);
-          tma_load_2d(a_base + s * kGStageBytes, tm, n0, c * kGTileK, smem_u32(&ctl->full[s]));
+          tma_load_2d_hint(a_base + s * kGStageBytes, tm, n0, c * kGTileK, smem_u32(&ctl->full[s]), w_policy);
         }
       }
       if (!ok) {

@@ -130,6 +130,8 @@ prolog_sgemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;
+      // weights are read once per call: first to leave L2, so that activations and partial sums stay there
+      const uint64_t w_policy = l2_policy_evict_first();
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const SItem w = s_item(p, item);
         const int k0 = w.split * p.per_split;
@@ -146,10 +148,10 @@ prolog_sgemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const int krow = w.b * p.w_batch_rows + (k0 + c) * kChunkK;
           mbar_arrive_expect_tx(bar, kSWBytes + x_bytes);
           if (kI8) {
-            tma_load_2d(dst, &tmap_w, n0, krow, bar);
+            tma_load_2d_hint(dst, &tmap_w, n0, krow, bar, w_policy);
           } else {
-            tma_load_2d(dst, &tmap_w, n0 * 2, krow, bar);
-            tma_load_2d(dst + kSWBytes / 2, &tmap_w, n0 * 2 + 128, krow, bar);
+            tma_load_2d_hint(dst, &tmap_w, n0 * 2, krow, bar, w_policy);
+            tma_load_2d_hint(dst + kSWBytes / 2, &tmap_w, n0 * 2 + 128, krow, bar, w_policy);
           }
           tma_load_2d(dst + kSWBytes, &tmap_x, w.b * p.x_batch_bytes + (k0 + c) * 128, w.tb * p.t_pad, bar);
         }
