@@ -729,6 +729,12 @@ def main():
         torch.cuda.synchronize()
         kernel_ms[name] = time_each(fn, args.steps, stream, before)
     assert pto.workspace_status(dev)[0] == 0, "device status flagged an error"
+    # the whole step with 256 MB written before every replay: the timed loop above replays the same inputs, so the
+    # rows the attention gathered in one step (about 100 MB on one GPU) are partly still in L2 in the next
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    cold_ms = time_each(step, args.steps, stream, flush.zero_)
 
     # ---- sustained: the same replay looped for at least two seconds, clocks sampled (nothing is set) -------------
     sustained = None
@@ -858,7 +864,7 @@ def main():
 
     # max over ranks
     v = torch.tensor([total_ms, e2e_s, kernel_ms["li_score"], kernel_ms["topk"], kernel_ms["sfa"], eager_ms,
-                      sustained["ms_per_step"] if sustained else 0.0, weak_ms or 0.0, layer_s or 0.0, h2d_ms],
+                      sustained["ms_per_step"] if sustained else 0.0, weak_ms or 0.0, layer_s or 0.0, h2d_ms, cold_ms],
                      dtype=torch.float64, device=dev)
     # algorithmic bytes and flops summed over the ranks' shards
     by = gen.algorithmic_bytes(d)
@@ -869,7 +875,7 @@ def main():
     if world > 1:
         dist.all_reduce(v, op=dist.ReduceOp.MAX)
         dist.all_reduce(w, op=dist.ReduceOp.SUM)
-    (total_ms, e2e_s, li_ms, topk_ms, sfa_ms, eager_ms, sus_ms_step, weak_ms, layer_s, h2d_ms) = (float(x) for x in v.tolist())
+    (total_ms, e2e_s, li_ms, topk_ms, sfa_ms, eager_ms, sus_ms_step, weak_ms, layer_s, h2d_ms, cold_ms) = (float(x) for x in v.tolist())
     by_li, by_sfa, by_score, fl_sfa, t_all, ops_li = (float(x) for x in w.tolist())
 
     if rank == 0:
@@ -928,7 +934,8 @@ def main():
                        "scale_dtype": args.scale_dtype,
                        "partition": f"{partition}; no collective on the data path",
                        "l2": f"inputs ({d.block_num * 128 * (132 + 656) / 1e9:.2f} GB of cache on rank 0) larger than L2, "
-                             "no flush needed between steps"},
+                             "no flush between the timed steps; `step_cold_l2` is the same step with 256 MB written "
+                             "before every replay"},
             "parity_checked": bool(parity and parity["ok"]), "parity": parity,
             "multi_gpu_validation": multi,
             "roofline": roof_sfa if dominant == "sfa" else roof_li,
@@ -937,6 +944,10 @@ def main():
                               "frac": step_gbs / peak, "algorithmic_bytes_per_step_all_ranks":
                                   {"indexer": int(by_li), "attention": int(by_sfa), "total": int(by_li + by_sfa)},
                               "note": "per GPU: all ranks' algorithmic bytes / N over the max-over-ranks step time"},
+            "step_cold_l2": {"ms_per_step": cold_ms, "value": t_all / (cold_ms * 1e-3),
+                             "note": "every replay timed alone with CUDA events, 256 MB written before it: the replayed "
+                                     "inputs are the same every step, so without the flush part of the rows the "
+                                     "attention gathered (and the queries) are still in L2 from the step before"},
             "kernel_ms": {"li_score": li_ms, "topk": topk_ms, "sfa": sfa_ms, "sum": li_ms + topk_ms + sfa_ms,
                           "note": "each kernel alone, CUDA events around every launch, max over ranks; the attention "
                                   "launch includes its combine kernel when the rows are split over CTAs"},
